@@ -1,0 +1,689 @@
+// Host side of the C ABI declared in include/nvfp4_b200.h: argument validation,
+// schedule choice, tensor-map encoding, workspace layout and launches. No function
+// here allocates device memory, throws, or synchronises except nvfp4_plan_status.
+
+#include "../../include/nvfp4_b200.h"
+
+#include <algorithm>
+#include <climits>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "nvfp4_gemm_kernel.cuh"
+#include "nvfp4_glue_kernels.cuh"
+
+using namespace nvfp4;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+int fail_cuda(cudaError_t err, const char* what) {
+  // Clear the sticky-free error so that later calls do not see it again.
+  cudaGetLastError();
+  return fail(static_cast<int>(err), "%s: %s", what, cudaGetErrorString(err));
+}
+
+#define CUDA_TRY(expr)                                   \
+  do {                                                   \
+    cudaError_t err__ = (expr);                          \
+    if (err__ != cudaSuccess) return fail_cuda(err__, #expr); \
+  } while (0)
+
+struct DeviceGuard {
+  int saved = -1;
+  bool active = false;
+  cudaError_t enter(int device) {
+    cudaError_t e = cudaGetDevice(&saved);
+    if (e != cudaSuccess) return e;
+    if (saved != device) {
+      e = cudaSetDevice(device);
+      if (e != cudaSuccess) return e;
+      active = true;
+    }
+    return cudaSuccess;
+  }
+  ~DeviceGuard() {
+    if (active) cudaSetDevice(saved);
+  }
+};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library has no
+// link-time dependency on libcuda (it must load on machines without a driver).
+int get_encoder(EncodeTiledFn* out) {
+  static std::mutex mu;
+  static EncodeTiledFn cached = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t err =
+        cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (err != cudaSuccess) return fail_cuda(err, "cudaGetDriverEntryPoint");
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+      return fail(NVFP4_E_UNSUPPORTED_DEVICE, "driver has no cuTensorMapEncodeTiled");
+    }
+    cached = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = cached;
+  return 0;
+}
+
+// Packed E2M1 operand [batches][rows][k/2] bytes as a rank-3 uint8 tensor with a
+// 128-byte (256-element) x box_rows box, 128-byte swizzle, zero fill out of bounds.
+int encode_operand_map(CUtensorMap* map, const void* ptr, int rows, int k, int batches,
+                       int box_rows) {
+  EncodeTiledFn encode = nullptr;
+  if (int rc = get_encoder(&encode)) return rc;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(k) / 2;
+  const cuuint64_t dims[3] = {row_bytes, static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(batches)};
+  const cuuint64_t strides[2] = {row_bytes, row_bytes * static_cast<cuuint64_t>(rows)};
+  const cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), 1u};
+  const cuuint32_t elem_strides[3] = {1u, 1u, 1u};
+  CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims,
+                        strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    return fail(static_cast<int>(res),
+                "cuTensorMapEncodeTiled failed (%d) for rows=%d k=%d batches=%d box_rows=%d",
+                static_cast<int>(res), rows, k, batches, box_rows);
+  }
+  return 0;
+}
+
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+size_t round_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
+
+enum PlanKind { kDense = 0, kDual = 1, kGrouped = 2 };
+
+using KernelFn = void (*)(const KernelParams);
+
+struct KernelChoice {
+  KernelFn fn;
+  int smem_bytes;
+  int stages;
+  int threads;
+};
+
+template <class Cfg>
+KernelChoice make_choice() {
+  return KernelChoice{&nvfp4_gemm_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::STAGES, Cfg::THREADS};
+}
+
+// kind, out_kind, tile_n -> kernel instantiation. Returns fn == nullptr if absent.
+KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
+  if (kind == kDual) {
+    return make_choice<GemmConfig<256, true, __half, false>>();
+  }
+  if (kind == kGrouped) {
+    switch (tile_n) {
+      case 64: return make_choice<GemmConfig<64, false, __half, true>>();
+      case 128: return make_choice<GemmConfig<128, false, __half, true>>();
+      case 256: return make_choice<GemmConfig<256, false, __half, true>>();
+    }
+  } else if (out_kind == NVFP4_OUT_F16) {
+    switch (tile_n) {
+      case 64: return make_choice<GemmConfig<64, false, __half, false>>();
+      case 128: return make_choice<GemmConfig<128, false, __half, false>>();
+      case 256: return make_choice<GemmConfig<256, false, __half, false>>();
+    }
+  } else {
+    switch (tile_n) {
+      case 64: return make_choice<GemmConfig<64, false, float, false>>();
+      case 128: return make_choice<GemmConfig<128, false, float, false>>();
+      case 256: return make_choice<GemmConfig<256, false, float, false>>();
+    }
+  }
+  return KernelChoice{nullptr, 0, 0, 0};
+}
+
+}  // namespace
+
+struct nvfp4_plan {
+  int kind = kDense;
+  int device = 0;
+  int out_kind = NVFP4_OUT_F16;
+  int sm_count = 0;
+  int tile_n = 128;   // MMA N
+  int out_tile_n = 128;
+  int schedule = 1;   // 1 data parallel, 2 stream-K
+  int ctas = 1;
+  KernelChoice kernel{};
+  std::vector<ProblemDesc> problems;  // pointers filled at launch / bind
+  long long total_tiles = 0, total_units = 0;
+  long long slot_floats = 0;
+  size_t off_counters = 0, off_table = 0, off_maps = 0, off_partials = 0, ws_bytes = 0;
+  // Last operands a dense/dual launch encoded maps for.
+  const void* bound[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  void* bound_ws = nullptr;
+  bool params_valid = false;
+  KernelParams params{};
+  std::vector<uint8_t> staging;  // grouped: table + maps as uploaded
+};
+
+namespace {
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  if (v == nullptr || *v == '\0') return fallback;
+  return std::atoi(v);
+}
+
+// Tile width, schedule and grid for a list of problems whose tile counts are already
+// filled for every candidate width. Data parallel when whole tiles fill the SMs
+// evenly enough; otherwise stream-K over (tile, k-tile) units.
+void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
+  long long tiles = 0, units = 0;
+  for (ProblemDesc& pd : plan->problems) {
+    pd.tile_begin = tiles;
+    pd.unit_begin = units;
+    const long long t = static_cast<long long>(pd.tiles_m) * pd.tiles_n * pd.batches;
+    tiles += t;
+    units += t * pd.k_tiles;
+  }
+  plan->total_tiles = tiles;
+  plan->total_units = units;
+
+  const int sms = plan->sm_count;
+  int schedule = config != nullptr && config->schedule > 0 ? config->schedule
+                                                            : env_int("NVFP4_SCHEDULE", 0);
+  int ctas = config != nullptr && config->ctas > 0 ? config->ctas : env_int("NVFP4_CTAS", 0);
+  if (ctas > sms) ctas = sms;
+
+  if (schedule != 1 && schedule != 2) {
+    if (tiles >= sms) {
+      const long long waves = (tiles + sms - 1) / sms;
+      const double efficiency = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+      schedule = efficiency >= 0.9 ? 1 : 2;
+    } else {
+      // Fewer tiles than SMs: split K while every CTA keeps at least four k-tiles.
+      const long long by_units = units / 4;
+      schedule = by_units > tiles ? 2 : 1;
+    }
+  }
+  if (ctas <= 0) {
+    if (schedule == 1) {
+      ctas = static_cast<int>(std::min<long long>(sms, tiles));
+    } else {
+      const long long by_units = std::max<long long>(tiles, units / 4);
+      ctas = static_cast<int>(std::min<long long>(sms, std::max<long long>(1, by_units)));
+    }
+  }
+  if (schedule == 1) ctas = static_cast<int>(std::min<long long>(ctas, tiles));
+  if (schedule == 2) ctas = static_cast<int>(std::min<long long>(ctas, units));
+  if (ctas < 1) ctas = 1;
+  plan->schedule = schedule;
+  plan->ctas = ctas;
+
+  // Workspace: [status 256 B][counters][group table][group maps][partials].
+  size_t off = 256;
+  plan->off_counters = off;
+  off += round_up(static_cast<size_t>(tiles) * sizeof(unsigned int), 256);
+  plan->off_table = off;
+  if (plan->kind == kGrouped) {
+    off += round_up(plan->problems.size() * sizeof(ProblemDesc), 256);
+    plan->off_maps = off;
+    off += round_up(plan->problems.size() * 2 * sizeof(CUtensorMap), 256);
+  } else {
+    plan->off_maps = off;
+  }
+  plan->off_partials = off;
+  plan->slot_floats = 128ll * plan->tile_n;
+  if (schedule == 2) {
+    off += static_cast<size_t>(2) * ctas * plan->slot_floats * sizeof(float);
+  }
+  plan->ws_bytes = off;
+}
+
+int fill_problem(ProblemDesc* pd, int m, int n, int k, int batches, int out_tile_n) {
+  std::memset(pd, 0, sizeof(*pd));
+  pd->m = m;
+  pd->n = n;
+  pd->k = k;
+  pd->batches = batches;
+  pd->tiles_m = ceil_div(m, 128);
+  pd->tiles_n = ceil_div(n, out_tile_n);
+  pd->k_tiles = ceil_div(k, 256);
+  pd->sf_kb = ceil_div(k, 64);
+  pd->sf_mb = ceil_div(m, 128);
+  pd->sf_nb = ceil_div(n, 128);
+  return 0;
+}
+
+int check_device(int device, int* sm_count) {
+  int count = 0;
+  CUDA_TRY(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "device %d out of range (%d devices)", device, count);
+  }
+  int major = 0, minor = 0;
+  CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device));
+  if (major != 10 || minor != 0) {
+    return fail(NVFP4_E_UNSUPPORTED_DEVICE,
+                "device %d has compute capability %d.%d; these kernels are built for 10.0 "
+                "(sm_100a) only",
+                device, major, minor);
+  }
+  if (sm_count != nullptr) {
+    CUDA_TRY(cudaDeviceGetAttribute(sm_count, cudaDevAttrMultiProcessorCount, device));
+  }
+  return 0;
+}
+
+int default_tile_n(const nvfp4_config* config, int fallback) {
+  int t = config != nullptr && config->tile_n > 0 ? config->tile_n : env_int("NVFP4_TILE_N", 0);
+  if (t == 0) t = fallback;
+  return t;
+}
+
+int prepare_kernel(nvfp4_plan* plan) {
+  plan->kernel = select_kernel(plan->kind, plan->out_kind, plan->tile_n);
+  if (plan->kernel.fn == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "no kernel for tile_n=%d", plan->tile_n);
+  }
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
+  CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void*>(plan->kernel.fn),
+                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                plan->kernel.smem_bytes));
+  return 0;
+}
+
+void fill_common_params(nvfp4_plan* plan, void* workspace) {
+  KernelParams& kp = plan->params;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  kp.status = reinterpret_cast<int*>(ws);
+  kp.counters = reinterpret_cast<unsigned int*>(ws + plan->off_counters);
+  kp.partials = reinterpret_cast<float*>(ws + plan->off_partials);
+  kp.problems = reinterpret_cast<const ProblemDesc*>(ws + plan->off_table);
+  kp.maps = reinterpret_cast<const CUtensorMap*>(ws + plan->off_maps);
+  kp.total_tiles = plan->total_tiles;
+  kp.total_units = plan->total_units;
+  kp.slot_floats = plan->slot_floats;
+  kp.num_problems = static_cast<int>(plan->problems.size());
+  kp.mode = plan->schedule == 2 ? kModeStreamK : kModeDataParallel;
+  bool streams = true;
+  for (const ProblemDesc& pd : plan->problems) {
+    if (pd.tiles_m > 1) streams = false;
+  }
+  kp.b_streams = streams ? 1 : 0;
+  kp.probe = env_int("NVFP4_PROBE_FLAGS", 0);
+}
+
+int launch_plan(nvfp4_plan* plan, void* stream) {
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
+  void* args[1] = {&plan->params};
+  CUDA_TRY(cudaLaunchKernel(reinterpret_cast<const void*>(plan->kernel.fn), dim3(plan->ctas),
+                            dim3(plan->kernel.threads), args, plan->kernel.smem_bytes,
+                            static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+bool aligned(const void* p, uintptr_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
+
+int check_dense_shape(int m, int n, int k, int l, int out_bytes) {
+  if (m < 1 || n < 1 || k < 1 || l < 1 || k % 32 != 0 || (static_cast<long long>(n) * out_bytes) % 16 != 0) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "unsupported problem m=%d n=%d k=%d l=%d", m, n, k, l);
+  }
+  if (l > 1) {
+    const long long mk = static_cast<long long>(m) * k, nk = static_cast<long long>(n) * k,
+                    mn = static_cast<long long>(m) * n;
+    if (std::max(mk, std::max(nk, mn)) > INT_MAX) {
+      return fail(NVFP4_E_UNSUPPORTED_SHAPE, "batch stride exceeds the 32-bit range");
+    }
+  }
+  return 0;
+}
+
+int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int m, int n, int k,
+                      int l, const nvfp4_config* config) {
+  if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
+  *out = nullptr;
+  if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "unknown output kind %d", out_kind);
+  }
+  if (int rc = check_dense_shape(m, n, k, l, out_kind == NVFP4_OUT_F16 ? 2 : 4)) return rc;
+  int sms = 0;
+  if (int rc = check_device(device, &sms)) return rc;
+  nvfp4_plan* plan = new (std::nothrow) nvfp4_plan();
+  if (plan == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "out of host memory");
+  plan->kind = kind;
+  plan->device = device;
+  plan->out_kind = out_kind;
+  plan->sm_count = sms;
+  if (kind == kDual) {
+    plan->tile_n = 256;
+    plan->out_tile_n = 128;
+  } else {
+    plan->tile_n = default_tile_n(config, 128);
+    plan->out_tile_n = plan->tile_n;
+  }
+  plan->problems.resize(1);
+  fill_problem(&plan->problems[0], m, n, k, l, plan->out_tile_n);
+  finish_schedule(plan, config);
+  if (int rc = prepare_kernel(plan)) {
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvfp4_version(void) { return 1000; }
+
+const char* nvfp4_last_error(void) { return g_last_error.c_str(); }
+
+int nvfp4_device_supported(int device) {
+  int rc = check_device(device, nullptr);
+  if (rc == 0) return 1;
+  if (rc == NVFP4_E_UNSUPPORTED_DEVICE) return 0;
+  return rc;
+}
+
+int nvfp4_gemm_plan_create(nvfp4_plan** plan, int device, int out_kind, int m, int n, int k,
+                           int l, const nvfp4_config* config) {
+  return create_dense_like(plan, kDense, device, out_kind, m, n, k, l, config);
+}
+
+int nvfp4_dual_gemm_plan_create(nvfp4_plan** plan, int device, int m, int n, int k, int l,
+                                const nvfp4_config* config) {
+  return create_dense_like(plan, kDual, device, NVFP4_OUT_F16, m, n, k, l, config);
+}
+
+int nvfp4_group_gemm_plan_create(nvfp4_plan** out, int device, int groups, const int* mnk,
+                                 const nvfp4_config* config) {
+  if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
+  *out = nullptr;
+  if (groups < 1 || mnk == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "expected at least one group");
+  }
+  for (int g = 0; g < groups; ++g) {
+    const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
+    if (m < 1 || n < 1 || k < 1 || k % 32 != 0 || n % 8 != 0) {
+      return fail(NVFP4_E_UNSUPPORTED_SHAPE, "group %d: unsupported problem m=%d n=%d k=%d", g,
+                  m, n, k);
+    }
+  }
+  int sms = 0;
+  if (int rc = check_device(device, &sms)) return rc;
+  nvfp4_plan* plan = new (std::nothrow) nvfp4_plan();
+  if (plan == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "out of host memory");
+  plan->kind = kGrouped;
+  plan->device = device;
+  plan->out_kind = NVFP4_OUT_F16;
+  plan->sm_count = sms;
+  plan->tile_n = default_tile_n(config, 128);
+  plan->out_tile_n = plan->tile_n;
+  plan->problems.resize(groups);
+  for (int g = 0; g < groups; ++g) {
+    fill_problem(&plan->problems[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2], 1,
+                 plan->out_tile_n);
+  }
+  finish_schedule(plan, config);
+  if (int rc = prepare_kernel(plan)) {
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return 0;
+}
+
+void nvfp4_plan_destroy(nvfp4_plan* plan) { delete plan; }
+
+size_t nvfp4_plan_workspace_bytes(const nvfp4_plan* plan) {
+  return plan != nullptr ? plan->ws_bytes : 0;
+}
+
+int nvfp4_plan_init_workspace(const nvfp4_plan* plan, void* workspace, void* stream) {
+  if (plan == nullptr || workspace == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "plan or workspace is null");
+  }
+  if (!aligned(workspace, 256)) return fail(NVFP4_E_MISALIGNED, "workspace must be 256-byte aligned");
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
+  CUDA_TRY(cudaMemsetAsync(workspace, 0, plan->off_table, static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info) {
+  if (plan == nullptr || info == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null argument");
+  info->tile_m = 128;
+  info->tile_n = plan->out_tile_n;
+  info->tile_k = 256;
+  info->stages = plan->kernel.stages;
+  info->schedule = plan->schedule;
+  info->ctas = plan->ctas;
+  info->threads = plan->kernel.threads;
+  info->smem_bytes = plan->kernel.smem_bytes;
+  info->tiles = plan->total_tiles;
+  info->units = plan->total_units;
+  info->sm_count = plan->sm_count;
+  return 0;
+}
+
+int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                      const void* sfb, const float* alpha, void* d, void* workspace,
+                      void* stream) {
+  if (plan == nullptr || plan->kind != kDense) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dense GEMM plan");
+  }
+  if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || alpha == nullptr ||
+      d == nullptr || workspace == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  }
+  if (!aligned(a, 16) || !aligned(b, 16) || !aligned(sfa, 16) || !aligned(sfb, 16) ||
+      !aligned(d, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
+    return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
+  }
+  const void* now[8] = {a, b, nullptr, sfa, sfb, nullptr, alpha, d};
+  if (!plan->params_valid || plan->bound_ws != workspace ||
+      std::memcmp(now, plan->bound, sizeof(now)) != 0) {
+    ProblemDesc& pd = plan->problems[0];
+    KernelParams& kp = plan->params;
+    if (int rc = encode_operand_map(&kp.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
+    if (int rc = encode_operand_map(&kp.map_b, b, pd.n, pd.k, pd.batches, plan->tile_n)) return rc;
+    kp.map_b2 = kp.map_b;
+    pd.sfa = static_cast<const uint8_t*>(sfa);
+    pd.sfb = static_cast<const uint8_t*>(sfb);
+    pd.sfb2 = nullptr;
+    pd.d = d;
+    kp.dense = pd;
+    kp.alpha = alpha;
+    fill_common_params(plan, workspace);
+    std::memcpy(plan->bound, now, sizeof(now));
+    plan->bound_ws = workspace;
+    plan->params_valid = true;
+  }
+  return launch_plan(plan, stream);
+}
+
+int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+                           const void* sfa, const void* sfb1, const void* sfb2,
+                           const float* alpha, void* d, void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kDual) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dual GEMM plan");
+  }
+  if (a == nullptr || b1 == nullptr || b2 == nullptr || sfa == nullptr || sfb1 == nullptr ||
+      sfb2 == nullptr || alpha == nullptr || d == nullptr || workspace == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  }
+  if (!aligned(a, 16) || !aligned(b1, 16) || !aligned(b2, 16) || !aligned(sfa, 16) ||
+      !aligned(sfb1, 16) || !aligned(sfb2, 16) || !aligned(d, 16) || !aligned(alpha, 4) ||
+      !aligned(workspace, 256)) {
+    return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
+  }
+  const void* now[8] = {a, b1, b2, sfa, sfb1, sfb2, alpha, d};
+  if (!plan->params_valid || plan->bound_ws != workspace ||
+      std::memcmp(now, plan->bound, sizeof(now)) != 0) {
+    ProblemDesc& pd = plan->problems[0];
+    KernelParams& kp = plan->params;
+    if (int rc = encode_operand_map(&kp.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
+    if (int rc = encode_operand_map(&kp.map_b, b1, pd.n, pd.k, pd.batches, 128)) return rc;
+    if (int rc = encode_operand_map(&kp.map_b2, b2, pd.n, pd.k, pd.batches, 128)) return rc;
+    pd.sfa = static_cast<const uint8_t*>(sfa);
+    pd.sfb = static_cast<const uint8_t*>(sfb1);
+    pd.sfb2 = static_cast<const uint8_t*>(sfb2);
+    pd.d = d;
+    kp.dense = pd;
+    kp.alpha = alpha;
+    fill_common_params(plan, workspace);
+    std::memcpy(plan->bound, now, sizeof(now));
+    plan->bound_ws = workspace;
+    plan->params_valid = true;
+  }
+  return launch_plan(plan, stream);
+}
+
+int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* const* b,
+                          const void* const* sfa, const void* const* sfb, void* const* d,
+                          void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kGrouped) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped GEMM plan");
+  }
+  if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || d == nullptr ||
+      workspace == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null pointer array");
+  }
+  if (!aligned(workspace, 256)) return fail(NVFP4_E_MISALIGNED, "workspace must be 256-byte aligned");
+  const size_t groups = plan->problems.size();
+  for (size_t g = 0; g < groups; ++g) {
+    if (a[g] == nullptr || b[g] == nullptr || sfa[g] == nullptr || sfb[g] == nullptr ||
+        d[g] == nullptr) {
+      return fail(NVFP4_E_INVALID_ARGUMENT, "group %zu: null operand", g);
+    }
+    if (!aligned(a[g], 16) || !aligned(b[g], 16) || !aligned(sfa[g], 16) ||
+        !aligned(sfb[g], 16) || !aligned(d[g], 16)) {
+      return fail(NVFP4_E_MISALIGNED, "group %zu: operands must be 16-byte aligned", g);
+    }
+  }
+  const size_t table_bytes = plan->off_partials - plan->off_table;
+  plan->staging.assign(table_bytes, 0);
+  ProblemDesc* table = reinterpret_cast<ProblemDesc*>(plan->staging.data());
+  CUtensorMap* maps =
+      reinterpret_cast<CUtensorMap*>(plan->staging.data() + (plan->off_maps - plan->off_table));
+  for (size_t g = 0; g < groups; ++g) {
+    ProblemDesc& pd = plan->problems[g];
+    pd.sfa = static_cast<const uint8_t*>(sfa[g]);
+    pd.sfb = static_cast<const uint8_t*>(sfb[g]);
+    pd.sfb2 = nullptr;
+    pd.d = d[g];
+    table[g] = pd;
+    CUtensorMap tmp;
+    if (int rc = encode_operand_map(&tmp, a[g], pd.m, pd.k, 1, 128)) return rc;
+    std::memcpy(&maps[2 * g], &tmp, sizeof(tmp));
+    if (int rc = encode_operand_map(&tmp, b[g], pd.n, pd.k, 1, plan->tile_n)) return rc;
+    std::memcpy(&maps[2 * g + 1], &tmp, sizeof(tmp));
+  }
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
+  CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + plan->off_table,
+                           plan->staging.data(), table_bytes, cudaMemcpyHostToDevice,
+                           static_cast<cudaStream_t>(stream)));
+  KernelParams& kp = plan->params;
+  std::memset(&kp.dense, 0, sizeof(kp.dense));
+  kp.alpha = nullptr;
+  fill_common_params(plan, workspace);
+  plan->bound_ws = workspace;
+  plan->params_valid = true;
+  return 0;
+}
+
+int nvfp4_group_gemm_launch(nvfp4_plan* plan, void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kGrouped) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped GEMM plan");
+  }
+  if (!plan->params_valid || plan->bound_ws != workspace) {
+    return fail(NVFP4_E_NOT_BOUND, "call nvfp4_group_gemm_bind with this workspace first");
+  }
+  return launch_plan(plan, stream);
+}
+
+int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int* status) {
+  if (plan == nullptr || workspace == nullptr || status == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null argument");
+  }
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int value = 0;
+  CUDA_TRY(cudaMemcpyAsync(&value, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  *status = value;
+  if (value != 0) {
+    CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int), s));
+    return fail(NVFP4_E_DEVICE_TIMEOUT, "kernel abandoned a bounded wait (code %d)", value);
+  }
+  return 0;
+}
+
+int nvfp4_pack_scales(const void* scales, void* packed, int rows, int cols, int batches,
+                      void* stream) {
+  if (scales == nullptr || packed == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  if (rows < 1 || cols < 1 || batches < 1) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "unsupported scales rows=%d cols=%d batches=%d", rows,
+                cols, batches);
+  }
+  if (!aligned(packed, 16)) return fail(NVFP4_E_MISALIGNED, "packed scales must be 16-byte aligned");
+  const long long lines =
+      static_cast<long long>(batches) * ceil_div(rows, 128) * ceil_div(cols, 4) * 32;
+  const int threads = 256;
+  const long long blocks = std::min<long long>((lines + threads - 1) / threads, 148 * 16);
+  pack_scales_kernel<<<static_cast<unsigned int>(blocks), threads, 0,
+                       static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(scales), static_cast<uint8_t*>(packed), rows, cols, batches);
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int nvfp4_silu_product(const float* h1, const float* h2, void* out, int64_t size, void* stream) {
+  if (h1 == nullptr || h2 == nullptr || out == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  }
+  if (size < 1) return fail(NVFP4_E_UNSUPPORTED_SHAPE, "size must be positive");
+  if (!aligned(h1, 4) || !aligned(h2, 4) || !aligned(out, 2)) {
+    return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
+  }
+  const int vector_ok = aligned(h1, 16) && aligned(h2, 16) && aligned(out, 16) ? 1 : 0;
+  const int threads = 256;
+  const long long work = vector_ok ? (size + 7) / 8 : size;
+  const long long blocks = std::min<long long>((work + threads - 1) / threads, 148 * 16);
+  silu_product_kernel<<<static_cast<unsigned int>(blocks), threads, 0,
+                        static_cast<cudaStream_t>(stream)>>>(
+      h1, h2, static_cast<__half*>(out), static_cast<long long>(size), vector_ok);
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

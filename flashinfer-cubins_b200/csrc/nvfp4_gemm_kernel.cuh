@@ -1,0 +1,577 @@
+// The NVFP4 block-scaled GEMM kernel for sm_100a: one persistent, warp-specialised
+// kernel template that serves the dense/batched GEMM, the fused dual GEMM and the
+// ragged grouped GEMM.
+//
+//   D[m, n] = alpha * sum_k (A[m, k] * SFA[m, k/16]) * (B[n, k] * SFB[n, k/16])
+//
+// A and B are packed E2M1 (two values per byte, low nibble = even k, K contiguous),
+// SFA/SFB are UE4M3 bytes in the blocked 128x4 layout: scale (r, c) of a batch lives
+// at byte ((r/128) * kb + c/4) * 512 + (r%32) * 16 + ((r/32)%4) * 4 + c%4, kb =
+// ceil(k/64) (the layout of harness/workloads/quantization.py:90-102 in the reference).
+//
+// Roles (192 threads): warp 0 lane 0 issues TMA loads into a ring of shared-memory
+// stages; warp 1 lane 0 copies scale atoms into tensor memory (tcgen05.cp) and issues
+// tcgen05.mma kind::mxf4nvf4 (128 x BN x 64 per instruction, accumulators in tensor
+// memory); warps 2-5 read finished accumulators (tcgen05.ld), apply the epilogue and
+// store. A 512-byte scale atom is exactly the 32 x 16-byte source of one
+// tcgen05.cp.32x128b.warpx4, so scales go global -> shared -> tensor memory unchanged.
+//
+// Work is a list of (tile, k-tile range) segments that every role derives from the
+// same counters: in data-parallel mode CTA c takes tiles c, c + grid, ...; in stream-K
+// mode the (tile, k-tile) units of all tiles are cut into `grid` equal contiguous
+// ranges. A segment that does not cover its tile's whole K writes an FP32 partial to
+// the workspace; the last CTA to arrive at the tile (one atomic counter per tile, reset
+// by that CTA) adds the partials in segment order and finishes the tile, so results do
+// not depend on arrival order. No role waits on another CTA.
+//
+// Every mbarrier wait is bounded; a role that gives up records a code in the status
+// word, raises the shared abort flag and falls through to the common exit where tensor
+// memory is freed.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "sm100_ptx.cuh"
+
+namespace nvfp4 {
+
+// One GEMM problem: the dense (batched) problem, or one group of a grouped GEMM.
+struct alignas(16) ProblemDesc {
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  const uint8_t* sfb2;  // dual GEMM: scales of the second B
+  void* d;
+  int m, n, k, batches;
+  int tiles_m, tiles_n;  // output tiles per batch
+  int k_tiles;           // ceil(k / 256)
+  int sf_kb;             // scale atoms along K: ceil(k / 64)
+  int sf_mb, sf_nb;      // scale atom rows: ceil(m / 128), ceil(n / 128)
+  int pad0, pad1;
+  long long tile_begin;  // first global tile index of this problem
+  long long unit_begin;  // first global (tile, k-tile) unit of this problem
+};
+
+enum : int { kModeDataParallel = 0, kModeStreamK = 1 };
+
+enum : int {
+  kStatusOk = 0,
+  kStatusProducerTimeout = 1,
+  kStatusMmaInputTimeout = 2,
+  kStatusMmaAccumTimeout = 3,
+  kStatusEpilogueTimeout = 4,
+};
+
+struct alignas(64) KernelParams {
+  CUtensorMap map_a, map_b, map_b2;  // dense / dual: by value
+  ProblemDesc dense;
+  const ProblemDesc* problems;  // grouped: one per group, device memory
+  const CUtensorMap* maps;      // grouped: maps[2g] = A_g, maps[2g + 1] = B_g
+  const float* alpha;           // device scalar, may be null (= 1)
+  float* partials;              // stream-K: 2 * grid slots of slot_floats FP32 each
+  unsigned int* counters;       // stream-K: one per tile, zero between launches
+  int* status;                  // one word, 0 unless a wait was abandoned
+  long long total_tiles, total_units;
+  long long slot_floats;
+  int num_problems;
+  int mode;
+  int b_streams;  // B is read once: mark its loads evict-first in L2
+  int probe;      // timing experiments only; ignored unless built with NVFP4_PROBE
+};
+
+// Timing experiments (results become wrong): compiled out of the product build.
+#ifdef NVFP4_PROBE
+#define NVFP4_PROBE_FLAG(p, bit) (((p).probe >> (bit)) & 1)
+#else
+#define NVFP4_PROBE_FLAG(p, bit) 0
+#endif
+
+struct Segment {
+  int prob;
+  int m_tile, n_tile, batch;
+  int k0, k1;              // k-tile range [k0, k1)
+  long long tile_global;   // index into counters
+  long long tile_unit0;    // first global unit of this tile
+};
+
+template <bool GROUPED>
+struct WorkIter {
+  const KernelParams& p;
+  ProblemDesc pd;
+  long long cur, end, step;
+  int prob;
+
+  __device__ __forceinline__ explicit WorkIter(const KernelParams& params) : p(params) {
+    const long long cta = blockIdx.x, grid = gridDim.x;
+    if (p.mode == kModeDataParallel) {
+      cur = cta;
+      end = p.total_tiles;
+      step = grid;
+    } else {
+      cur = p.total_units * cta / grid;
+      end = p.total_units * (cta + 1) / grid;
+      step = 0;
+    }
+    prob = 0;
+    load(0);
+  }
+
+  __device__ __forceinline__ void load(int g) {
+    if constexpr (GROUPED) {
+      pd = p.problems[g];
+    } else {
+      pd = p.dense;
+    }
+  }
+
+  __device__ __forceinline__ long long tiles_of() const {
+    return static_cast<long long>(pd.tiles_m) * pd.tiles_n * pd.batches;
+  }
+
+  // Tile index inside the current problem -> (batch, m_tile, n_tile). Tiles are
+  // numbered down bands of eight tile rows so that tiles running at the same time
+  // share rows of A and B in L2.
+  __device__ __forceinline__ void decode(long long t, Segment& s) const {
+    const int per_batch = pd.tiles_m * pd.tiles_n;
+    s.batch = static_cast<int>(t / per_batch);
+    const int r = static_cast<int>(t % per_batch);
+    const int band_tiles = 8 * pd.tiles_n;
+    const int band = r / band_tiles;
+    const int in_band = r % band_tiles;
+    const int height = min(8, pd.tiles_m - band * 8);
+    s.m_tile = band * 8 + in_band % height;
+    s.n_tile = in_band / height;
+  }
+
+  __device__ __forceinline__ bool next(Segment& s) {
+    if (cur >= end) return false;
+    if (p.mode == kModeDataParallel) {
+      while (cur >= pd.tile_begin + tiles_of()) load(++prob);
+      const long long t = cur - pd.tile_begin;
+      decode(t, s);
+      s.k0 = 0;
+      s.k1 = pd.k_tiles;
+      s.tile_global = cur;
+      s.tile_unit0 = pd.unit_begin + t * pd.k_tiles;
+      cur += step;
+    } else {
+      while (cur >= pd.unit_begin + tiles_of() * pd.k_tiles) load(++prob);
+      const long long local = cur - pd.unit_begin;
+      const long long t = local / pd.k_tiles;
+      decode(t, s);
+      s.k0 = static_cast<int>(local % pd.k_tiles);
+      const long long len = min(static_cast<long long>(pd.k_tiles - s.k0), end - cur);
+      s.k1 = s.k0 + static_cast<int>(len);
+      s.tile_global = pd.tile_begin + t;
+      s.tile_unit0 = pd.unit_begin + t * pd.k_tiles;
+      cur += len;
+    }
+    s.prob = prob;
+    return true;
+  }
+};
+
+constexpr int const_min(int a, int b) { return a < b ? a : b; }
+constexpr int const_max(int a, int b) { return a > b ? a : b; }
+constexpr int const_pow2_at_least(int v) {
+  int r = 32;
+  while (r < v) r *= 2;
+  return r;
+}
+
+template <int BN_, bool DUAL_, typename OutT_, bool GROUPED_>
+struct GemmConfig {
+  static constexpr int BN = BN_;  // MMA N; for the dual GEMM both B tiles side by side
+  static constexpr bool DUAL = DUAL_;
+  static constexpr bool GROUPED = GROUPED_;
+  using OutT = OutT_;
+  static constexpr int BM = 128;
+  static constexpr int OUT_BN = DUAL ? BN / 2 : BN;  // output columns per tile
+  static constexpr int A_BYTES = BM * 128;           // 128 rows x 256 E2M1
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SFB_BLOCKS = (BN + 127) / 128;  // 128-row scale atoms per k-block
+  static constexpr int SFA_BYTES = 4 * 512;
+  static constexpr int SFB_BYTES = 4 * 512 * SFB_BLOCKS;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;  // 1 KiB alignment slack + static
+  static constexpr int STAGES = const_min(8, SMEM_BUDGET / STAGE_BYTES);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int ACC_BUFS = BN <= 128 ? 2 : 1;
+  static constexpr int SFB_COLS = const_max(4, BN / 32);  // columns per k-block
+  static constexpr int SFA_COL = ACC_BUFS * BN;
+  static constexpr int SFB_COL = SFA_COL + 16;
+  static constexpr int TMEM_COLS = const_pow2_at_least(SFB_COL + 4 * SFB_COLS);
+  static constexpr int THREADS = 192;
+  static_assert(BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
+  static_assert(!DUAL || BN == 256, "dual GEMM uses two 128-column B tiles");
+  static_assert(TMEM_COLS <= 512, "tensor memory exceeded");
+  static_assert(STAGES >= 2, "pipeline too shallow");
+};
+
+__device__ __forceinline__ void report_failure(const KernelParams& p, volatile int* abort_flag,
+                                               int code) {
+  *abort_flag = 1;
+  atomicCAS(p.status, 0, code);
+}
+
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+// Stores 32 consecutive output columns of one row, in 16-byte pieces, dropping the
+// pieces that start at or beyond column n (n is a multiple of the piece width).
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* row_ptr, int col0, int n,
+                                                const float (&v)[32]) {
+  if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (col0 + 8 * g < n) {
+        __half2 h0 = __floats2half2_rn(v[8 * g + 0], v[8 * g + 1]);
+        __half2 h1 = __floats2half2_rn(v[8 * g + 2], v[8 * g + 3]);
+        __half2 h2 = __floats2half2_rn(v[8 * g + 4], v[8 * g + 5]);
+        __half2 h3 = __floats2half2_rn(v[8 * g + 6], v[8 * g + 7]);
+        uint4 q;
+        q.x = *reinterpret_cast<uint32_t*>(&h0);
+        q.y = *reinterpret_cast<uint32_t*>(&h1);
+        q.z = *reinterpret_cast<uint32_t*>(&h2);
+        q.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(row_ptr + col0 + 8 * g) = q;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (col0 + 4 * g < n) {
+        float4 q = make_float4(v[4 * g + 0], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        *reinterpret_cast<float4*>(row_ptr + col0 + 4 * g) = q;
+      }
+    }
+  }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
+  constexpr int BN = Cfg::BN;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int ACC_BUFS = Cfg::ACC_BUFS;
+  using OutT = typename Cfg::OutT;
+
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ alignas(8) uint64_t bar_full[STAGES];
+  __shared__ alignas(8) uint64_t bar_empty[STAGES];
+  __shared__ alignas(8) uint64_t bar_acc_full[ACC_BUFS];
+  __shared__ alignas(8) uint64_t bar_acc_empty[ACC_BUFS];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int epi_last_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+#pragma unroll
+    for (int a = 0; a < ACC_BUFS; ++a) {
+      mbar_init(smem_u32(&bar_acc_full[a]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[a]), 128);
+    }
+    abort_flag = 0;
+    epi_last_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_slot), Cfg::TMEM_COLS);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      const uint64_t pol_a = l2_policy_evict_last();
+      const uint64_t pol_b = p.b_streams ? l2_policy_evict_first() : l2_policy_evict_last();
+      if constexpr (!Cfg::GROUPED) {
+        prefetch_tensormap(&p.map_a);
+        prefetch_tensormap(&p.map_b);
+        if constexpr (Cfg::DUAL) prefetch_tensormap(&p.map_b2);
+      }
+      WorkIter<Cfg::GROUPED> it(p);
+      Segment s;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      while (ok && it.next(s)) {
+        const ProblemDesc& pd = it.pd;
+        const CUtensorMap* map_a = Cfg::GROUPED ? &p.maps[2 * s.prob] : &p.map_a;
+        const CUtensorMap* map_b = Cfg::GROUPED ? &p.maps[2 * s.prob + 1] : &p.map_b;
+        const int m0 = s.m_tile * Cfg::BM;
+        const int n0 = s.n_tile * Cfg::OUT_BN;
+        const long long atom_row_a = static_cast<long long>(s.batch) * pd.sf_mb + s.m_tile;
+        const uint8_t* sfa_row = pd.sfa + atom_row_a * pd.sf_kb * 512;
+        // First 128-row scale atom row of this tile's B rows.
+        const int nb0 = n0 / 128;
+        for (int kt = s.k0; kt < s.k1; ++kt) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) {
+            report_failure(p, abort_ptr, kStatusProducerTimeout);
+            ok = false;
+            break;
+          }
+          const int atoms = min(4, pd.sf_kb - 4 * kt);
+          const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * 512u;
+          int sfb_valid = 0;
+#pragma unroll
+          for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+            const int nb = Cfg::DUAL ? nb0 : nb0 + i;
+            if (nb < pd.sf_nb) ++sfb_valid;
+          }
+          const uint32_t bar = smem_u32(&bar_full[stage]);
+          const bool probe_no_ab = NVFP4_PROBE_FLAG(p, 2);
+          mbar_expect_tx(bar, (probe_no_ab ? 0u : Cfg::A_BYTES + Cfg::B_BYTES) +
+                                  sf_bytes * (1u + sfb_valid));
+          const uint32_t a_dst = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+          const uint32_t sfa_dst = b_dst + Cfg::B_BYTES;
+          const uint32_t sfb_dst = sfa_dst + Cfg::SFA_BYTES;
+          if (probe_no_ab) {
+          } else if constexpr (!Cfg::DUAL) {
+            tma_load_3d(a_dst, map_a, bar, kt * 128, m0, s.batch, pol_a);
+            tma_load_3d(b_dst, map_b, bar, kt * 128, n0, s.batch, pol_b);
+          } else {
+            tma_load_3d(a_dst, map_a, bar, kt * 128, m0, s.batch, pol_a);
+            tma_load_3d(b_dst, map_b, bar, kt * 128, n0, s.batch, pol_b);
+            tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kt * 128, n0, s.batch, pol_b);
+          }
+          bulk_load(sfa_dst, sfa_row + static_cast<long long>(kt) * 2048, sf_bytes, bar, pol_a);
+#pragma unroll
+          for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+            const int nb = Cfg::DUAL ? nb0 : nb0 + i;
+            if (nb < pd.sf_nb) {
+              const uint8_t* base = (Cfg::DUAL && i == 1) ? pd.sfb2 : pd.sfb;
+              const long long atom_row_b = static_cast<long long>(s.batch) * pd.sf_nb + nb;
+              bulk_load(sfb_dst + i * 2048,
+                        base + (atom_row_b * pd.sf_kb + 4ll * kt) * 512, sf_bytes, bar, pol_b);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_ptr != 0) {
+        // Abandoned run: give copies still in flight time to land before the CTA exits.
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = nvf4_instr_desc(128, BN);
+      WorkIter<Cfg::GROUPED> it(p);
+      Segment s;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      while (ok && it.next(s)) {
+        const ProblemDesc& pd = it.pd;
+        if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) {
+          report_failure(p, abort_ptr, kStatusMmaAccumTimeout);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        // A 64-column tile uses half of a 128-row scale atom: columns 0-1 or 2-3.
+        const uint32_t sfb_half = (BN == 64) ? 2u * (s.n_tile & 1) : 0u;
+        for (int kt = s.k0; kt < s.k1; ++kt) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr)) {
+            report_failure(p, abort_ptr, kStatusMmaInputTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_src = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t b_src = a_src + Cfg::A_BYTES;
+          const uint32_t sfa_src = b_src + Cfg::B_BYTES;
+          const uint32_t sfb_src = sfa_src + Cfg::SFA_BYTES;
+          const int atoms = min(4, pd.sf_kb - 4 * kt);
+          for (int j = 0; j < (NVFP4_PROBE_FLAG(p, 0) ? 0 : atoms); ++j) {
+            tc_copy_32x128b_x4(tmem_base + Cfg::SFA_COL + 4 * j,
+                               smem_matrix_desc(sfa_src + 512 * j, 0, 128, 0));
+#pragma unroll
+            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+              tc_copy_32x128b_x4(tmem_base + Cfg::SFB_COL + j * Cfg::SFB_COLS + 4 * i,
+                                 smem_matrix_desc(sfb_src + i * 2048 + 512 * j, 0, 128, 0));
+            }
+          }
+          // 128-byte swizzled K-major tiles: eight-row groups 1024 bytes apart; one
+          // K = 64 step is 32 bytes further along the row.
+          const uint64_t desc_a = smem_matrix_desc(a_src, 16, 1024, 2);
+          const uint64_t desc_b = smem_matrix_desc(b_src, 16, 1024, 2);
+          for (int j = 0; j < (NVFP4_PROBE_FLAG(p, 1) ? 0 : (NVFP4_PROBE_FLAG(p, 3) ? 1 : atoms)); ++j) {
+            tc_mma_nvf4(d_tmem, desc_a + 2 * j, desc_b + 2 * j, idesc,
+                        tmem_base + Cfg::SFA_COL + 4 * j,
+                        tmem_base + Cfg::SFB_COL + j * Cfg::SFB_COLS + sfb_half,
+                        (kt > s.k0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&bar_empty[stage]));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&bar_acc_full[acc]));
+        if (++acc == ACC_BUFS) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may read
+    const int row = quarter * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
+    const long long grid = gridDim.x;
+    const long long cta = blockIdx.x;
+    WorkIter<Cfg::GROUPED> it(p);
+    Segment s;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    while (it.next(s)) {
+      const ProblemDesc& pd = it.pd;
+      if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr)) {
+        report_failure(p, abort_ptr, kStatusEpilogueTimeout);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      const int grow = s.m_tile * Cfg::BM + row;
+      const int n0 = s.n_tile * Cfg::OUT_BN;
+      OutT* out_row = reinterpret_cast<OutT*>(pd.d) +
+                      (static_cast<long long>(s.batch) * pd.m + grow) * pd.n;
+      const bool whole = (s.k0 == 0 && s.k1 == pd.k_tiles);
+
+      if (whole) {
+#pragma unroll 1
+        for (int c = 0; c < Cfg::OUT_BN / 32; ++c) {
+          uint32_t r1[32];
+          float v[32];
+          tmem_load_32(taddr + c * 32, r1);
+          if constexpr (Cfg::DUAL) {
+            uint32_t r2[32];
+            tmem_load_32(taddr + Cfg::OUT_BN + c * 32, r2);
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v[i] = silu_f32(__uint_as_float(r1[i]) * alpha) * (__uint_as_float(r2[i]) * alpha);
+            }
+          } else {
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * alpha;
+          }
+          if (c == Cfg::OUT_BN / 32 - 1) {
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+          }
+          if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+        }
+      } else {
+        // Partial sum of this segment -> workspace slot, column-major so that the
+        // 32 rows of a warp write 128 contiguous bytes.
+        const long long my_start = p.total_units * cta / grid;
+        const long long my_slot = 2 * cta + (my_start < s.tile_unit0 ? 1 : 0);
+        float* ws = p.partials + my_slot * p.slot_floats;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r1[32];
+          tmem_load_32(taddr + c * 32, r1);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            ws[(c * 32 + i) * 128 + row] = __uint_as_float(r1[i]);
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+        __threadfence();
+        named_barrier_sync(1, 128);
+        const long long unit_last = s.tile_unit0 + pd.k_tiles - 1;
+        const long long first_cta = ((s.tile_unit0 + 1) * grid - 1) / p.total_units;
+        const long long last_cta = ((unit_last + 1) * grid - 1) / p.total_units;
+        if (epi_tid == 0) {
+          const unsigned int parts = static_cast<unsigned int>(last_cta - first_cta + 1);
+          const unsigned int old = atomicAdd(&p.counters[s.tile_global], 1u);
+          const int last = (old == parts - 1u) ? 1 : 0;
+          if (last) p.counters[s.tile_global] = 0u;
+          epi_last_flag = last;
+        }
+        named_barrier_sync(1, 128);
+        if (epi_last_flag) {
+          __threadfence();
+#pragma unroll 1
+          for (int c = 0; c < Cfg::OUT_BN / 32; ++c) {
+            float s1[32];
+            float s2[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              s1[i] = 0.0f;
+              s2[i] = 0.0f;
+            }
+#pragma unroll 1
+            for (long long b = first_cta; b <= last_cta; ++b) {
+              const long long b_start = p.total_units * b / grid;
+              const long long slot = 2 * b + (b_start < s.tile_unit0 ? 1 : 0);
+              const float* src = p.partials + slot * p.slot_floats;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                s1[i] += __ldcg(src + (c * 32 + i) * 128 + row);
+                if constexpr (Cfg::DUAL) {
+                  s2[i] += __ldcg(src + (Cfg::OUT_BN + c * 32 + i) * 128 + row);
+                }
+              }
+            }
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if constexpr (Cfg::DUAL) {
+                v[i] = silu_f32(s1[i] * alpha) * (s2[i] * alpha);
+              } else {
+                v[i] = s1[i] * alpha;
+              }
+            }
+            if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+          }
+        }
+      }
+      if (++acc == ACC_BUFS) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace nvfp4

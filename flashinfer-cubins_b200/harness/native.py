@@ -1,0 +1,256 @@
+"""ctypes binding of the C-ABI library ``lib/libnvfp4_b200.so`` (``include/nvfp4_b200.h``).
+
+The library is the only native code of this package: hand-written sm_100a kernels
+behind plain C entry points. This module replaces the reference's libcuda binding
+(``harness/cuda_driver.py`` there): instead of loading a cubin and marshalling a
+CUTLASS ``Params`` struct, the workloads hand device pointers and shapes to the
+library. There is no fallback: if the library is missing, ``load()`` raises.
+
+Status codes map to exceptions the way the reference's host code behaves
+(``harness/workloads/nvfp4_gemm.py:226-231,440-443``): invalid operands raise
+``ValueError`` before anything is launched, an unsupported device or a CUDA error
+raises ``RuntimeError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+PACKAGE_ROOT = Path(__file__).resolve().parents[1]
+LIBRARY_PATH = PACKAGE_ROOT / "lib" / "libnvfp4_b200.so"
+
+E_INVALID_ARGUMENT = -1
+E_UNSUPPORTED_SHAPE = -2
+E_MISALIGNED = -3
+E_UNSUPPORTED_DEVICE = -4
+E_DEVICE_TIMEOUT = -5
+E_NOT_BOUND = -6
+
+OUT_F16 = 0
+OUT_F32 = 1
+
+SCHEDULE_NAMES = {1: "data_parallel", 2: "stream_k"}
+
+
+class NativeError(RuntimeError):
+    """A CUDA error or a device-side timeout reported by the library."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"nvfp4 library error {status}: {message}")
+        self.status = status
+
+
+class Config(ctypes.Structure):
+    _fields_ = [("tile_n", ctypes.c_int), ("schedule", ctypes.c_int), ("ctas", ctypes.c_int)]
+
+
+class PlanInfo(ctypes.Structure):
+    _fields_ = [
+        ("tile_m", ctypes.c_int),
+        ("tile_n", ctypes.c_int),
+        ("tile_k", ctypes.c_int),
+        ("stages", ctypes.c_int),
+        ("schedule", ctypes.c_int),
+        ("ctas", ctypes.c_int),
+        ("threads", ctypes.c_int),
+        ("smem_bytes", ctypes.c_int),
+        ("tiles", ctypes.c_int64),
+        ("units", ctypes.c_int64),
+        ("sm_count", ctypes.c_int),
+    ]
+
+
+_P = ctypes.c_void_p
+_PROTOTYPES = {
+    "nvfp4_version": (ctypes.c_int, []),
+    "nvfp4_last_error": (ctypes.c_char_p, []),
+    "nvfp4_device_supported": (ctypes.c_int, [ctypes.c_int]),
+    "nvfp4_gemm_plan_create": (
+        ctypes.c_int,
+        [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+         ctypes.c_int, ctypes.c_int, ctypes.POINTER(Config)],
+    ),
+    "nvfp4_dual_gemm_plan_create": (
+        ctypes.c_int,
+        [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+         ctypes.c_int, ctypes.POINTER(Config)],
+    ),
+    "nvfp4_group_gemm_plan_create": (
+        ctypes.c_int,
+        [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+         ctypes.POINTER(Config)],
+    ),
+    "nvfp4_plan_destroy": (None, [_P]),
+    "nvfp4_plan_workspace_bytes": (ctypes.c_size_t, [_P]),
+    "nvfp4_plan_init_workspace": (ctypes.c_int, [_P, _P, _P]),
+    "nvfp4_plan_info_get": (ctypes.c_int, [_P, ctypes.POINTER(PlanInfo)]),
+    "nvfp4_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "nvfp4_dual_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "nvfp4_group_gemm_bind": (
+        ctypes.c_int,
+        [_P, ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P),
+         ctypes.POINTER(_P), _P, _P],
+    ),
+    "nvfp4_group_gemm_launch": (ctypes.c_int, [_P, _P, _P]),
+    "nvfp4_plan_status": (ctypes.c_int, [_P, _P, _P, ctypes.POINTER(ctypes.c_int)]),
+    "nvfp4_pack_scales": (
+        ctypes.c_int, [_P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
+    ),
+    "nvfp4_silu_product": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P]),
+}
+
+_lock = threading.Lock()
+_library: ctypes.CDLL | None = None
+
+
+def exported_symbols() -> tuple[str, ...]:
+    """Names this binding expects the library to export."""
+    return tuple(_PROTOTYPES)
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library; raises ``FileNotFoundError`` if it has not been built
+    (``python __graft_entry__.py`` or ``harness.build.build()`` builds it)."""
+    global _library
+    with _lock:
+        if _library is None:
+            if not LIBRARY_PATH.is_file():
+                raise FileNotFoundError(
+                    f"{LIBRARY_PATH} is missing; build it with harness.build.build()"
+                )
+            library = ctypes.CDLL(str(LIBRARY_PATH))
+            for name, (restype, argtypes) in _PROTOTYPES.items():
+                function = getattr(library, name)
+                function.restype = restype
+                function.argtypes = argtypes
+            _library = library
+        return _library
+
+
+def unload() -> None:
+    """Forget the loaded library; the next ``load()`` binds it again."""
+    global _library
+    with _lock:
+        _library = None
+
+
+def check(status: int) -> None:
+    """Raise for a non-zero library status."""
+    if status == 0:
+        return
+    message = (load().nvfp4_last_error() or b"").decode(errors="replace")
+    if status in (E_UNSUPPORTED_DEVICE,):
+        raise RuntimeError(message)
+    if status in (E_DEVICE_TIMEOUT,):
+        raise NativeError(status, message)
+    if status < 0:
+        raise ValueError(message)
+    raise NativeError(status, message)
+
+
+def device_supported(index: int) -> bool:
+    status = load().nvfp4_device_supported(index)
+    if status in (0, 1):
+        return bool(status)
+    check(status)
+    return False
+
+
+class Plan:
+    """Owner of one ``nvfp4_plan`` handle."""
+
+    def __init__(self, handle: int):
+        self._handle = ctypes.c_void_p(handle)
+
+    @staticmethod
+    def _config(tile_n: int = 0, schedule: int = 0, ctas: int = 0):
+        if not (tile_n or schedule or ctas):
+            return None
+        return ctypes.byref(Config(tile_n, schedule, ctas))
+
+    @classmethod
+    def dense(cls, device: int, out_kind: int, m: int, n: int, k: int, l: int, **config):  # noqa: E741
+        handle = _P()
+        check(load().nvfp4_gemm_plan_create(
+            ctypes.byref(handle), device, out_kind, m, n, k, l, cls._config(**config)))
+        return cls(handle.value)
+
+    @classmethod
+    def dual(cls, device: int, m: int, n: int, k: int, l: int, **config):  # noqa: E741
+        handle = _P()
+        check(load().nvfp4_dual_gemm_plan_create(
+            ctypes.byref(handle), device, m, n, k, l, cls._config(**config)))
+        return cls(handle.value)
+
+    @classmethod
+    def grouped(cls, device: int, problems, **config):
+        flat = [int(v) for problem in problems for v in problem]
+        array = (ctypes.c_int * len(flat))(*flat)
+        handle = _P()
+        check(load().nvfp4_group_gemm_plan_create(
+            ctypes.byref(handle), device, len(flat) // 3, array, cls._config(**config)))
+        return cls(handle.value)
+
+    @property
+    def handle(self) -> ctypes.c_void_p:
+        if self._handle is None:
+            raise RuntimeError("plan is destroyed")
+        return self._handle
+
+    def workspace_bytes(self) -> int:
+        return int(load().nvfp4_plan_workspace_bytes(self.handle))
+
+    def init_workspace(self, workspace: int, stream: int) -> None:
+        check(load().nvfp4_plan_init_workspace(self.handle, workspace, stream))
+
+    def info(self) -> dict:
+        info = PlanInfo()
+        check(load().nvfp4_plan_info_get(self.handle, ctypes.byref(info)))
+        result = {name: getattr(info, name) for name, _ in PlanInfo._fields_}
+        result["schedule"] = SCHEDULE_NAMES.get(result["schedule"], str(result["schedule"]))
+        return result
+
+    def launch_dense(self, a, b, sfa, sfb, alpha, d, workspace, stream) -> None:
+        check(load().nvfp4_gemm_launch(self.handle, a, b, sfa, sfb, alpha, d, workspace, stream))
+
+    def launch_dual(self, a, b1, b2, sfa, sfb1, sfb2, alpha, d, workspace, stream) -> None:
+        check(load().nvfp4_dual_gemm_launch(
+            self.handle, a, b1, b2, sfa, sfb1, sfb2, alpha, d, workspace, stream))
+
+    def bind_groups(self, a, b, sfa, sfb, d, workspace, stream) -> None:
+        def array(values):
+            return (_P * len(values))(*values)
+
+        check(load().nvfp4_group_gemm_bind(
+            self.handle, array(a), array(b), array(sfa), array(sfb), array(d), workspace, stream))
+
+    def launch_groups(self, workspace, stream) -> None:
+        check(load().nvfp4_group_gemm_launch(self.handle, workspace, stream))
+
+    def status(self, workspace, stream) -> int:
+        """Synchronise ``stream`` and return the device status word (0 = ok);
+        raises ``NativeError`` if a kernel abandoned a bounded wait."""
+        value = ctypes.c_int(0)
+        check(load().nvfp4_plan_status(self.handle, workspace, stream, ctypes.byref(value)))
+        return value.value
+
+    def destroy(self) -> None:
+        if self._handle is not None:
+            load().nvfp4_plan_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def pack_scales(scales: int, packed: int, rows: int, cols: int, batches: int, stream: int) -> None:
+    check(load().nvfp4_pack_scales(scales, packed, rows, cols, batches, stream))
+
+
+def silu_product(h1: int, h2: int, out: int, size: int, stream: int) -> None:
+    check(load().nvfp4_silu_product(h1, h2, out, size, stream))

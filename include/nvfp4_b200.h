@@ -1,0 +1,158 @@
+/*
+ * C ABI of the B200 (sm_100a) NVFP4 block-scaled GEMM family: dense/batched GEMM,
+ * fused dual GEMM with silu gate, ragged grouped GEMM, and the two glue kernels of
+ * the dual-GEMM pipeline. Each entry point names the interface of
+ * Aalanli/flashinfer-cubins it stands in for (file:line within that project).
+ *
+ * Conventions
+ *   - Every function returns an int status and never throws, aborts or traps:
+ *       0   success
+ *      <0   invalid argument (NVFP4_E_*); nothing was launched
+ *      >0   a CUDA runtime/driver error code (cudaError_t / CUresult)
+ *     nvfp4_last_error() returns text for the calling thread's last failure.
+ *   - All data pointers are device pointers on the plan's device unless the
+ *     parameter is documented as host memory. Launches are asynchronous on the
+ *     stream passed in (a cudaStream_t passed as void*).
+ *   - The library allocates no device memory: a plan reports the workspace it needs
+ *     (nvfp4_plan_workspace_bytes) and the caller passes that buffer to every
+ *     launch. The workspace must be initialised once with nvfp4_plan_init_workspace
+ *     (it zeroes the status word and the per-tile arrival counters) and must not be
+ *     shared by launches that can overlap on the GPU.
+ *   - Operand layout (harness/workloads/quantization.py:1-37): packed E2M1 bytes,
+ *     low nibble = even K index, K contiguous, storage [batch][rows][k/2]; UE4M3
+ *     scales, one per 16 K elements, in the blocked layout
+ *     [batch][ceil(rows/128)][ceil(k/64)][32][4][4] (quantization.py:90-102);
+ *     output [batch][m][n] row-major.
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVFP4_E_INVALID_ARGUMENT (-1) /* null pointer, bad enum, bad handle */
+#define NVFP4_E_UNSUPPORTED_SHAPE (-2) /* m,n,k,l < 1, k % 32, n alignment, int32 range */
+#define NVFP4_E_MISALIGNED (-3)        /* operand not 16-byte aligned (alpha: 4) */
+#define NVFP4_E_UNSUPPORTED_DEVICE (-4) /* not compute capability 10.0 */
+#define NVFP4_E_DEVICE_TIMEOUT (-5)    /* a kernel abandoned a bounded wait (status word) */
+#define NVFP4_E_NOT_BOUND (-6)         /* grouped launch before nvfp4_group_gemm_bind */
+
+/* Output/element kinds of a plan. */
+#define NVFP4_OUT_F16 0 /* nvfp4_gemm: FP16 D (harness/workloads/nvfp4_gemm.py:511-530) */
+#define NVFP4_OUT_F32 1 /* nvfp4_dual_gemm_gemm: FP32 D (nvfp4_dual_gemm.py:172-188) */
+
+/* Optional tuning overrides; zero/negative fields mean "choose automatically". */
+typedef struct nvfp4_config {
+  int tile_n;   /* 64, 128 or 256 */
+  int schedule; /* 1 = data parallel (whole tiles), 2 = stream-K (split along K) */
+  int ctas;     /* persistent grid size, at most the SM count */
+} nvfp4_config;
+
+/* What a plan decided; filled by nvfp4_plan_info. */
+typedef struct nvfp4_plan_info {
+  int tile_m, tile_n, tile_k;
+  int stages;
+  int schedule; /* 1 data parallel, 2 stream-K */
+  int ctas;
+  int threads;
+  int smem_bytes;
+  int64_t tiles;
+  int64_t units; /* (tile, 256-wide k-tile) units */
+  int sm_count;
+} nvfp4_plan_info;
+
+typedef struct nvfp4_plan nvfp4_plan;
+
+/* Library version, major * 1000 + minor. */
+int nvfp4_version(void);
+
+/* Text of the calling thread's last error ("" if none). */
+const char* nvfp4_last_error(void);
+
+/* 1 if CUDA device `device` can run these kernels (compute capability 10.0), 0 if
+ * not, <0 / >0 on error. Replaces Workload.is_supported / _check_supported
+ * (harness/workload.py:410-416, harness/workloads/nvfp4_gemm.py:440-443): the check
+ * runs on the host, nothing is launched on an unsupported device. */
+int nvfp4_device_supported(int device);
+
+/* Dense/batched GEMM plan: D[l] = alpha * (A[l]*SFA[l]) (B[l]*SFB[l])^T.
+ * Replaces CutlassFp4Gemm.build_params' shape validation, scheduler and grid choice
+ * (harness/workloads/nvfp4_gemm.py:198-387). Requires m,n,k,l >= 1, k % 32 == 0,
+ * (n * sizeof(out)) % 16 == 0. */
+int nvfp4_gemm_plan_create(nvfp4_plan** plan, int device, int out_kind, int m, int n, int k,
+                           int l, const nvfp4_config* config);
+
+/* Fused dual GEMM plan: D = half(silu(alpha*A*B1^T) * (alpha*A*B2^T)). The reference
+ * runs this as two GEMM launches plus silu_product
+ * (harness/workloads/nvfp4_dual_gemm.py:1-30, resources/nvfp4_dual_gemm/task.yml:12-26);
+ * here it is one launch. Output FP16, n % 8 == 0. */
+int nvfp4_dual_gemm_plan_create(nvfp4_plan** plan, int device, int m, int n, int k, int l,
+                                const nvfp4_config* config);
+
+/* Grouped GEMM plan for `groups` independent problems; `mnk` is host memory,
+ * 3 * groups ints (m_g, n_g, k_g). Replaces NVFP4GroupGEMM.build_params /
+ * array_bytes (harness/workloads/nvfp4_group_gemm.py:250-501). Output FP16. */
+int nvfp4_group_gemm_plan_create(nvfp4_plan** plan, int device, int groups, const int* mnk,
+                                 const nvfp4_config* config);
+
+void nvfp4_plan_destroy(nvfp4_plan* plan);
+
+/* Bytes of caller-provided device workspace the plan's launches need (>= 256). */
+size_t nvfp4_plan_workspace_bytes(const nvfp4_plan* plan);
+
+/* Zeroes the workspace's status word and arrival counters; call once per workspace
+ * before the first launch (stream-ordered). */
+int nvfp4_plan_init_workspace(const nvfp4_plan* plan, void* workspace, void* stream);
+
+int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info);
+
+/* One dense GEMM launch. Replaces CutlassFp4Gemm.launch_config + _launch
+ * (harness/workloads/nvfp4_gemm.py:395-435). `alpha` is a device FP32 scalar read by
+ * the kernel (nvfp4_gemm.py:35-39); `d` is FP16 or FP32 per the plan. Tensor maps are
+ * re-encoded only when a pointer differs from the previous launch of this plan. */
+int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                      const void* sfb, const float* alpha, void* d, void* workspace,
+                      void* stream);
+
+/* One fused dual-GEMM launch (see nvfp4_dual_gemm_plan_create). */
+int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+                           const void* sfa, const void* sfb1, const void* sfb2,
+                           const float* alpha, void* d, void* workspace, void* stream);
+
+/* Records the groups' device pointers (host arrays of `groups` pointers each),
+ * encodes the per-group tensor maps and copies the group table into the workspace
+ * (one stream-ordered host-to-device copy). Replaces NVFP4GroupGEMM.launch_config
+ * (harness/workloads/nvfp4_group_gemm.py:514-591). */
+int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* const* b,
+                          const void* const* sfa, const void* const* sfb, void* const* d,
+                          void* workspace, void* stream);
+
+/* One launch covering every group. Replaces NVFP4GroupGEMM._launch
+ * (harness/workloads/nvfp4_group_gemm.py:593-600). */
+int nvfp4_group_gemm_launch(nvfp4_plan* plan, void* workspace, void* stream);
+
+/* Synchronises `stream`, reads the workspace's status word into *status and clears
+ * it. Returns NVFP4_E_DEVICE_TIMEOUT if it was non-zero. */
+int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int* status);
+
+/* Logical E4M3 scales [batches][rows][cols] -> blocked layout, zero padded, flat
+ * [batches][round_up(rows,128) * round_up(cols,4)]. Replaces the pack_scales kernel
+ * (impls/nvfp4_dual_gemm/kernels/pack_scales.cu:9-19,
+ * harness/workloads/nvfp4_dual_gemm.py:269-296). */
+int nvfp4_pack_scales(const void* scales, void* packed, int rows, int cols, int batches,
+                      void* stream);
+
+/* out[i] = half(silu(h1[i]) * h2[i]) over `size` FP32 elements. Replaces the
+ * silu_product kernel (impls/nvfp4_dual_gemm/kernels/silu_product.cu:7-9,
+ * harness/workloads/nvfp4_dual_gemm.py:352-367). */
+int nvfp4_silu_product(const float* h1, const float* h2, void* out, int64_t size, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NVFP4_B200_H_ */
