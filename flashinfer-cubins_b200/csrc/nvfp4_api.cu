@@ -316,8 +316,7 @@ int prepare_kernel(nvfp4_plan* plan) {
   return 0;
 }
 
-void fill_common_params(nvfp4_plan* plan, void* workspace) {
-  KernelParams& kp = plan->params;
+void fill_common_params(const nvfp4_plan* plan, KernelParams& kp, void* workspace) {
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   kp.status = reinterpret_cast<int*>(ws);
   kp.counters = reinterpret_cast<unsigned int*>(ws + plan->off_counters);
@@ -337,10 +336,10 @@ void fill_common_params(nvfp4_plan* plan, void* workspace) {
   kp.probe = env_int("NVFP4_PROBE_FLAGS", 0);
 }
 
-int launch_plan(nvfp4_plan* plan, void* stream) {
+int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream) {
   DeviceGuard guard;
   CUDA_TRY(guard.enter(plan->device));
-  void* args[1] = {&plan->params};
+  void* args[1] = {&kp};
   CUDA_TRY(cudaLaunchKernel(reinterpret_cast<const void*>(plan->kernel.fn), dim3(plan->ctas),
                             dim3(plan->kernel.threads), args, plan->kernel.smem_bytes,
                             static_cast<cudaStream_t>(stream)));
@@ -370,7 +369,11 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
   if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "unknown output kind %d", out_kind);
   }
-  if (int rc = check_dense_shape(m, n, k, l, out_kind == NVFP4_OUT_F16 ? 2 : 4)) return rc;
+  // The fused dual GEMM also takes n % 8 == 4 (8-byte aligned FP16 rows), because its
+  // FP32-output stage does.
+  if (int rc = check_dense_shape(m, n, k, l, (out_kind == NVFP4_OUT_F16 && kind != kDual) ? 2 : 4)) {
+    return rc;
+  }
   int sms = 0;
   if (int rc = check_device(device, &sms)) return rc;
   nvfp4_plan* plan = new (std::nothrow) nvfp4_plan();
@@ -521,12 +524,12 @@ int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void
     pd.d = d;
     kp.dense = pd;
     kp.alpha = alpha;
-    fill_common_params(plan, workspace);
+    fill_common_params(plan, kp, workspace);
     std::memcpy(plan->bound, now, sizeof(now));
     plan->bound_ws = workspace;
     plan->params_valid = true;
   }
-  return launch_plan(plan, stream);
+  return launch_plan(plan, plan->params, stream);
 }
 
 int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
@@ -540,7 +543,7 @@ int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, cons
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
   }
   if (!aligned(a, 16) || !aligned(b1, 16) || !aligned(b2, 16) || !aligned(sfa, 16) ||
-      !aligned(sfb1, 16) || !aligned(sfb2, 16) || !aligned(d, 16) || !aligned(alpha, 4) ||
+      !aligned(sfb1, 16) || !aligned(sfb2, 16) || !aligned(d, 8) || !aligned(alpha, 4) ||
       !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
@@ -558,12 +561,12 @@ int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, cons
     pd.d = d;
     kp.dense = pd;
     kp.alpha = alpha;
-    fill_common_params(plan, workspace);
+    fill_common_params(plan, kp, workspace);
     std::memcpy(plan->bound, now, sizeof(now));
     plan->bound_ws = workspace;
     plan->params_valid = true;
   }
-  return launch_plan(plan, stream);
+  return launch_plan(plan, plan->params, stream);
 }
 
 int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* const* b,
@@ -611,11 +614,6 @@ int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* co
   CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + plan->off_table,
                            plan->staging.data(), table_bytes, cudaMemcpyHostToDevice,
                            static_cast<cudaStream_t>(stream)));
-  KernelParams& kp = plan->params;
-  std::memset(&kp.dense, 0, sizeof(kp.dense));
-  kp.alpha = nullptr;
-  fill_common_params(plan, workspace);
-  plan->bound_ws = workspace;
   plan->params_valid = true;
   return 0;
 }
@@ -624,10 +622,18 @@ int nvfp4_group_gemm_launch(nvfp4_plan* plan, void* workspace, void* stream) {
   if (plan == nullptr || plan->kind != kGrouped) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped GEMM plan");
   }
-  if (!plan->params_valid || plan->bound_ws != workspace) {
-    return fail(NVFP4_E_NOT_BOUND, "call nvfp4_group_gemm_bind with this workspace first");
+  if (workspace == nullptr || !aligned(workspace, 256)) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "workspace is null or not 256-byte aligned");
   }
-  return launch_plan(plan, stream);
+  if (!plan->params_valid) {
+    return fail(NVFP4_E_NOT_BOUND, "call nvfp4_group_gemm_bind on a workspace first");
+  }
+  // The group table and tensor maps live in the workspace, so one plan can serve
+  // several bound workspaces (different operand sets of the same shapes).
+  KernelParams kp{};
+  kp.alpha = nullptr;
+  fill_common_params(plan, kp, workspace);
+  return launch_plan(plan, kp, stream);
 }
 
 int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int* status) {

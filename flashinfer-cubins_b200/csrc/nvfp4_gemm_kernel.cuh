@@ -218,25 +218,40 @@ __device__ __forceinline__ void report_failure(const KernelParams& p, volatile i
 
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
 
-// Stores 32 consecutive output columns of one row, in 16-byte pieces, dropping the
+// Stores 32 consecutive output columns of one row in 16-byte pieces (8-byte pieces of
+// FP16 when n is only a multiple of 4, whose rows are 8-byte aligned), dropping the
 // pieces that start at or beyond column n (n is a multiple of the piece width).
 template <typename OutT>
 __device__ __forceinline__ void store_row_chunk(OutT* row_ptr, int col0, int n,
                                                 const float (&v)[32]) {
   if constexpr (sizeof(OutT) == 2) {
+    if ((n & 7) == 0) {
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      if (col0 + 8 * g < n) {
-        __half2 h0 = __floats2half2_rn(v[8 * g + 0], v[8 * g + 1]);
-        __half2 h1 = __floats2half2_rn(v[8 * g + 2], v[8 * g + 3]);
-        __half2 h2 = __floats2half2_rn(v[8 * g + 4], v[8 * g + 5]);
-        __half2 h3 = __floats2half2_rn(v[8 * g + 6], v[8 * g + 7]);
-        uint4 q;
-        q.x = *reinterpret_cast<uint32_t*>(&h0);
-        q.y = *reinterpret_cast<uint32_t*>(&h1);
-        q.z = *reinterpret_cast<uint32_t*>(&h2);
-        q.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(row_ptr + col0 + 8 * g) = q;
+      for (int g = 0; g < 4; ++g) {
+        if (col0 + 8 * g < n) {
+          __half2 h0 = __floats2half2_rn(v[8 * g + 0], v[8 * g + 1]);
+          __half2 h1 = __floats2half2_rn(v[8 * g + 2], v[8 * g + 3]);
+          __half2 h2 = __floats2half2_rn(v[8 * g + 4], v[8 * g + 5]);
+          __half2 h3 = __floats2half2_rn(v[8 * g + 6], v[8 * g + 7]);
+          uint4 q;
+          q.x = *reinterpret_cast<uint32_t*>(&h0);
+          q.y = *reinterpret_cast<uint32_t*>(&h1);
+          q.z = *reinterpret_cast<uint32_t*>(&h2);
+          q.w = *reinterpret_cast<uint32_t*>(&h3);
+          *reinterpret_cast<uint4*>(row_ptr + col0 + 8 * g) = q;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        if (col0 + 4 * g < n) {
+          __half2 h0 = __floats2half2_rn(v[4 * g + 0], v[4 * g + 1]);
+          __half2 h1 = __floats2half2_rn(v[4 * g + 2], v[4 * g + 3]);
+          uint2 q;
+          q.x = *reinterpret_cast<uint32_t*>(&h0);
+          q.y = *reinterpret_cast<uint32_t*>(&h1);
+          *reinterpret_cast<uint2*>(row_ptr + col0 + 4 * g) = q;
+        }
       }
     }
   } else {
@@ -309,6 +324,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       Segment s;
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t stage_smem = smem_base;
+      const uint32_t full0 = smem_u32(&bar_full[0]);
+      const uint32_t empty0 = smem_u32(&bar_empty[0]);
       bool ok = true;
       while (ok && it.next(s)) {
         const ProblemDesc& pd = it.pd;
@@ -316,55 +334,61 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         const CUtensorMap* map_b = Cfg::GROUPED ? &p.maps[2 * s.prob + 1] : &p.map_b;
         const int m0 = s.m_tile * Cfg::BM;
         const int n0 = s.n_tile * Cfg::OUT_BN;
+        // Scale atoms of this tile's rows: one 512-byte atom per 64 K elements, four per
+        // k-tile, contiguous along K.
         const long long atom_row_a = static_cast<long long>(s.batch) * pd.sf_mb + s.m_tile;
-        const uint8_t* sfa_row = pd.sfa + atom_row_a * pd.sf_kb * 512;
-        // First 128-row scale atom row of this tile's B rows.
-        const int nb0 = n0 / 128;
+        const uint8_t* sfa_src = pd.sfa + (atom_row_a * pd.sf_kb + 4ll * s.k0) * 512;
+        const int nb0 = n0 / 128;  // first 128-row scale atom row of the tile's B rows
+        const uint8_t* sfb_src[Cfg::SFB_BLOCKS];
+        int sfb_valid = 0;
+#pragma unroll
+        for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+          const int nb = Cfg::DUAL ? nb0 : nb0 + i;
+          const uint8_t* base = (Cfg::DUAL && i == 1) ? pd.sfb2 : pd.sfb;
+          const long long atom_row_b = static_cast<long long>(s.batch) * pd.sf_nb + nb;
+          sfb_src[i] = nb < pd.sf_nb ? base + (atom_row_b * pd.sf_kb + 4ll * s.k0) * 512 : nullptr;
+          if (nb < pd.sf_nb) ++sfb_valid;
+        }
+        const bool probe_no_ab = NVFP4_PROBE_FLAG(p, 2);
+        const uint32_t ab_bytes = probe_no_ab ? 0u : Cfg::A_BYTES + Cfg::B_BYTES;
+        int atoms_left = pd.sf_kb - 4 * s.k0;
+        int kbyte = s.k0 * 128;
         for (int kt = s.k0; kt < s.k1; ++kt) {
-          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr)) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusProducerTimeout);
             ok = false;
             break;
           }
-          const int atoms = min(4, pd.sf_kb - 4 * kt);
-          const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * 512u;
-          int sfb_valid = 0;
-#pragma unroll
-          for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-            const int nb = Cfg::DUAL ? nb0 : nb0 + i;
-            if (nb < pd.sf_nb) ++sfb_valid;
-          }
-          const uint32_t bar = smem_u32(&bar_full[stage]);
-          const bool probe_no_ab = NVFP4_PROBE_FLAG(p, 2);
-          mbar_expect_tx(bar, (probe_no_ab ? 0u : Cfg::A_BYTES + Cfg::B_BYTES) +
-                                  sf_bytes * (1u + sfb_valid));
-          const uint32_t a_dst = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sf_bytes = atoms_left >= 4 ? 2048u : static_cast<uint32_t>(atoms_left) * 512u;
+          const uint32_t bar = full0 + 8 * stage;
+          mbar_expect_tx(bar, ab_bytes + (NVFP4_PROBE_FLAG(p, 5) ? 0u : sf_bytes * (1u + sfb_valid)));
+          const uint32_t a_dst = stage_smem;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           const uint32_t sfa_dst = b_dst + Cfg::B_BYTES;
           const uint32_t sfb_dst = sfa_dst + Cfg::SFA_BYTES;
-          if (probe_no_ab) {
-          } else if constexpr (!Cfg::DUAL) {
-            tma_load_3d(a_dst, map_a, bar, kt * 128, m0, s.batch, pol_a);
-            tma_load_3d(b_dst, map_b, bar, kt * 128, n0, s.batch, pol_b);
-          } else {
-            tma_load_3d(a_dst, map_a, bar, kt * 128, m0, s.batch, pol_a);
-            tma_load_3d(b_dst, map_b, bar, kt * 128, n0, s.batch, pol_b);
-            tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kt * 128, n0, s.batch, pol_b);
-          }
-          bulk_load(sfa_dst, sfa_row + static_cast<long long>(kt) * 2048, sf_bytes, bar, pol_a);
-#pragma unroll
-          for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-            const int nb = Cfg::DUAL ? nb0 : nb0 + i;
-            if (nb < pd.sf_nb) {
-              const uint8_t* base = (Cfg::DUAL && i == 1) ? pd.sfb2 : pd.sfb;
-              const long long atom_row_b = static_cast<long long>(s.batch) * pd.sf_nb + nb;
-              bulk_load(sfb_dst + i * 2048,
-                        base + (atom_row_b * pd.sf_kb + 4ll * kt) * 512, sf_bytes, bar, pol_b);
+          if (!probe_no_ab) {
+            tma_load_3d(a_dst, map_a, bar, kbyte, m0, s.batch, pol_a);
+            tma_load_3d(b_dst, map_b, bar, kbyte, n0, s.batch, pol_b);
+            if constexpr (Cfg::DUAL) {
+              tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kbyte, n0, s.batch, pol_b);
             }
           }
+          if (!NVFP4_PROBE_FLAG(p, 5)) bulk_load(sfa_dst, sfa_src, sf_bytes, bar, pol_a);
+#pragma unroll
+          for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+            if (sfb_src[i] != nullptr && !NVFP4_PROBE_FLAG(p, 5)) {
+              bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, bar, pol_b);
+              sfb_src[i] += 2048;
+            }
+          }
+          sfa_src += 2048;
+          atoms_left -= 4;
+          kbyte += 128;
+          stage_smem += Cfg::STAGE_BYTES;
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
+            stage_smem = smem_base;
           }
         }
       }
@@ -377,10 +401,26 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = nvf4_instr_desc(128, BN);
+      // Descriptor words that never change: the high halves (stride, version, swizzle)
+      // and, per stage, the low halves (address >> 4, leading offset). A stage is
+      // STAGE_BYTES / 16 further in the address field; a K = 64 step 2 further; a scale
+      // atom 32 further.
+      constexpr uint32_t kHiOperand = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kHiScale = (128u >> 4) | (1u << 14);
+      constexpr uint32_t kStage16 = Cfg::STAGE_BYTES >> 4;
+      const uint32_t lo_a0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
+      const uint32_t lo_b0 = lo_a0 + (Cfg::A_BYTES >> 4);
+      const uint32_t lo_sfa0 = (smem_base + Cfg::A_BYTES + Cfg::B_BYTES) >> 4;
+      const uint32_t lo_sfb0 = lo_sfa0 + (Cfg::SFA_BYTES >> 4);
+      const uint32_t t_sfa = tmem_base + Cfg::SFA_COL;
+      const uint32_t t_sfb = tmem_base + Cfg::SFB_COL;
+      const uint32_t full0 = smem_u32(&bar_full[0]);
+      const uint32_t empty0 = smem_u32(&bar_empty[0]);
       WorkIter<Cfg::GROUPED> it(p);
       Segment s;
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t stage16 = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
@@ -393,42 +433,64 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         // A 64-column tile uses half of a 128-row scale atom: columns 0-1 or 2-3.
-        const uint32_t sfb_half = (BN == 64) ? 2u * (s.n_tile & 1) : 0u;
+        const uint32_t t_sfb_mma = t_sfb + ((BN == 64) ? 2u * (s.n_tile & 1) : 0u);
+        int atoms_left = pd.sf_kb - 4 * s.k0;
+        uint32_t accumulate = 0;
         for (int kt = s.k0; kt < s.k1; ++kt) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr)) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusMmaInputTimeout);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_src = smem_base + stage * Cfg::STAGE_BYTES;
-          const uint32_t b_src = a_src + Cfg::A_BYTES;
-          const uint32_t sfa_src = b_src + Cfg::B_BYTES;
-          const uint32_t sfb_src = sfa_src + Cfg::SFA_BYTES;
-          const int atoms = min(4, pd.sf_kb - 4 * kt);
-          for (int j = 0; j < (NVFP4_PROBE_FLAG(p, 0) ? 0 : atoms); ++j) {
-            tc_copy_32x128b_x4(tmem_base + Cfg::SFA_COL + 4 * j,
-                               smem_matrix_desc(sfa_src + 512 * j, 0, 128, 0));
+          const uint32_t lo_a = lo_a0 + stage16;
+          const uint32_t lo_b = lo_b0 + stage16;
+          const uint32_t lo_sfa = lo_sfa0 + stage16;
+          const uint32_t lo_sfb = lo_sfb0 + stage16;
+          if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 0) && !NVFP4_PROBE_FLAG(p, 1) &&
+              !NVFP4_PROBE_FLAG(p, 3)) {
 #pragma unroll
-            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-              tc_copy_32x128b_x4(tmem_base + Cfg::SFB_COL + j * Cfg::SFB_COLS + 4 * i,
-                                 smem_matrix_desc(sfb_src + i * 2048 + 512 * j, 0, 128, 0));
+            for (int j = 0; j < 4; ++j) {
+              tc_copy_32x128b_x4(t_sfa + 4 * j, pack_desc(lo_sfa + 32 * j, kHiScale));
+#pragma unroll
+              for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+                tc_copy_32x128b_x4(t_sfb + j * Cfg::SFB_COLS + 4 * i,
+                                   pack_desc(lo_sfb + 128 * i + 32 * j, kHiScale));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
+                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sfa + 4 * j,
+                          t_sfb_mma + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
+            }
+          } else {
+            // K tail (fewer than four 64-wide blocks left) and timing experiments.
+            const int atoms = min(4, atoms_left);
+            for (int j = 0; j < (NVFP4_PROBE_FLAG(p, 0) ? 0 : atoms); ++j) {
+              tc_copy_32x128b_x4(t_sfa + 4 * j, pack_desc(lo_sfa + 32 * j, kHiScale));
+              if (NVFP4_PROBE_FLAG(p, 6)) break;
+#pragma unroll
+              for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+                tc_copy_32x128b_x4(t_sfb + j * Cfg::SFB_COLS + 4 * i,
+                                   pack_desc(lo_sfb + 128 * i + 32 * j, kHiScale));
+              }
+            }
+            const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : (NVFP4_PROBE_FLAG(p, 3) ? 1 : atoms);
+            for (int j = 0; j < mmas; ++j) {
+              tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
+                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sfa + 4 * j,
+                          t_sfb_mma + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
             }
           }
-          // 128-byte swizzled K-major tiles: eight-row groups 1024 bytes apart; one
-          // K = 64 step is 32 bytes further along the row.
-          const uint64_t desc_a = smem_matrix_desc(a_src, 16, 1024, 2);
-          const uint64_t desc_b = smem_matrix_desc(b_src, 16, 1024, 2);
-          for (int j = 0; j < (NVFP4_PROBE_FLAG(p, 1) ? 0 : (NVFP4_PROBE_FLAG(p, 3) ? 1 : atoms)); ++j) {
-            tc_mma_nvf4(d_tmem, desc_a + 2 * j, desc_b + 2 * j, idesc,
-                        tmem_base + Cfg::SFA_COL + 4 * j,
-                        tmem_base + Cfg::SFB_COL + j * Cfg::SFB_COLS + sfb_half,
-                        (kt > s.k0 || j > 0) ? 1u : 0u);
-          }
-          tc_commit(smem_u32(&bar_empty[stage]));
+          accumulate = 1;
+          atoms_left -= 4;
+          tc_commit(empty0 + 8 * stage);
+          stage16 += kStage16;
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
+            stage16 = 0;
           }
         }
         if (!ok) break;
@@ -491,19 +553,21 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
         }
       } else {
-        // Partial sum of this segment -> workspace slot, column-major so that the
-        // 32 rows of a warp write 128 contiguous bytes.
+        // Partial sum of this segment -> workspace slot as float4 [column / 4][row], so
+        // that the 32 rows of a warp write (and later read) 512 contiguous bytes.
         const long long my_start = p.total_units * cta / grid;
         const long long my_slot = 2 * cta + (my_start < s.tile_unit0 ? 1 : 0);
-        float* ws = p.partials + my_slot * p.slot_floats;
+        float4* ws = reinterpret_cast<float4*>(p.partials + my_slot * p.slot_floats);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r1[32];
           tmem_load_32(taddr + c * 32, r1);
           tmem_load_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            ws[(c * 32 + i) * 128 + row] = __uint_as_float(r1[i]);
+          for (int q = 0; q < 8; ++q) {
+            ws[(c * 8 + q) * 128 + row] =
+                make_float4(__uint_as_float(r1[4 * q]), __uint_as_float(r1[4 * q + 1]),
+                            __uint_as_float(r1[4 * q + 2]), __uint_as_float(r1[4 * q + 3]));
           }
         }
         tc_fence_before_sync();
@@ -532,16 +596,31 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
               s1[i] = 0.0f;
               s2[i] = 0.0f;
             }
-#pragma unroll 1
+#pragma unroll 2
             for (long long b = first_cta; b <= last_cta; ++b) {
               const long long b_start = p.total_units * b / grid;
               const long long slot = 2 * b + (b_start < s.tile_unit0 ? 1 : 0);
-              const float* src = p.partials + slot * p.slot_floats;
+              const float4* src = reinterpret_cast<const float4*>(p.partials + slot * p.slot_floats);
+              float4 t1[8];
+              float4 t2[8];
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                s1[i] += __ldcg(src + (c * 32 + i) * 128 + row);
+              for (int q = 0; q < 8; ++q) {
+                t1[q] = __ldcg(src + (c * 8 + q) * 128 + row);
                 if constexpr (Cfg::DUAL) {
-                  s2[i] += __ldcg(src + (Cfg::OUT_BN + c * 32 + i) * 128 + row);
+                  t2[q] = __ldcg(src + (Cfg::OUT_BN / 4 + c * 8 + q) * 128 + row);
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                s1[4 * q + 0] += t1[q].x;
+                s1[4 * q + 1] += t1[q].y;
+                s1[4 * q + 2] += t1[q].z;
+                s1[4 * q + 3] += t1[q].w;
+                if constexpr (Cfg::DUAL) {
+                  s2[4 * q + 0] += t2[q].x;
+                  s2[4 * q + 1] += t2[q].y;
+                  s2[4 * q + 2] += t2[q].z;
+                  s2[4 * q + 3] += t2[q].w;
                 }
               }
             }

@@ -172,6 +172,13 @@ __device__ __forceinline__ uint64_t smem_matrix_desc(uint32_t addr, uint32_t lea
   return d;
 }
 
+// A descriptor from its two 32-bit halves.
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // 32 rows x 16 bytes of shared memory -> 4 columns of tensor memory, the same
 // data in each of the four 32-lane quarters.
 __device__ __forceinline__ void tc_copy_32x128b_x4(uint32_t tmem_addr, uint64_t desc) {

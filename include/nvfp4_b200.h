@@ -89,7 +89,7 @@ int nvfp4_gemm_plan_create(nvfp4_plan** plan, int device, int out_kind, int m, i
 /* Fused dual GEMM plan: D = half(silu(alpha*A*B1^T) * (alpha*A*B2^T)). The reference
  * runs this as two GEMM launches plus silu_product
  * (harness/workloads/nvfp4_dual_gemm.py:1-30, resources/nvfp4_dual_gemm/task.yml:12-26);
- * here it is one launch. Output FP16, n % 8 == 0. */
+ * here it is one launch. Output FP16, n % 4 == 0 (as for the FP32 stage). */
 int nvfp4_dual_gemm_plan_create(nvfp4_plan** plan, int device, int m, int n, int k, int l,
                                 const nvfp4_config* config);
 
@@ -131,7 +131,9 @@ int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* co
                           const void* const* sfa, const void* const* sfb, void* const* d,
                           void* workspace, void* stream);
 
-/* One launch covering every group. Replaces NVFP4GroupGEMM._launch
+/* One launch covering every group, reading the group table that
+ * nvfp4_group_gemm_bind wrote into `workspace` (one plan may be bound to several
+ * workspaces, one per operand set). Replaces NVFP4GroupGEMM._launch
  * (harness/workloads/nvfp4_group_gemm.py:593-600). */
 int nvfp4_group_gemm_launch(nvfp4_plan* plan, void* workspace, void* stream);
 

@@ -1,0 +1,106 @@
+"""The benchmark configurations at full size on a B200, checked through properties
+that need no CPU oracle run: bit-exactness against an FP32 torch matmul on the GPU for
+integer scales (sums exact in any order), agreement within the tolerance for N(0,1)
+operands, N-shard consistency, alpha scaling, and run-to-run determinism."""
+
+import pytest
+import torch
+
+from harness import CaseSpec, get_workload, sharding
+from harness.workloads import quantization as q
+from harness.workloads.nvfp4_gemm import to_task_scales
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def exact_matmul():
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    yield
+    torch.backends.cuda.matmul.allow_tf32 = previous
+
+
+def normal_operand(rows, k, seed, device):
+    """N(0,1) FP32 from a CPU generator, quantised to NVFP4 on the device."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, k, generator=g).to(device)
+    packed, scales = q.quantize_nvfp4(x)
+    return packed[..., None], scales[..., None]
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 7168, 16384), (8192, 8192, 8192)])
+def test_dense_full_size_exact_with_integer_scales(m, n, k):
+    with get_workload("nvfp4_gemm").from_arch("sm_100a", device="cuda") as workload:
+        case = CaseSpec("full", {"m": m, "n": n, "k": k, "l": 1, "values": "restricted",
+                                 "scales": "int1_2"}, 3)
+        inputs = workload.get_inputs(case)
+        (ref,) = workload.get_reference(inputs)
+        (out,) = workload.run(inputs)
+        (again,) = workload.run(inputs)
+        torch.cuda.synchronize()
+        workload.check_status()
+        assert torch.equal(out, ref), "integer-scale result must be bit-identical"
+        assert torch.equal(out, again), "two launches must agree bit for bit"
+
+
+def test_dense_decode_shape_with_normal_operands_and_shards():
+    m, n, k = 128, 7168, 16384
+    dev = torch.device("cuda")
+    with get_workload("nvfp4_gemm").from_arch("sm_100a", device="cuda") as workload:
+        a, sa = normal_operand(m, k, 1, dev)
+        b, sb = normal_operand(n, k, 2, dev)
+        alpha = torch.ones(1, device=dev)
+        inputs = (a, b, to_task_scales(sa), to_task_scales(sb), alpha)
+        (ref,) = workload.get_reference(inputs)
+        (out,) = workload.run(inputs)
+        (again,) = workload.run(inputs)
+        torch.cuda.synchronize()
+        workload.validate((ref,), (out,))
+        assert torch.equal(out, again)
+        # alpha = 2**-3 scales every output exactly (power of two, no overflow).
+        eighth = (a, b, inputs[2], inputs[3], torch.full((1,), 0.125, device=dev))
+        (scaled,) = workload.run(eighth)
+        torch.cuda.synchronize()
+        assert torch.equal(scaled.float(), (out.float() * 0.125).half().float())
+        # Every 8-way N shard equals the matching columns of the full result within the
+        # tolerance (a shard splits K differently, so sums may round differently).
+        for rank in (0, 3, 7):
+            part, (start, stop) = sharding.shard_dense_inputs(inputs, rank, 8)
+            (piece,) = workload.run(part)
+            torch.cuda.synchronize()
+            workload.validate((ref[:, start:stop].contiguous(),), (piece.contiguous(),))
+        workload.check_status()
+
+
+def test_dual_config_matches_reference_with_normal_operands():
+    m, n, k = 256, 4096, 7168
+    dev = torch.device("cuda")
+    with get_workload("nvfp4_dual_gemm").from_arch("sm_100a", device="cuda") as workload:
+        a, sa = normal_operand(m, k, 1, dev)
+        b1, s1 = normal_operand(n, k, 2, dev)
+        b2, s2 = normal_operand(n, k, 3, dev)
+        inputs = (a, b1, b2, to_task_scales(sa), to_task_scales(s1), to_task_scales(s2),
+                  torch.ones(1, device=dev))
+        (ref,) = workload.get_reference(inputs)
+        (out,) = workload.run(inputs)
+        torch.cuda.synchronize()
+        workload.check_status()
+        # With global scale 1 a few gate products exceed the FP16 range: both sides must
+        # produce the same infinities.
+        assert torch.equal(torch.isinf(ref), torch.isinf(out))
+        finite = torch.isfinite(ref)
+        torch.testing.assert_close(out[finite], ref[finite], rtol=1e-2, atol=1e-2)
+
+
+def test_grouped_config_exact_with_task_distribution():
+    ms = (40, 96, 128, 256, 384, 512, 768, 1024)
+    with get_workload("nvfp4_group_gemm").from_arch("sm_100a", device="cuda") as workload:
+        case = CaseSpec("config5", {"groups": [(m, 4096, 7168) for m in ms]}, 1111)
+        inputs = workload.get_inputs(case)
+        ref = workload.get_reference(inputs)
+        out = workload.run(inputs)
+        torch.cuda.synchronize()
+        workload.check_status()
+        for got, want in zip(out, ref):
+            assert torch.equal(got, want)

@@ -1,0 +1,233 @@
+"""Parity of the CUDA path on a B200, through the operator API and the C ABI: every
+smoke case of every workload against the harness's torch reference (the reference
+project's own check, tests/test_workloads.py:98-157 there) and against the numpy
+oracle; inputs not mutated; library re-bind; prepared launches allocate nothing and
+return the same outputs; the device status word stays zero."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+from gpu_util import (assert_matches_oracle, blocked_storage, integer_scaled, oracle_dense,
+                      snapshot, storage, unchanged)
+from harness import enumerate_workloads, get_workload, native
+from oracle import nvfp4_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+WORKLOADS = ("nvfp4_gemm", "nvfp4_dual_gemm_gemm", "nvfp4_dual_gemm", "nvfp4_group_gemm",
+             "nvfp4_dual_gemm_pack_scales", "nvfp4_dual_gemm_silu_product")
+
+
+@pytest.fixture(scope="module", autouse=True)
+def exact_matmul():
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    yield
+    torch.backends.cuda.matmul.allow_tf32 = previous
+
+
+def check_prepared(workload, case, inputs, before, ref):
+    tag = f"{workload.name}/{case.name}"
+    launch, outputs = workload.prepare(inputs)
+    torch.cuda.synchronize()
+    for call in range(2):
+        allocated = torch.cuda.memory_stats()["allocation.all.allocated"]
+        result = launch()
+        new = torch.cuda.memory_stats()["allocation.all.allocated"] - allocated
+        assert not new, f"{tag}: prepared launch {call} allocated {new} blocks"
+        assert result is outputs, f"{tag}: prepared launch must return its outputs"
+        torch.cuda.synchronize()
+        if call == 0:
+            workload.validate(ref, outputs)
+    for old, new_input in zip(before, inputs):
+        assert unchanged(old, new_input), f"{tag}: prepared launch mutated inputs"
+
+
+def oracle_check(workload, case, inputs, out):
+    name = f"{workload.name}/{case.name}"
+    exact = integer_scaled(case) or (
+        case.params.get("scales") is None and workload.name in ("nvfp4_gemm", "nvfp4_group_gemm"))
+    if workload.name == "nvfp4_gemm":
+        assert_matches_oracle(out[0], oracle_dense(inputs), name, exact and case.params.get("alpha", 1.0) == 1.0)
+    elif workload.name == "nvfp4_dual_gemm_gemm":
+        a, b, sfa, sfb, alpha = inputs
+        m, half_k, batches = a.shape
+        n, k = b.shape[0], 2 * half_k
+        rb_a, rb_n, cb = -(-m // 128), -(-n // 128), -(-(k // 16) // 4)
+        sa = o.from_blocked(sfa.view(torch.uint8).cpu().numpy().reshape(batches, rb_a, cb, 32, 4, 4), m, k // 16)
+        sb = o.from_blocked(sfb.view(torch.uint8).cpu().numpy().reshape(batches, rb_n, cb, 32, 4, 4), n, k // 16)
+        expected = o.gemm(storage(a), storage(b), sa, sb, float(alpha.item()))
+        assert_matches_oracle(out[0], expected, name, integer_scaled(case), rtol=1e-4, atol=1e-4)
+    elif workload.name == "nvfp4_dual_gemm":
+        a, b1, b2, sfa, sfb1, sfb2, alpha = inputs
+        m, half_k, _ = a.shape
+        n, k = b1.shape[0], 2 * half_k
+        sa = o.from_blocked(blocked_storage(sfa), m, k // 16)
+        s1 = o.from_blocked(blocked_storage(sfb1), n, k // 16)
+        s2 = o.from_blocked(blocked_storage(sfb2), n, k // 16)
+        expected = o.dual_gemm(storage(a), storage(b1), storage(b2), sa, s1, s2, float(alpha.item()))
+        assert_matches_oracle(out[0], expected, name, False)
+    elif workload.name == "nvfp4_group_gemm":
+        problems = []
+        for a, b, sfa, sfb in workload.groups_of(inputs):
+            m, n, k = workload.problem_of((a, b))
+            sa = o.from_blocked(sfa.view(torch.uint8).cpu().numpy()[None], m, k // 16)[0]
+            sb = o.from_blocked(sfb.view(torch.uint8).cpu().numpy()[None], n, k // 16)[0]
+            problems.append((a.cpu().numpy(), b.cpu().numpy(), sa, sb))
+        for index, expected in enumerate(o.group_gemm(problems)):
+            assert_matches_oracle(out[index], expected, f"{name}/{index}", exact)
+    elif workload.name == "nvfp4_dual_gemm_pack_scales":
+        expected = o.pack_scales(storage(inputs[0]))
+        assert np.array_equal(out[0].view(torch.uint8).cpu().numpy(), expected), name
+    else:
+        expected = o.silu_product(storage(inputs[0]), storage(inputs[1]))
+        assert_matches_oracle(out[0], expected, name, False)
+
+
+@pytest.mark.parametrize("name", WORKLOADS)
+def test_smoke_cases_match_reference_and_oracle(name):
+    cls = get_workload(name)
+    assert cls in enumerate_workloads("sm_100a")
+    with cls.from_arch("sm_100a", device="cuda") as workload:
+        assert workload.is_supported(), "not a B200"
+        cases = [c for c in workload.get_cases() if c.suite == "smoke"]
+        assert cases
+        for index, case in enumerate(cases):
+            inputs = workload.get_inputs(case)
+            before = snapshot(inputs)
+            ref = workload.get_reference(inputs)
+            out = workload.run(inputs)
+            torch.cuda.synchronize()
+            workload.validate(ref, out)
+            oracle_check(workload, case, inputs, out)
+            for old, new in zip(before, inputs):
+                assert unchanged(old, new), f"{name}/{case.name} mutated inputs"
+            if index == 0:
+                workload.patch_image(workload.get_image())
+                again = workload.run(inputs)
+                torch.cuda.synchronize()
+                workload.validate(ref, again)
+            check_prepared(workload, case, inputs, before, ref)
+            workload.check_status()
+
+
+def test_golden_fixtures_through_the_c_abi():
+    """Inputs and outputs recorded from the reference itself; the kernel is called with
+    raw pointers, as a foreign-language binding would."""
+    data = load_golden("nvfp4_gemm_cases.npz")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    for name in sorted({key.split("/")[0] for key in data}):
+        t = {f: torch.from_numpy(data[f"{name}/{f}"]).to(dev) for f in ("a", "b", "sfa", "sfb", "alpha")}
+        batches, m, half_k = t["a"].shape
+        n, k = t["b"].shape[1], 2 * half_k
+        d = torch.full((batches, m, n), float("nan"), dtype=torch.float16, device=dev)
+        plan = native.Plan.dense(0, native.OUT_F16, m, n, k, batches)
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        plan.launch_dense(t["a"].data_ptr(), t["b"].data_ptr(), t["sfa"].data_ptr(),
+                          t["sfb"].data_ptr(), t["alpha"].data_ptr(), d.data_ptr(),
+                          ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        np.testing.assert_allclose(d.cpu().numpy().astype(np.float32),
+                                   data[name + "/d"].astype(np.float32), rtol=1e-3, atol=1e-3,
+                                   err_msg=name)
+        plan.destroy()
+
+    dual = load_golden("nvfp4_dual_gemm_cases.npz")
+    for name in sorted({key.split("/")[0] for key in dual}):
+        g = {f: dual[f"{name}/{f}"] for f in ("a", "b1", "b2", "sa", "s1", "s2", "out")}
+        batches, m, half_k = g["a"].shape
+        n, k = g["b1"].shape[1], 2 * half_k
+        ops = [torch.from_numpy(x).to(dev) for x in (
+            g["a"], g["b1"], g["b2"], o.to_blocked(g["sa"]), o.to_blocked(g["s1"]), o.to_blocked(g["s2"]))]
+        alpha = torch.full((1,), float(dual[name + "/alpha"]), device=dev)
+        d = torch.full((batches, m, n), float("nan"), dtype=torch.float16, device=dev)
+        plan = native.Plan.dual(0, m, n, k, batches)
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        plan.launch_dual(*(x.data_ptr() for x in ops), alpha.data_ptr(), d.data_ptr(),
+                         ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        np.testing.assert_allclose(d.cpu().numpy().astype(np.float32), g["out"].astype(np.float32),
+                                   rtol=1e-3, atol=1e-3, err_msg=name)
+        plan.destroy()
+
+
+@pytest.mark.parametrize("tile_n", (64, 128, 256))
+@pytest.mark.parametrize("schedule", (1, 2))
+def test_every_tile_width_and_schedule(tile_n, schedule):
+    """The dense kernel's three tile widths under both schedules (whole tiles and
+    stream-K with its fix-up) on shapes with partial tiles, batches and a K tail; integer
+    scales, so results must equal the oracle bit for bit however K is split."""
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    cases = [c for c in workload.get_cases() if c.suite == "smoke" and integer_scaled(c)
+             and c.params.get("alpha", 1.0) == 1.0]
+    assert len(cases) >= 5
+    for case in cases:
+        inputs = workload.get_inputs(case)
+        a, b, sfa, sfb, alpha = inputs
+        m, n, k, batches = (case.params[key] for key in "mnkl")
+        d = torch.full((batches, m, n), float("nan"), dtype=torch.float16, device=dev)
+        plan = native.Plan.dense(0, native.OUT_F16, m, n, k, batches, tile_n=tile_n,
+                                 schedule=schedule)
+        info = plan.info()
+        assert info["tile_n"] == tile_n
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        for _ in range(2):  # the second launch reuses the self-resetting tile counters
+            d.fill_(float("nan"))
+            plan.launch_dense(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                              alpha.data_ptr(), d.data_ptr(), ws.data_ptr(), stream)
+            assert plan.status(ws.data_ptr(), stream) == 0
+            assert_matches_oracle(d.permute(1, 2, 0), oracle_dense(inputs),
+                                  f"{case.name}/bn{tile_n}/{info['schedule']}", True)
+        plan.destroy()
+
+
+def test_grouped_stream_k_and_rebinding():
+    """One grouped plan bound to two operand sets (two workspaces), stream-K forced so
+    that tiles of different groups share CTAs and the fix-up runs across groups."""
+    workload = get_workload("nvfp4_group_gemm")(None, device="cuda")
+    case = next(c for c in workload.get_cases() if c.name == "skewed_full")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    plan = native.Plan.grouped(0, case.params["groups"], schedule=2)
+    assert plan.info()["schedule"] == "stream_k"
+    sets = []
+    for seed in (5, 6):
+        inputs = workload.get_inputs(type(case)(case.name, case.params, seed, case.suite))
+        outputs = workload.allocate_outputs(inputs)
+        config = workload.launch_config(inputs, outputs)
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        plan.bind_groups(*config.pointers, ws.data_ptr(), stream)
+        sets.append((inputs, outputs, ws))
+    for inputs, outputs, ws in sets + sets[::-1]:
+        for out in outputs:
+            out.fill_(float("nan"))
+        plan.launch_groups(ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        ref = workload.get_reference(inputs)
+        for got, want in zip(outputs, ref):
+            assert torch.equal(got, want)
+    plan.destroy()
+
+
+def test_native_rejects_misaligned_and_wrong_plans():
+    stream = torch.cuda.current_stream().cuda_stream
+    plan = native.Plan.dense(0, native.OUT_F16, 128, 128, 128, 1)
+    buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    base = buf.data_ptr()
+    with pytest.raises(ValueError):
+        plan.launch_dense(base + 8, base, base, base, base, base, base, stream)
+    with pytest.raises(ValueError):
+        plan.launch_dual(base, base, base, base, base, base, base, base, base, stream)
+    with pytest.raises(ValueError):
+        native.Plan.dense(0, native.OUT_F16, 128, 128, 128, 1, tile_n=96)
+    assert native.device_supported(0)
+    plan.destroy()
