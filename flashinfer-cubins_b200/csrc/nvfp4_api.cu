@@ -340,9 +340,21 @@ int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream) {
   DeviceGuard guard;
   CUDA_TRY(guard.enter(plan->device));
   void* args[1] = {&kp};
-  CUDA_TRY(cudaLaunchKernel(reinterpret_cast<const void*>(plan->kernel.fn), dim3(plan->ctas),
-                            dim3(plan->kernel.threads), args, plan->kernel.smem_bytes,
-                            static_cast<cudaStream_t>(stream)));
+  // Programmatic stream serialization (as the reference's dense launches use,
+  // harness/workloads/nvfp4_gemm.py:143-147): this kernel's prologue may overlap the
+  // tail of the kernel before it; it waits on the device before touching global memory.
+  static const bool use_pdl = env_int("NVFP4_PDL", 1) != 0;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(plan->ctas);
+  config.blockDim = dim3(plan->kernel.threads);
+  config.dynamicSmemBytes = plan->kernel.smem_bytes;
+  config.stream = static_cast<cudaStream_t>(stream);
+  config.attrs = attribute;
+  config.numAttrs = use_pdl ? 1 : 0;
+  CUDA_TRY(cudaLaunchKernelExC(&config, reinterpret_cast<const void*>(plan->kernel.fn), args));
   return 0;
 }
 
@@ -386,7 +398,11 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     plan->tile_n = 256;
     plan->out_tile_n = 128;
   } else {
-    plan->tile_n = default_tile_n(config, 128);
+    // 256-column tiles once they still give every SM at least two tiles: half the A
+    // re-reads and a single-buffered accumulator pay off only when tiles are plentiful.
+    const long long wide_tiles =
+        static_cast<long long>(ceil_div(m, 128)) * ceil_div(n, 256) * l;
+    plan->tile_n = default_tile_n(config, wide_tiles >= 2ll * sms ? 256 : 128);
     plan->out_tile_n = plan->tile_n;
   }
   plan->problems.resize(1);
@@ -447,7 +463,11 @@ int nvfp4_group_gemm_plan_create(nvfp4_plan** out, int device, int groups, const
   plan->device = device;
   plan->out_kind = NVFP4_OUT_F16;
   plan->sm_count = sms;
-  plan->tile_n = default_tile_n(config, 128);
+  long long wide_tiles = 0;
+  for (int g = 0; g < groups; ++g) {
+    wide_tiles += static_cast<long long>(ceil_div(mnk[3 * g], 128)) * ceil_div(mnk[3 * g + 1], 256);
+  }
+  plan->tile_n = default_tile_n(config, wide_tiles >= 2ll * sms ? 256 : 128);
   plan->out_tile_n = plan->tile_n;
   plan->problems.resize(groups);
   for (int g = 0; g < groups; ++g) {

@@ -9,12 +9,14 @@
 // at byte ((r/128) * kb + c/4) * 512 + (r%32) * 16 + ((r/32)%4) * 4 + c%4, kb =
 // ceil(k/64) (the layout of harness/workloads/quantization.py:90-102 in the reference).
 //
-// Roles (192 threads): warp 0 lane 0 issues TMA loads into a ring of shared-memory
-// stages; warp 1 lane 0 copies scale atoms into tensor memory (tcgen05.cp) and issues
-// tcgen05.mma kind::mxf4nvf4 (128 x BN x 64 per instruction, accumulators in tensor
-// memory); warps 2-5 read finished accumulators (tcgen05.ld), apply the epilogue and
-// store. A 512-byte scale atom is exactly the 32 x 16-byte source of one
-// tcgen05.cp.32x128b.warpx4, so scales go global -> shared -> tensor memory unchanged.
+// Roles (320 threads): warp 0 lane 0 issues TMA loads into a ring of shared-memory
+// stages; warps 6-9 move each stage's scale atoms from shared memory into that stage's
+// columns of tensor memory (one warp per 32-lane quarter: a 512-byte atom is 32 rows of
+// 16 bytes, i.e. one ld.shared.v4 + one tcgen05.st.32x32b.x4 per warp, no reshuffle);
+// warp 1 lane 0 issues tcgen05.mma kind::mxf4nvf4 (128 x BN x 64 per instruction,
+// accumulators in tensor memory); warps 2-5 read finished accumulators (tcgen05.ld),
+// apply the epilogue and store. Keeping the scale copies off the MMA issue queue
+// matters: tcgen05.cp there cost about as much queue time as the MMAs themselves.
 //
 // Work is a list of (tile, k-tile range) segments that every role derives from the
 // same counters: in data-parallel mode CTA c takes tiles c, c + grid, ...; in stream-K
@@ -62,6 +64,7 @@ enum : int {
   kStatusMmaInputTimeout = 2,
   kStatusMmaAccumTimeout = 3,
   kStatusEpilogueTimeout = 4,
+  kStatusScaleTimeout = 5,
 };
 
 struct alignas(64) KernelParams {
@@ -200,10 +203,11 @@ struct GemmConfig {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
   static constexpr int ACC_BUFS = BN <= 128 ? 2 : 1;
   static constexpr int SFB_COLS = const_max(4, BN / 32);  // columns per k-block
-  static constexpr int SFA_COL = ACC_BUFS * BN;
-  static constexpr int SFB_COL = SFA_COL + 16;
-  static constexpr int TMEM_COLS = const_pow2_at_least(SFB_COL + 4 * SFB_COLS);
-  static constexpr int THREADS = 192;
+  // Scale columns of one stage: SFA (4 k-blocks x 4) then SFB (4 k-blocks x SFB_COLS).
+  static constexpr int SF_STAGE_COLS = 16 + 4 * SFB_COLS;
+  static constexpr int SF_COL = ACC_BUFS * BN;  // first scale column
+  static constexpr int TMEM_COLS = const_pow2_at_least(SF_COL + STAGES * SF_STAGE_COLS);
+  static constexpr int THREADS = 320;
   static_assert(BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
   static_assert(!DUAL || BN == 256, "dual GEMM uses two 128-column B tiles");
   static_assert(TMEM_COLS <= 512, "tensor memory exceeded");
@@ -265,6 +269,55 @@ __device__ __forceinline__ void store_row_chunk(OutT* row_ptr, int col0, int n,
   }
 }
 
+// Adds to s1 (and s2 for the dual GEMM) the 32-column chunk `c` of row `row` of the
+// partial tiles that CTAs [first, last] left in the workspace for the tile whose first
+// unit is `tile_unit0`, in CTA order; loads of two partials are in flight together.
+template <class Cfg>
+__device__ __forceinline__ void add_partials(const KernelParams& p, float (&s1)[32],
+                                             float (&s2)[32], long long first, long long last,
+                                             long long tile_unit0, long long grid, int c, int row) {
+  constexpr int GROUP = 1;
+#pragma unroll 1
+  for (long long b0 = first; b0 <= last; b0 += GROUP) {
+    float4 t1[GROUP][8];
+    float4 t2[GROUP][8];
+#pragma unroll
+    for (int u = 0; u < GROUP; ++u) {
+      const long long b = b0 + u;
+      if (b <= last) {
+        const long long b_start = p.total_units * b / grid;
+        const long long slot = 2 * b + (b_start < tile_unit0 ? 1 : 0);
+        const float4* src = reinterpret_cast<const float4*>(p.partials + slot * p.slot_floats);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          t1[u][q] = __ldcg(src + (c * 8 + q) * 128 + row);
+          if constexpr (Cfg::DUAL) {
+            t2[u][q] = __ldcg(src + (Cfg::OUT_BN / 4 + c * 8 + q) * 128 + row);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < GROUP; ++u) {
+      if (b0 + u <= last) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          s1[4 * q + 0] += t1[u][q].x;
+          s1[4 * q + 1] += t1[u][q].y;
+          s1[4 * q + 2] += t1[u][q].z;
+          s1[4 * q + 3] += t1[u][q].w;
+          if constexpr (Cfg::DUAL) {
+            s2[4 * q + 0] += t2[u][q].x;
+            s2[4 * q + 1] += t2[u][q].y;
+            s2[4 * q + 2] += t2[u][q].z;
+            s2[4 * q + 3] += t2[u][q].w;
+          }
+        }
+      }
+    }
+  }
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
@@ -278,6 +331,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   __shared__ alignas(8) uint64_t bar_empty[STAGES];
   __shared__ alignas(8) uint64_t bar_acc_full[ACC_BUFS];
   __shared__ alignas(8) uint64_t bar_acc_empty[ACC_BUFS];
+  __shared__ alignas(8) uint64_t bar_sf_full[STAGES];  // a stage's scale atoms have landed
+  __shared__ alignas(8) uint64_t bar_scales[STAGES];   // ... and are in tensor memory
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int epi_last_flag;
@@ -291,6 +346,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_sf_full[s]), 1);
+      mbar_init(smem_u32(&bar_scales[s]), 4);
     }
 #pragma unroll
     for (int a = 0; a < ACC_BUFS; ++a) {
@@ -309,6 +366,11 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
+  // Everything above touched only this CTA's shared and tensor memory, so under
+  // programmatic dependent launch it overlaps the previous kernel's tail; nothing below
+  // may read or write global memory before that kernel has finished.
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -326,6 +388,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       uint32_t phase = 0;
       uint32_t stage_smem = smem_base;
       const uint32_t full0 = smem_u32(&bar_full[0]);
+      const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
       const uint32_t empty0 = smem_u32(&bar_empty[0]);
       bool ok = true;
       while (ok && it.next(s)) {
@@ -361,25 +424,36 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           }
           const uint32_t sf_bytes = atoms_left >= 4 ? 2048u : static_cast<uint32_t>(atoms_left) * 512u;
           const uint32_t bar = full0 + 8 * stage;
-          mbar_expect_tx(bar, ab_bytes + (NVFP4_PROBE_FLAG(p, 5) ? 0u : sf_bytes * (1u + sfb_valid)));
+          const uint32_t sf_bar = sf_full0 + 8 * stage;
           const uint32_t a_dst = stage_smem;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           const uint32_t sfa_dst = b_dst + Cfg::B_BYTES;
           const uint32_t sfb_dst = sfa_dst + Cfg::SFA_BYTES;
+          // Scales first, on their own barrier: they are small, land early, and the
+          // scale movers can put them into tensor memory while A and B are still in
+          // flight.
+          if (!NVFP4_PROBE_FLAG(p, 5)) {
+            mbar_expect_tx(sf_bar, sf_bytes * (1u + sfb_valid));
+            bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol_a);
+#pragma unroll
+            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+              if (sfb_src[i] != nullptr) {
+                bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, sf_bar, pol_b);
+                sfb_src[i] += 2048;
+              }
+            }
+          } else {
+            mbar_arrive(sf_bar);
+          }
           if (!probe_no_ab) {
+            mbar_expect_tx(bar, ab_bytes);
             tma_load_3d(a_dst, map_a, bar, kbyte, m0, s.batch, pol_a);
             tma_load_3d(b_dst, map_b, bar, kbyte, n0, s.batch, pol_b);
             if constexpr (Cfg::DUAL) {
               tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kbyte, n0, s.batch, pol_b);
             }
-          }
-          if (!NVFP4_PROBE_FLAG(p, 5)) bulk_load(sfa_dst, sfa_src, sf_bytes, bar, pol_a);
-#pragma unroll
-          for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-            if (sfb_src[i] != nullptr && !NVFP4_PROBE_FLAG(p, 5)) {
-              bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, bar, pol_b);
-              sfb_src[i] += 2048;
-            }
+          } else {
+            mbar_arrive(bar);
           }
           sfa_src += 2048;
           atoms_left -= 4;
@@ -401,26 +475,23 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = nvf4_instr_desc(128, BN);
-      // Descriptor words that never change: the high halves (stride, version, swizzle)
-      // and, per stage, the low halves (address >> 4, leading offset). A stage is
-      // STAGE_BYTES / 16 further in the address field; a K = 64 step 2 further; a scale
-      // atom 32 further.
+      // Descriptor words that never change: the high half (stride between eight-row
+      // groups 1024 bytes, version, 128-byte swizzle) and, per stage, the low half
+      // (address >> 4, leading offset). A stage is STAGE_BYTES / 16 further in the
+      // address field; a K = 64 step is 32 bytes = 2 further along the swizzled row.
       constexpr uint32_t kHiOperand = (1024u >> 4) | (1u << 14) | (2u << 29);
-      constexpr uint32_t kHiScale = (128u >> 4) | (1u << 14);
       constexpr uint32_t kStage16 = Cfg::STAGE_BYTES >> 4;
       const uint32_t lo_a0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
       const uint32_t lo_b0 = lo_a0 + (Cfg::A_BYTES >> 4);
-      const uint32_t lo_sfa0 = (smem_base + Cfg::A_BYTES + Cfg::B_BYTES) >> 4;
-      const uint32_t lo_sfb0 = lo_sfa0 + (Cfg::SFA_BYTES >> 4);
-      const uint32_t t_sfa = tmem_base + Cfg::SFA_COL;
-      const uint32_t t_sfb = tmem_base + Cfg::SFB_COL;
       const uint32_t full0 = smem_u32(&bar_full[0]);
       const uint32_t empty0 = smem_u32(&bar_empty[0]);
+      const uint32_t scales0 = smem_u32(&bar_scales[0]);
       WorkIter<Cfg::GROUPED> it(p);
       Segment s;
       int stage = 0;
       uint32_t phase = 0;
       uint32_t stage16 = 0;
+      uint32_t t_sf = tmem_base + Cfg::SF_COL;  // this stage's scale columns
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
@@ -433,11 +504,12 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         // A 64-column tile uses half of a 128-row scale atom: columns 0-1 or 2-3.
-        const uint32_t t_sfb_mma = t_sfb + ((BN == 64) ? 2u * (s.n_tile & 1) : 0u);
+        const uint32_t sfb_half = (BN == 64) ? 2u * (s.n_tile & 1) : 0u;
         int atoms_left = pd.sf_kb - 4 * s.k0;
         uint32_t accumulate = 0;
         for (int kt = s.k0; kt < s.k1; ++kt) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr) ||
+              !mbar_wait(scales0 + 8 * stage, phase, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusMmaInputTimeout);
             ok = false;
             break;
@@ -445,52 +517,33 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           tc_fence_after_sync();
           const uint32_t lo_a = lo_a0 + stage16;
           const uint32_t lo_b = lo_b0 + stage16;
-          const uint32_t lo_sfa = lo_sfa0 + stage16;
-          const uint32_t lo_sfb = lo_sfb0 + stage16;
-          if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 0) && !NVFP4_PROBE_FLAG(p, 1) &&
-              !NVFP4_PROBE_FLAG(p, 3)) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              tc_copy_32x128b_x4(t_sfa + 4 * j, pack_desc(lo_sfa + 32 * j, kHiScale));
-#pragma unroll
-              for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-                tc_copy_32x128b_x4(t_sfb + j * Cfg::SFB_COLS + 4 * i,
-                                   pack_desc(lo_sfb + 128 * i + 32 * j, kHiScale));
-              }
-            }
+          const uint32_t t_sfb = t_sf + 16 + sfb_half;
+          if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 1)) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
-                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sfa + 4 * j,
-                          t_sfb_mma + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
+                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
+                          t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
             }
           } else {
-            // K tail (fewer than four 64-wide blocks left) and timing experiments.
-            const int atoms = min(4, atoms_left);
-            for (int j = 0; j < (NVFP4_PROBE_FLAG(p, 0) ? 0 : atoms); ++j) {
-              tc_copy_32x128b_x4(t_sfa + 4 * j, pack_desc(lo_sfa + 32 * j, kHiScale));
-              if (NVFP4_PROBE_FLAG(p, 6)) break;
-#pragma unroll
-              for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-                tc_copy_32x128b_x4(t_sfb + j * Cfg::SFB_COLS + 4 * i,
-                                   pack_desc(lo_sfb + 128 * i + 32 * j, kHiScale));
-              }
-            }
-            const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : (NVFP4_PROBE_FLAG(p, 3) ? 1 : atoms);
+            // K tail: fewer than four 64-wide blocks left (or a timing experiment).
+            const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
             for (int j = 0; j < mmas; ++j) {
               tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
-                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sfa + 4 * j,
-                          t_sfb_mma + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
+                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
+                          t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
             }
           }
           accumulate = 1;
           atoms_left -= 4;
           tc_commit(empty0 + 8 * stage);
           stage16 += kStage16;
+          t_sf += Cfg::SF_STAGE_COLS;
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
             stage16 = 0;
+            t_sf = tmem_base + Cfg::SF_COL;
           }
         }
         if (!ok) break;
@@ -501,7 +554,77 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         }
       }
     }
-  } else {
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ scale movers
+    // Warp q of the four owns tensor-memory lanes 32q..32q+31. For every stage it copies
+    // the stage's scale atoms (shared memory, written by the producer's bulk copies)
+    // into the stage's scale columns: lane i takes the atom's 16-byte row i, which holds
+    // the scales of rows i, 32+i, 64+i, 96+i for one 64-wide K block = four columns.
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t full0 = smem_u32(&bar_sf_full[0]);
+    const uint32_t scales0 = smem_u32(&bar_scales[0]);
+    const uint32_t row_off = static_cast<uint32_t>(lane) * 16u;
+    WorkIter<Cfg::GROUPED> it(p);
+    Segment s;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
+    uint32_t t_sf = tmem_base + lane_base + Cfg::SF_COL;
+    bool ok = true;
+    while (ok && it.next(s)) {
+      int atoms_left = it.pd.sf_kb - 4 * s.k0;
+      for (int kt = s.k0; kt < s.k1; ++kt) {
+        if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
+          report_failure(p, abort_ptr, kStatusScaleTimeout);
+          ok = false;
+          break;
+        }
+        const int atoms = min(4, atoms_left);
+        if (atoms == 4) {
+          uint4 va[4];
+          uint4 vb[4][Cfg::SFB_BLOCKS];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            va[j] = ld_shared_v4(sf_smem + 512 * j + row_off);
+#pragma unroll
+            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+              vb[j][i] = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 * i + 512 * j + row_off);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            tmem_store_4(t_sf + 4 * j, va[j]);
+#pragma unroll
+            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+              tmem_store_4(t_sf + 16 + j * Cfg::SFB_COLS + 4 * i, vb[j][i]);
+            }
+          }
+        } else {
+          for (int j = 0; j < atoms; ++j) {
+            tmem_store_4(t_sf + 4 * j, ld_shared_v4(sf_smem + 512 * j + row_off));
+#pragma unroll
+            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+              tmem_store_4(t_sf + 16 + j * Cfg::SFB_COLS + 4 * i,
+                           ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 * i + 512 * j + row_off));
+            }
+          }
+        }
+        tmem_store_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(scales0 + 8 * stage);
+        atoms_left -= 4;
+        sf_smem += Cfg::STAGE_BYTES;
+        t_sf += Cfg::SF_STAGE_COLS;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+          sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
+          t_sf = tmem_base + lane_base + Cfg::SF_COL;
+        }
+      }
+    }
+  } else if (warp >= 2) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may read
     const int row = quarter * 32 + lane;
@@ -565,14 +688,13 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           tmem_load_wait();
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
+            if (NVFP4_PROBE_FLAG(p, 7)) break;
             ws[(c * 8 + q) * 128 + row] =
                 make_float4(__uint_as_float(r1[4 * q]), __uint_as_float(r1[4 * q + 1]),
                             __uint_as_float(r1[4 * q + 2]), __uint_as_float(r1[4 * q + 3]));
           }
         }
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bar_acc_empty[acc]));
-        __threadfence();
+        if (!NVFP4_PROBE_FLAG(p, 9)) __threadfence();
         named_barrier_sync(1, 128);
         const long long unit_last = s.tile_unit0 + pd.k_tiles - 1;
         const long long first_cta = ((s.tile_unit0 + 1) * grid - 1) / p.total_units;
@@ -596,34 +718,26 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
               s1[i] = 0.0f;
               s2[i] = 0.0f;
             }
-#pragma unroll 2
-            for (long long b = first_cta; b <= last_cta; ++b) {
-              const long long b_start = p.total_units * b / grid;
-              const long long slot = 2 * b + (b_start < s.tile_unit0 ? 1 : 0);
-              const float4* src = reinterpret_cast<const float4*>(p.partials + slot * p.slot_floats);
-              float4 t1[8];
-              float4 t2[8];
+            // Partials are added in segment order, so the sum does not depend on which
+            // CTA arrives last: the segments before this CTA's from the workspace, its
+            // own straight from tensor memory (it is still there), then the rest.
+            const long long stop_before = NVFP4_PROBE_FLAG(p, 8) ? first_cta - 1 : cta - 1;
+            const long long stop_after = NVFP4_PROBE_FLAG(p, 8) ? cta : last_cta;
+            add_partials<Cfg>(p, s1, s2, first_cta, stop_before, s.tile_unit0, grid, c, row);
+            {
+              uint32_t own[32];
+              tmem_load_32(taddr + c * 32, own);
+              tmem_load_wait();
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                t1[q] = __ldcg(src + (c * 8 + q) * 128 + row);
-                if constexpr (Cfg::DUAL) {
-                  t2[q] = __ldcg(src + (Cfg::OUT_BN / 4 + c * 8 + q) * 128 + row);
-                }
-              }
+              for (int i = 0; i < 32; ++i) s1[i] += __uint_as_float(own[i]);
+              if constexpr (Cfg::DUAL) {
+                tmem_load_32(taddr + Cfg::OUT_BN + c * 32, own);
+                tmem_load_wait();
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                s1[4 * q + 0] += t1[q].x;
-                s1[4 * q + 1] += t1[q].y;
-                s1[4 * q + 2] += t1[q].z;
-                s1[4 * q + 3] += t1[q].w;
-                if constexpr (Cfg::DUAL) {
-                  s2[4 * q + 0] += t2[q].x;
-                  s2[4 * q + 1] += t2[q].y;
-                  s2[4 * q + 2] += t2[q].z;
-                  s2[4 * q + 3] += t2[q].w;
-                }
+                for (int i = 0; i < 32; ++i) s2[i] += __uint_as_float(own[i]);
               }
             }
+            add_partials<Cfg>(p, s1, s2, cta + 1, stop_after, s.tile_unit0, grid, c, row);
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -636,6 +750,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
           }
         }
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_acc_empty[acc]));
       }
       if (++acc == ACC_BUFS) {
         acc = 0;

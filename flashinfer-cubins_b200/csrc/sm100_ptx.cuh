@@ -223,8 +223,40 @@ __device__ __forceinline__ void tmem_load_32(uint32_t addr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// Warp-collective: four 32-bit columns of this thread's lane from registers.
+__device__ __forceinline__ void tmem_store_4(uint32_t addr, uint4 v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void tmem_load_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Programmatic dependent launch: `grid_dependency_wait` blocks until the preceding
+// kernel in the stream has completed and its writes are visible (a no-op when the
+// kernel was not launched with programmatic stream serialization);
+// `grid_launch_dependents` lets the next kernel start launching while this one runs.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {

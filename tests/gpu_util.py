@@ -40,10 +40,11 @@ def assert_matches_oracle(actual: torch.Tensor, expected: np.ndarray, name: str,
                                    rtol=rtol, atol=atol, err_msg=name)
 
 
-def integer_scaled(case) -> bool:
+def integer_scaled(case, default=None) -> bool:
     """Cases whose FP32 sums are exact in any order (integer scales, power-of-two or
-    unit alpha), so the kernel must equal the oracle bit for bit."""
-    scales = case.params.get("scales")
+    unit alpha), so the kernel must equal the oracle bit for bit. ``default`` is the
+    workload's scale distribution when the case names none."""
+    scales = case.params.get("scales", default)
     alpha = case.params.get("alpha", 1.0)
     return scales in ("int0_3", "int1_2") and alpha in (1.0, 0.015625)
 

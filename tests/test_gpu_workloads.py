@@ -47,8 +47,8 @@ def check_prepared(workload, case, inputs, before, ref):
 
 def oracle_check(workload, case, inputs, out):
     name = f"{workload.name}/{case.name}"
-    exact = integer_scaled(case) or (
-        case.params.get("scales") is None and workload.name in ("nvfp4_gemm", "nvfp4_group_gemm"))
+    default = {"nvfp4_gemm": "int0_3", "nvfp4_group_gemm": "int1_2"}.get(workload.name)
+    exact = integer_scaled(case, default)
     if workload.name == "nvfp4_gemm":
         assert_matches_oracle(out[0], oracle_dense(inputs), name, exact and case.params.get("alpha", 1.0) == 1.0)
     elif workload.name == "nvfp4_dual_gemm_gemm":
@@ -165,8 +165,8 @@ def test_every_tile_width_and_schedule(tile_n, schedule):
     workload = get_workload("nvfp4_gemm")(None, device="cuda")
     dev = torch.device("cuda:0")
     stream = torch.cuda.current_stream().cuda_stream
-    cases = [c for c in workload.get_cases() if c.suite == "smoke" and integer_scaled(c)
-             and c.params.get("alpha", 1.0) == 1.0]
+    cases = [c for c in workload.get_cases() if c.suite == "smoke"
+             and integer_scaled(c, "int0_3") and c.params.get("alpha", 1.0) == 1.0]
     assert len(cases) >= 5
     for case in cases:
         inputs = workload.get_inputs(case)
