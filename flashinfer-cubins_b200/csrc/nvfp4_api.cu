@@ -172,8 +172,9 @@ struct nvfp4_plan {
   int sm_count = 0;
   int tile_n = 128;   // MMA N
   int out_tile_n = 128;
-  int schedule = 1;   // 1 data parallel, 2 stream-K
+  int schedule = 1;   // 1 data parallel, 2 stream-K, 3 cluster split-K
   int ctas = 1;
+  int split = 1;      // cluster size of schedule 3
   KernelChoice kernel{};
   std::vector<ProblemDesc> problems;  // pointers filled at launch / bind
   long long total_tiles = 0, total_units = 0;
@@ -216,16 +217,43 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
   int ctas = config != nullptr && config->ctas > 0 ? config->ctas : env_int("NVFP4_CTAS", 0);
   if (ctas > sms) ctas = sms;
 
-  if (schedule != 1 && schedule != 2) {
-    if (tiles >= sms) {
-      const long long waves = (tiles + sms - 1) / sms;
-      const double efficiency = static_cast<double>(tiles) / static_cast<double>(waves * sms);
-      schedule = efficiency >= 0.9 ? 1 : 2;
-    } else {
-      // Fewer tiles than SMs: split K while every CTA keeps at least four k-tiles.
-      const long long by_units = units / 4;
-      schedule = by_units > tiles ? 2 : 1;
+  // Cluster split-K (dense and dual GEMM): `split` CTAs of a cluster share a tile's K and
+  // reduce through peer shared memory. Candidates are the power-of-two cluster sizes
+  // that keep at least one k-tile per CTA, own 32-column multiples, and fit the SMs.
+  int split = 1;
+  if (plan->kind != kGrouped && plan->problems.size() == 1 && tiles < sms) {
+    const int k_tiles = plan->problems[0].k_tiles;
+    const int forced = env_int("NVFP4_SPLIT", 0);
+    for (int s = 2; s <= 8; s *= 2) {
+      if (tiles * s > sms || s > k_tiles || (plan->out_tile_n / s) % 32 != 0) break;
+      if (forced == 0 || s <= forced) split = s;
     }
+  }
+  if (schedule == 3 && split < 2) schedule = 0;
+  if (schedule != 1 && schedule != 2 && schedule != 3) {
+    // Pick the schedule with the smallest estimated time. Measured on B200: a k-tile step
+    // of one CTA takes about 0.5 us with 128-column tiles (0.8 us with 256) once the
+    // pipeline is full, whatever the schedule; finishing split tiles through the
+    // workspace costs about 8 us at the end of the kernel, through a cluster's shared
+    // memory about 2.5 us.
+    const double step_us = plan->tile_n > 128 ? 0.8 : 0.5;
+    const double k_per_tile = static_cast<double>(units) / static_cast<double>(tiles);
+    const long long waves = (tiles + sms - 1) / sms;
+    const double t_whole = static_cast<double>(waves) * k_per_tile * step_us;
+    const long long sk_ctas = std::min<long long>(sms, std::max<long long>(tiles, units / 4));
+    const double t_stream = static_cast<double>(units) / static_cast<double>(sk_ctas) * step_us + 8.0;
+    double t_cluster = 1e30;
+    if (split >= 2) {
+      const int k_tiles = plan->problems[0].k_tiles;
+      t_cluster = static_cast<double>((k_tiles + split - 1) / split) * step_us + 2.5;
+    }
+    schedule = 1;
+    double best = t_whole;
+    if (t_stream < best && units > tiles) {
+      schedule = 2;
+      best = t_stream;
+    }
+    if (t_cluster < best) schedule = 3;
   }
   if (ctas <= 0) {
     if (schedule == 1) {
@@ -237,9 +265,11 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
   }
   if (schedule == 1) ctas = static_cast<int>(std::min<long long>(ctas, tiles));
   if (schedule == 2) ctas = static_cast<int>(std::min<long long>(ctas, units));
+  if (schedule == 3) ctas = static_cast<int>(tiles) * split;
   if (ctas < 1) ctas = 1;
   plan->schedule = schedule;
   plan->ctas = ctas;
+  plan->split = schedule == 3 ? split : 1;
 
   // Workspace: [status 256 B][counters][group table][group maps][partials].
   size_t off = 256;
@@ -258,6 +288,7 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
   if (schedule == 2) {
     off += static_cast<size_t>(2) * ctas * plan->slot_floats * sizeof(float);
   }
+  // (Cluster split-K exchanges partials through shared memory: no slots.)
   plan->ws_bytes = off;
 }
 
@@ -327,7 +358,8 @@ void fill_common_params(const nvfp4_plan* plan, KernelParams& kp, void* workspac
   kp.total_units = plan->total_units;
   kp.slot_floats = plan->slot_floats;
   kp.num_problems = static_cast<int>(plan->problems.size());
-  kp.mode = plan->schedule == 2 ? kModeStreamK : kModeDataParallel;
+  kp.mode = plan->schedule == 1 ? kModeDataParallel : kModeStreamK;
+  kp.split = plan->split;
   bool streams = true;
   for (const ProblemDesc& pd : plan->problems) {
     if (pd.tiles_m > 1) streams = false;
@@ -344,16 +376,27 @@ int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream) {
   // harness/workloads/nvfp4_gemm.py:143-147): this kernel's prologue may overlap the
   // tail of the kernel before it; it waits on the device before touching global memory.
   static const bool use_pdl = env_int("NVFP4_PDL", 1) != 0;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attribute[2];
+  int attributes = 0;
+  if (use_pdl) {
+    attribute[attributes].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[attributes].val.programmaticStreamSerializationAllowed = 1;
+    ++attributes;
+  }
+  if (plan->split > 1) {
+    attribute[attributes].id = cudaLaunchAttributeClusterDimension;
+    attribute[attributes].val.clusterDim.x = static_cast<unsigned int>(plan->split);
+    attribute[attributes].val.clusterDim.y = 1;
+    attribute[attributes].val.clusterDim.z = 1;
+    ++attributes;
+  }
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(plan->ctas);
   config.blockDim = dim3(plan->kernel.threads);
   config.dynamicSmemBytes = plan->kernel.smem_bytes;
   config.stream = static_cast<cudaStream_t>(stream);
   config.attrs = attribute;
-  config.numAttrs = use_pdl ? 1 : 0;
+  config.numAttrs = attributes;
   CUDA_TRY(cudaLaunchKernelExC(&config, reinterpret_cast<const void*>(plan->kernel.fn), args));
   return 0;
 }

@@ -65,6 +65,7 @@ enum : int {
   kStatusMmaAccumTimeout = 3,
   kStatusEpilogueTimeout = 4,
   kStatusScaleTimeout = 5,
+  kStatusClusterTimeout = 6,
 };
 
 struct alignas(64) KernelParams {
@@ -82,6 +83,9 @@ struct alignas(64) KernelParams {
   int mode;
   int b_streams;  // B is read once: mark its loads evict-first in L2
   int probe;      // timing experiments only; ignored unless built with NVFP4_PROBE
+  int split;      // > 1: CTAs of a cluster of this size split each tile's K (stream-K mode
+                  // with grid = tiles * split) and reduce through peer shared memory
+  int pad0, pad1, pad2;
 };
 
 // Timing experiments (results become wrong): compiled out of the product build.
@@ -318,6 +322,110 @@ __device__ __forceinline__ void add_partials(const KernelParams& p, float (&s1)[
   }
 }
 
+// Split-K inside a cluster: the `split` CTAs of a cluster hold partial sums of the same
+// tile (one K slice each) in tensor memory. CTA r owns output columns
+// [r * W, (r + 1) * W), W = tile width / split. Every CTA sends the columns it does not
+// own to their owners' shared memory (the pipeline stages, free once the mainloop is
+// done: each CTA first tells its peers so), then adds what it received to its own
+// columns in rank order and stores them. No global workspace, no atomics; the result
+// does not depend on timing. Called by the 128 epilogue threads.
+template <class Cfg>
+__device__ __forceinline__ void cluster_reduce(const KernelParams& p, const ProblemDesc& pd,
+                                               const Segment& s, uint32_t taddr,
+                                               uint32_t staging, uint32_t bar_ready,
+                                               uint32_t bar_data, volatile int* abort_ptr,
+                                               float alpha, int row, int epi_tid, int grow,
+                                               typename Cfg::OutT* out_row) {
+  using OutT = typename Cfg::OutT;
+  // The dual GEMM keeps two accumulators side by side (h1 in columns [0, OUT_BN), h2 in
+  // [OUT_BN, 2 * OUT_BN)); an owner of output columns needs both halves of them.
+  constexpr int HALVES = Cfg::DUAL ? 2 : 1;
+  const int split = p.split;
+  const int rank = static_cast<int>(cluster_cta_rank());
+  const int width = Cfg::OUT_BN / split;  // output columns per owner, a multiple of 32
+  const int chunks = width / 32;
+  // 1. My pipeline memory is free: tell every peer it may write into it.
+  if (epi_tid == 0) {
+    for (int peer = 0; peer < split; ++peer) {
+      if (peer != rank) mbar_arrive_cluster(cluster_map_shared(bar_ready, peer));
+    }
+  }
+  // 2. Wait until every peer has said the same.
+  if (!mbar_wait_cluster(bar_ready, 0, abort_ptr)) {
+    report_failure(p, abort_ptr, kStatusClusterTimeout);
+    return;
+  }
+  // 3. Send: slot index at the receiver = my rank among its peers.
+  for (int peer = 0; peer < split; ++peer) {
+    if (peer == rank) continue;
+    const int slot = rank < peer ? rank : rank - 1;
+    const uint32_t remote = cluster_map_shared(staging, peer);
+#pragma unroll 1
+    for (int c = 0; c < chunks; ++c) {
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        uint32_t r1[32];
+        tmem_load_32(taddr + h * Cfg::OUT_BN + peer * width + c * 32, r1);
+        tmem_load_wait();
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const uint32_t index = (((slot * chunks + c) * HALVES + h) * 8 + q) * 128 + row;
+          st_cluster_v4(remote + index * 16u,
+                        make_float4(__uint_as_float(r1[4 * q]), __uint_as_float(r1[4 * q + 1]),
+                                    __uint_as_float(r1[4 * q + 2]), __uint_as_float(r1[4 * q + 3])));
+        }
+      }
+    }
+    mbar_arrive_cluster(cluster_map_shared(bar_data, peer));
+  }
+  // 4. Wait for every peer's columns.
+  if (!mbar_wait_cluster(bar_data, 0, abort_ptr)) {
+    report_failure(p, abort_ptr, kStatusClusterTimeout);
+    return;
+  }
+  // 5. Own columns: add in rank order, finish, store.
+  const int n0 = s.n_tile * Cfg::OUT_BN + rank * width;
+#pragma unroll 1
+  for (int c = 0; c < chunks; ++c) {
+    float sum[HALVES][32];
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h) {
+      uint32_t own[32];
+      tmem_load_32(taddr + h * Cfg::OUT_BN + rank * width + c * 32, own);
+      tmem_load_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sum[h][i] = 0.0f;
+      for (int src = 0; src < split; ++src) {
+        if (src == rank) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sum[h][i] += __uint_as_float(own[i]);
+        } else {
+          const int slot = src < rank ? src : src - 1;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t index = (((slot * chunks + c) * HALVES + h) * 8 + q) * 128 + row;
+            const uint4 t = ld_shared_v4(staging + index * 16u);
+            sum[h][4 * q + 0] += __uint_as_float(t.x);
+            sum[h][4 * q + 1] += __uint_as_float(t.y);
+            sum[h][4 * q + 2] += __uint_as_float(t.z);
+            sum[h][4 * q + 3] += __uint_as_float(t.w);
+          }
+        }
+      }
+    }
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if constexpr (Cfg::DUAL) {
+        v[i] = silu_f32(sum[0][i] * alpha) * (sum[HALVES - 1][i] * alpha);
+      } else {
+        v[i] = sum[0][i] * alpha;
+      }
+    }
+    if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+  }
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
@@ -333,6 +441,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   __shared__ alignas(8) uint64_t bar_acc_empty[ACC_BUFS];
   __shared__ alignas(8) uint64_t bar_sf_full[STAGES];  // a stage's scale atoms have landed
   __shared__ alignas(8) uint64_t bar_scales[STAGES];   // ... and are in tensor memory
+  __shared__ alignas(8) uint64_t bar_peer_ready;  // every peer's pipeline memory is free
+  __shared__ alignas(8) uint64_t bar_peer_data;   // every peer's partial columns have arrived
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int epi_last_flag;
@@ -354,6 +464,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       mbar_init(smem_u32(&bar_acc_full[a]), 1);
       mbar_init(smem_u32(&bar_acc_empty[a]), 128);
     }
+    const uint32_t peers = p.split > 1 ? static_cast<uint32_t>(p.split - 1) : 1u;
+    mbar_init(smem_u32(&bar_peer_ready), peers);
+    mbar_init(smem_u32(&bar_peer_data), 128u * peers);
     abort_flag = 0;
     epi_last_flag = 0;
     mbar_fence_init();
@@ -363,6 +476,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   }
   tc_fence_before_sync();
   __syncthreads();
+  // Peers arrive on this CTA's barriers, so they must be initialised cluster-wide.
+  if (p.split > 1) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
@@ -675,6 +790,12 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           }
           if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
         }
+      } else if (p.split > 1) {
+        cluster_reduce<Cfg>(p, pd, s, taddr, smem_base, smem_u32(&bar_peer_ready),
+                            smem_u32(&bar_peer_data), abort_ptr, alpha, row, epi_tid, grow,
+                            out_row);
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bar_acc_empty[acc]));
       } else {
         // Partial sum of this segment -> workspace slot as float4 [column / 4][row], so
         // that the 32 rows of a warp write (and later read) 512 contiguous bytes.
@@ -762,6 +883,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
 
   tc_fence_before_sync();
   __syncthreads();
+  // No CTA of a cluster leaves while a peer could still write into its shared memory.
+  if (p.split > 1) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
     __syncwarp();

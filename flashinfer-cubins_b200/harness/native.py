@@ -31,7 +31,7 @@ E_NOT_BOUND = -6
 OUT_F16 = 0
 OUT_F32 = 1
 
-SCHEDULE_NAMES = {1: "data_parallel", 2: "stream_k"}
+SCHEDULE_NAMES = {1: "data_parallel", 2: "stream_k", 3: "cluster_split_k"}
 
 
 class NativeError(RuntimeError):

@@ -48,7 +48,9 @@ extern "C" {
 /* Optional tuning overrides; zero/negative fields mean "choose automatically". */
 typedef struct nvfp4_config {
   int tile_n;   /* 64, 128 or 256 */
-  int schedule; /* 1 = data parallel (whole tiles), 2 = stream-K (split along K) */
+  int schedule; /* 1 = data parallel (whole tiles), 2 = stream-K (split along K, partials
+                   through the workspace), 3 = cluster split-K (partials through peer
+                   shared memory; dense and dual GEMM with fewer tiles than SMs only) */
   int ctas;     /* persistent grid size, at most the SM count */
 } nvfp4_config;
 
@@ -56,7 +58,7 @@ typedef struct nvfp4_config {
 typedef struct nvfp4_plan_info {
   int tile_m, tile_n, tile_k;
   int stages;
-  int schedule; /* 1 data parallel, 2 stream-K */
+  int schedule; /* 1 data parallel, 2 stream-K, 3 cluster split-K */
   int ctas;
   int threads;
   int smem_bytes;

@@ -157,11 +157,13 @@ def test_golden_fixtures_through_the_c_abi():
 
 
 @pytest.mark.parametrize("tile_n", (64, 128, 256))
-@pytest.mark.parametrize("schedule", (1, 2))
+@pytest.mark.parametrize("schedule", (1, 2, 3))
 def test_every_tile_width_and_schedule(tile_n, schedule):
-    """The dense kernel's three tile widths under both schedules (whole tiles and
-    stream-K with its fix-up) on shapes with partial tiles, batches and a K tail; integer
-    scales, so results must equal the oracle bit for bit however K is split."""
+    """The dense kernel's three tile widths under every schedule (whole tiles, stream-K
+    with its workspace fix-up, cluster split-K with its shared-memory reduction; a plan
+    falls back to another schedule when the requested one does not apply) on shapes with
+    partial tiles, batches and a K tail; integer scales, so results must equal the oracle
+    bit for bit however K is split."""
     workload = get_workload("nvfp4_gemm")(None, device="cuda")
     dev = torch.device("cuda:0")
     stream = torch.cuda.current_stream().cuda_stream
@@ -186,6 +188,68 @@ def test_every_tile_width_and_schedule(tile_n, schedule):
             assert plan.status(ws.data_ptr(), stream) == 0
             assert_matches_oracle(d.permute(1, 2, 0), oracle_dense(inputs),
                                   f"{case.name}/bn{tile_n}/{info['schedule']}", True)
+        plan.destroy()
+
+
+@pytest.mark.parametrize("m,n,k,l,tile_n", [(128, 256, 4096, 1, 128), (300, 264, 2080, 2, 128),
+                                             (128, 1024, 8192, 1, 256), (17, 520, 4096, 1, 64),
+                                             (128, 7168, 2048, 1, 128)])
+def test_cluster_split_k(m, n, k, l, tile_n):  # noqa: E741
+    """Few tiles and a long K: the plan splits each tile's K over a thread-block cluster
+    and reduces through peer shared memory. Unit-range scales: the result must match the
+    torch reference within the tolerance, and two launches must agree bit for bit."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    for scales, exact in (("int0_3", True), ("uniform", False)):
+        case = CaseSpec("cluster", {"m": m, "n": n, "k": k, "l": l, "scales": scales}, 21)
+        inputs = workload.get_inputs(case)
+        a, b, sfa, sfb, alpha = inputs
+        plan = native.Plan.dense(0, native.OUT_F16, m, n, k, l, tile_n=tile_n, schedule=3)
+        info = plan.info()
+        assert info["schedule"] == "cluster_split_k", info
+        assert info["ctas"] % info["tiles"] == 0 and info["ctas"] > info["tiles"]
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        outs = []
+        for _ in range(2):
+            d = torch.full((l, m, n), float("nan"), dtype=torch.float16, device=dev)
+            plan.launch_dense(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                              alpha.data_ptr(), d.data_ptr(), ws.data_ptr(), stream)
+            assert plan.status(ws.data_ptr(), stream) == 0
+            outs.append(d)
+        assert torch.equal(outs[0], outs[1])
+        (ref,) = workload.get_reference(inputs)
+        if exact:
+            assert torch.equal(outs[0].permute(1, 2, 0), ref)
+        else:
+            torch.testing.assert_close(outs[0].permute(1, 2, 0), ref, rtol=1e-3, atol=1e-3)
+        plan.destroy()
+
+
+@pytest.mark.parametrize("schedule", (1, 2, 3))
+def test_dual_gemm_under_every_schedule(schedule):
+    """The fused dual GEMM with whole tiles, the workspace fix-up and the cluster
+    reduction (both accumulator halves travel to the owner of the output columns)."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_dual_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    for m, n, k, l in ((200, 264, 2080, 1), (256, 512, 7168, 1), (130, 136, 1024, 2)):  # noqa: E741
+        case = CaseSpec("dual", {"m": m, "n": n, "k": k, "l": l, "alpha": 0.25}, 31)
+        inputs = workload.get_inputs(case)
+        (ref,) = workload.get_reference(inputs)
+        plan = native.Plan.dual(0, m, n, k, l, schedule=schedule)
+        info = plan.info()
+        if schedule == 3:
+            assert info["schedule"] == "cluster_split_k", info
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        d = torch.full((l, m, n), float("nan"), dtype=torch.float16, device=dev)
+        plan.launch_dual(*(t.data_ptr() for t in inputs), d.data_ptr(), ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        torch.testing.assert_close(d.permute(1, 2, 0), ref, rtol=1e-3, atol=1e-3)
         plan.destroy()
 
 
