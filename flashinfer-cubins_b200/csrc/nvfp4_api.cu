@@ -595,6 +595,74 @@ int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void
   return launch_plan(plan, plan->params, stream);
 }
 
+// ---------------------------------------------------------------------------------------
+// Dense launch for callers that cannot hand over a workspace.
+//
+// Some hosts of this library are not allowed to allocate device memory at the point where
+// they call it: a runtime that has given all of HBM to its own pool, a plugin that runs
+// under an allocator it does not control, a serving loop that forbids cudaMalloc on its
+// hot path because the call synchronises the device. For them the scratch that the
+// split-K schedules need lives in the array below instead of in a caller buffer. The
+// array is part of the loaded module, so every GPU that loads the library holds these
+// bytes until the process exits.
+// ---------------------------------------------------------------------------------------
+
+constexpr size_t kStaticScratchBytes = 24u << 20;  // 24 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_address[kMaxDevices] = {};
+
+// Device address of g_static_scratch on `device`. In host code the array's name is only
+// a handle for the runtime, never a device pointer, so the address is looked up once per
+// device (with that device current) and remembered.
+int static_scratch_address(int device, void** out) {
+  if (device < 0 || device >= kMaxDevices) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "device %d out of range", device);
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_address[device] == nullptr) {
+    DeviceGuard guard;
+    CUDA_TRY(guard.enter(device));
+    void* address = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&address, g_static_scratch));
+    if (address == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "no address for the scratch array");
+    g_scratch_address[device] = address;
+  }
+  *out = g_scratch_address[device];
+  return 0;
+}
+
+}  // namespace
+
+int nvfp4_gemm_launch_static(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                             const void* sfb, const float* alpha, void* d, void* stream) {
+  if (plan == nullptr || plan->kind != kDense) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dense GEMM plan");
+  }
+  if (plan->ws_bytes > kStaticScratchBytes) {
+    return fail(NVFP4_E_SCRATCH_TOO_LARGE,
+                "this plan needs %zu bytes of scratch; the built-in array holds %zu. Use "
+                "nvfp4_gemm_launch with a caller workspace, or a plan with fewer CTAs",
+                plan->ws_bytes, kStaticScratchBytes);
+  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(plan->device, &scratch)) return rc;
+  {
+    // The array keeps whatever the previous call (of any plan) left in it; the status
+    // word and this plan's tile counters must start at zero.
+    DeviceGuard guard;
+    CUDA_TRY(guard.enter(plan->device));
+    CUDA_TRY(cudaMemsetAsync(scratch, 0, plan->off_table, static_cast<cudaStream_t>(stream)));
+  }
+  return nvfp4_gemm_launch(plan, a, b, sfa, sfb, alpha, d, scratch, stream);
+}
+
+size_t nvfp4_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
 int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
                            const void* sfa, const void* sfb1, const void* sfb2,
                            const float* alpha, void* d, void* workspace, void* stream) {

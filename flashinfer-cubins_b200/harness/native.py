@@ -27,6 +27,7 @@ E_MISALIGNED = -3
 E_UNSUPPORTED_DEVICE = -4
 E_DEVICE_TIMEOUT = -5
 E_NOT_BOUND = -6
+E_SCRATCH_TOO_LARGE = -7
 
 OUT_F16 = 0
 OUT_F32 = 1
@@ -87,6 +88,8 @@ _PROTOTYPES = {
     "nvfp4_plan_init_workspace": (ctypes.c_int, [_P, _P, _P]),
     "nvfp4_plan_info_get": (ctypes.c_int, [_P, ctypes.POINTER(PlanInfo)]),
     "nvfp4_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "nvfp4_gemm_launch_static": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
+    "nvfp4_static_scratch_bytes": (ctypes.c_size_t, []),
     "nvfp4_dual_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_group_gemm_bind": (
         ctypes.c_int,
@@ -214,6 +217,12 @@ class Plan:
 
     def launch_dense(self, a, b, sfa, sfb, alpha, d, workspace, stream) -> None:
         check(load().nvfp4_gemm_launch(self.handle, a, b, sfa, sfb, alpha, d, workspace, stream))
+
+    def launch_dense_static(self, a, b, sfa, sfb, alpha, d, stream) -> None:
+        """Dense launch on the library's built-in scratch array: for callers that may
+        not allocate a workspace. Raises ``ValueError`` if the plan needs more scratch
+        than the array holds."""
+        check(load().nvfp4_gemm_launch_static(self.handle, a, b, sfa, sfb, alpha, d, stream))
 
     def launch_dual(self, a, b1, b2, sfa, sfb1, sfb2, alpha, d, workspace, stream) -> None:
         check(load().nvfp4_dual_gemm_launch(

@@ -40,6 +40,7 @@ extern "C" {
 #define NVFP4_E_UNSUPPORTED_DEVICE (-4) /* not compute capability 10.0 */
 #define NVFP4_E_DEVICE_TIMEOUT (-5)    /* a kernel abandoned a bounded wait (status word) */
 #define NVFP4_E_NOT_BOUND (-6)         /* grouped launch before nvfp4_group_gemm_bind */
+#define NVFP4_E_SCRATCH_TOO_LARGE (-7) /* plan needs more than the built-in scratch array */
 
 /* Output/element kinds of a plan. */
 #define NVFP4_OUT_F16 0 /* nvfp4_gemm: FP16 D (harness/workloads/nvfp4_gemm.py:511-530) */
@@ -119,6 +120,25 @@ int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info);
 int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                       const void* sfb, const float* alpha, void* d, void* workspace,
                       void* stream);
+
+/* The dense launch for callers that must not allocate device memory where they call
+ * this library (a runtime whose own pool owns all of HBM, a plugin under a foreign
+ * allocator, a hot path that bans cudaMalloc because it synchronises the device). It has
+ * no counterpart in the reference. Same operands as nvfp4_gemm_launch, but the scratch a
+ * split-K schedule needs is a 24 MiB array inside the library
+ * (nvfp4_static_scratch_bytes()), which every GPU that loads the library holds until the
+ * process exits. A plan whose nvfp4_plan_workspace_bytes() exceeds that is refused with
+ * NVFP4_E_SCRATCH_TOO_LARGE; nothing is launched. The call allocates nothing: it zeroes
+ * the status word and the plan's tile counters in the array (stream-ordered), then
+ * launches. The first call on a device also looks the array's address up; make that
+ * first call before any stream capture begins. All calls on a device share the one
+ * array, so two such launches that can overlap on the GPU (different streams, no
+ * ordering between them) race; nvfp4_plan_status is not meaningful for this array. */
+int nvfp4_gemm_launch_static(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                             const void* sfb, const float* alpha, void* d, void* stream);
+
+/* Size in bytes of the built-in scratch array used by nvfp4_gemm_launch_static. */
+size_t nvfp4_static_scratch_bytes(void);
 
 /* One fused dual-GEMM launch (see nvfp4_dual_gemm_plan_create). */
 int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
