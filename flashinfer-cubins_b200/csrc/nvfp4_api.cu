@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 
 #include "nvfp4_gemm_kernel.cuh"
+#include "nvfp4_gemm_pair_kernel.cuh"
 #include "nvfp4_glue_kernels.cuh"
 
 using namespace nvfp4;
@@ -136,6 +137,11 @@ KernelChoice make_choice() {
   return KernelChoice{&nvfp4_gemm_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::STAGES, Cfg::THREADS};
 }
 
+template <class Cfg>
+KernelChoice make_pair_choice() {
+  return KernelChoice{&nvfp4_gemm_pair_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::STAGES, Cfg::THREADS};
+}
+
 // kind, out_kind, tile_n -> kernel instantiation. Returns fn == nullptr if absent.
 KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
   if (kind == kDual) {
@@ -175,6 +181,7 @@ struct nvfp4_plan {
   int schedule = 1;   // 1 data parallel, 2 stream-K, 3 cluster split-K
   int ctas = 1;
   int split = 1;      // cluster size of schedule 3
+  bool pair = false;  // 2-CTA kernel: 256 x 256 tiles, one cluster of two CTAs per tile
   KernelChoice kernel{};
   std::vector<ProblemDesc> problems;  // pointers filled at launch / bind
   long long total_tiles = 0, total_units = 0;
@@ -335,7 +342,12 @@ int default_tile_n(const nvfp4_config* config, int fallback) {
 }
 
 int prepare_kernel(nvfp4_plan* plan) {
-  plan->kernel = select_kernel(plan->kind, plan->out_kind, plan->tile_n);
+  if (plan->pair) {
+    plan->kernel = plan->out_kind == NVFP4_OUT_F16 ? make_pair_choice<PairConfig<__half>>()
+                                                   : make_pair_choice<PairConfig<float>>();
+  } else {
+    plan->kernel = select_kernel(plan->kind, plan->out_kind, plan->tile_n);
+  }
   if (plan->kernel.fn == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "no kernel for tile_n=%d", plan->tile_n);
   }
@@ -447,10 +459,42 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
         static_cast<long long>(ceil_div(m, 128)) * ceil_div(n, 256) * l;
     plan->tile_n = default_tile_n(config, wide_tiles >= 2ll * sms ? 256 : 128);
     plan->out_tile_n = plan->tile_n;
+    // Pairs of CTAs on 256 x 256 tiles (tcgen05.mma.cta_group::2) once there are at least
+    // two such tiles per pair of SMs: each CTA then loads only half of every B tile.
+    const long long pair_tiles = static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, 256) * l;
+    int want_pair = config != nullptr ? config->pair : 0;
+    if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
+    const bool explicit_tile = (config != nullptr && config->tile_n > 0) ||
+                               env_int("NVFP4_TILE_N", 0) > 0;
+    plan->pair = want_pair > 0 || (want_pair == 0 && !explicit_tile && pair_tiles >= sms);
+    if (plan->pair) {
+      plan->tile_n = 256;
+      plan->out_tile_n = 256;
+    }
   }
   plan->problems.resize(1);
   fill_problem(&plan->problems[0], m, n, k, l, plan->out_tile_n);
-  finish_schedule(plan, config);
+  if (plan->pair) {
+    // One schedule only: pair tiles dealt round-robin to the pairs of SMs.
+    ProblemDesc& pd = plan->problems[0];
+    const long long pair_tiles = static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, 256) * l;
+    pd.tiles_m = ceil_div(m, 256);
+    pd.tile_begin = 0;
+    pd.unit_begin = 0;
+    plan->total_tiles = pair_tiles;
+    plan->total_units = pair_tiles * pd.k_tiles;
+    plan->schedule = 1;
+    plan->split = 2;
+    plan->ctas = 2 * static_cast<int>(std::min<long long>(sms / 2, pair_tiles));
+    plan->off_counters = 256;
+    plan->off_table = 512;
+    plan->off_maps = 512;
+    plan->off_partials = 512;
+    plan->slot_floats = 0;
+    plan->ws_bytes = 512;
+  } else {
+    finish_schedule(plan, config);
+  }
   if (int rc = prepare_kernel(plan)) {
     delete plan;
     return rc;
@@ -545,7 +589,7 @@ int nvfp4_plan_init_workspace(const nvfp4_plan* plan, void* workspace, void* str
 
 int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info) {
   if (plan == nullptr || info == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null argument");
-  info->tile_m = 128;
+  info->tile_m = plan->pair ? 256 : 128;
   info->tile_n = plan->out_tile_n;
   info->tile_k = 256;
   info->stages = plan->kernel.stages;
@@ -579,7 +623,10 @@ int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void
     ProblemDesc& pd = plan->problems[0];
     KernelParams& kp = plan->params;
     if (int rc = encode_operand_map(&kp.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
-    if (int rc = encode_operand_map(&kp.map_b, b, pd.n, pd.k, pd.batches, plan->tile_n)) return rc;
+    if (int rc = encode_operand_map(&kp.map_b, b, pd.n, pd.k, pd.batches,
+                                    plan->pair ? 128 : plan->tile_n)) {
+      return rc;
+    }
     kp.map_b2 = kp.map_b;
     pd.sfa = static_cast<const uint8_t*>(sfa);
     pd.sfb = static_cast<const uint8_t*>(sfb);

@@ -1,0 +1,377 @@
+// NVFP4 block-scaled GEMM for large dense problems: two CTAs on neighbouring SMs work as
+// a pair on one 256 x 256 output tile with tcgen05.mma.cta_group::2.
+//
+// Why a pair: an SM can take in about 64 bytes per clock from L2. A single CTA on a
+// 128 x 256 tile needs 54 KB per 256-wide k-tile for 512 clocks of MMA work (105 B/clk),
+// so it is bound by that intake, not by the tensor pipe. In a pair each CTA loads its own
+// 128 rows of A and only *half* of the B tile (the MMA reads both halves from the two
+// CTAs' shared memory): 38 KB per k-tile for the same 512 clocks. No cluster multicast is
+// involved: every byte a CTA needs is loaded by that CTA.
+//
+// Per CTA (320 threads, same roles as the single-CTA kernel):
+//   warp 0      TMA producer: own A rows, own half of B, own SFA atoms, all SFB atoms.
+//               The A/B copies of both CTAs complete on the *leader's* full barrier
+//               (cp.async.bulk.tensor ... .cta_group::2), which the leader arms for the
+//               bytes of both.
+//   warps 6-9   scale movers: this CTA's scale atoms -> this CTA's tensor memory; the
+//               peer's movers arrive on the leader's barrier through shared::cluster.
+//   warp 1      leader CTA only: issues the MMAs (M = 256, N = 256, K = 64 each); its
+//               tcgen05.commit is multicast to both CTAs' barriers.
+//   warps 2-5   epilogue: each CTA stores its own 128 rows of the tile.
+// Tiles are dealt round-robin to the pairs (data parallel, persistent). The accumulator
+// (256 columns) is single-buffered; 5 stages of 38 KB.
+#pragma once
+
+#include "nvfp4_gemm_kernel.cuh"
+
+namespace nvfp4 {
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+
+// Arrive once on the barrier at this shared-memory offset in every CTA of `mask` when all
+// tcgen05 operations issued so far by this thread (for the pair) have completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar),
+      "h"(mask)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t tmem_d, uint64_t desc_a,
+                                                 uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], "
+      "p;\n\t"
+      "}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
+// Tiled copy into this CTA's shared memory whose completion is counted on a barrier that
+// may live in the peer CTA of the pair (`cluster_bar` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map,
+                                                 uint32_t cluster_bar, int c0, int c1, int c2,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2),
+      "l"(policy)
+      : "memory");
+}
+
+template <typename OutT_>
+struct PairConfig {
+  using OutT = OutT_;
+  static constexpr int TILE_M = 256, TILE_N = 256;
+  static constexpr int A_BYTES = 128 * 128;       // this CTA's 128 rows x 256 E2M1
+  static constexpr int B_BYTES = 128 * 128;       // this CTA's half of the B tile
+  static constexpr int SFA_BYTES = 4 * 512;       // this CTA's rows, four k-blocks
+  static constexpr int SFB_BYTES = 2 * 4 * 512;   // all 256 B rows
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES = 5;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int SF_STAGE_COLS = 16 + 4 * 8;
+  static constexpr int SF_COL = TILE_N;  // after the accumulator's 256 columns
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int THREADS = 320;
+  static_assert(SF_COL + STAGES * SF_STAGE_COLS <= TMEM_COLS, "tensor memory exceeded");
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
+  constexpr int STAGES = Cfg::STAGES;
+  using OutT = typename Cfg::OutT;
+
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ alignas(8) uint64_t bar_full[STAGES];     // used in the leader: A/B of both CTAs
+  __shared__ alignas(8) uint64_t bar_empty[STAGES];    // each CTA: stage may be refilled
+  __shared__ alignas(8) uint64_t bar_sf_full[STAGES];  // each CTA: own scale atoms landed
+  __shared__ alignas(8) uint64_t bar_scales[STAGES];   // leader: scales of both CTAs in TMEM
+  __shared__ alignas(8) uint64_t bar_acc_full;         // each CTA: tile accumulated
+  __shared__ alignas(8) uint64_t bar_acc_empty;        // leader: both epilogues have drained
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+  const uint32_t rank = cluster_cta_rank();  // 0 = leader
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_sf_full[s]), 1);
+      mbar_init(smem_u32(&bar_scales[s]), 8);
+    }
+    mbar_init(smem_u32(&bar_acc_full), 1);
+    mbar_init(smem_u32(&bar_acc_empty), 256);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(&tmem_base_slot), Cfg::TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers and tensor memory exist before anyone uses them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_flag;
+  grid_dependency_wait();
+  grid_launch_dependents();
+
+  const ProblemDesc& pd = p.dense;
+  const int pair_tiles_m = (pd.m + 255) / 256;
+  const int pair_tiles_n = (pd.n + 255) / 256;
+  const long long tiles = static_cast<long long>(pair_tiles_m) * pair_tiles_n * pd.batches;
+  const long long pairs = gridDim.x / 2;
+  const long long first_tile = blockIdx.x / 2;
+
+  // Tile index -> (batch, m, n): bands of eight tile rows, as in the single-CTA kernel.
+  auto decode = [&](long long t, int& batch, int& m_tile, int& n_tile) {
+    const int per_batch = pair_tiles_m * pair_tiles_n;
+    batch = static_cast<int>(t / per_batch);
+    const int r = static_cast<int>(t % per_batch);
+    const int band_tiles = 8 * pair_tiles_n;
+    const int band = r / band_tiles;
+    const int in_band = r % band_tiles;
+    const int height = min(8, pair_tiles_m - band * 8);
+    m_tile = band * 8 + in_band % height;
+    n_tile = in_band / height;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      const uint64_t pol = l2_policy_evict_last();
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(&p.map_b);
+      const uint32_t leader_full0 = cluster_map_shared(smem_u32(&bar_full[0]), 0);
+      const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
+      const uint32_t empty0 = smem_u32(&bar_empty[0]);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t stage_smem = smem_base;
+      bool ok = true;
+      for (long long t = first_tile; ok && t < tiles; t += pairs) {
+        int batch, m_tile, n_tile;
+        decode(t, batch, m_tile, n_tile);
+        const int m0 = m_tile * 256 + static_cast<int>(rank) * 128;
+        const int n0 = n_tile * 256 + static_cast<int>(rank) * 128;
+        const int mb = m_tile * 2 + static_cast<int>(rank);  // this CTA's SFA atom row
+        const int nb = n_tile * 2;                            // first of the tile's SFB atom rows
+        const bool sfa_valid = mb < pd.sf_mb;
+        const uint8_t* sfa_src =
+            pd.sfa + (static_cast<long long>(batch) * pd.sf_mb + mb) * pd.sf_kb * 512;
+        const uint8_t* sfb_src0 =
+            pd.sfb + (static_cast<long long>(batch) * pd.sf_nb + nb) * pd.sf_kb * 512;
+        const uint8_t* sfb_src1 = sfb_src0 + static_cast<long long>(pd.sf_kb) * 512;
+        const bool sfb1_valid = nb + 1 < pd.sf_nb;
+        int atoms_left = pd.sf_kb;
+        int kbyte = 0;
+        for (int kt = 0; kt < pd.k_tiles; ++kt) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_ptr)) {
+            report_failure(p, abort_ptr, kStatusProducerTimeout);
+            ok = false;
+            break;
+          }
+          const uint32_t sf_bytes =
+              atoms_left >= 4 ? 2048u : static_cast<uint32_t>(atoms_left) * 512u;
+          const uint32_t a_dst = stage_smem;
+          const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+          const uint32_t sfa_dst = b_dst + Cfg::B_BYTES;
+          const uint32_t sfb_dst = sfa_dst + Cfg::SFA_BYTES;
+          const uint32_t sf_bar = sf_full0 + 8 * stage;
+          mbar_expect_tx(sf_bar, sf_bytes * ((sfa_valid ? 1u : 0u) + 1u + (sfb1_valid ? 1u : 0u)));
+          if (sfa_valid) bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol);
+          bulk_load(sfb_dst, sfb_src0, sf_bytes, sf_bar, pol);
+          if (sfb1_valid) bulk_load(sfb_dst + 2048, sfb_src1, sf_bytes, sf_bar, pol);
+          // The leader arms its full barrier for the A and B bytes of both CTAs.
+          if (leader) mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
+          tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
+          tma_load_3d_pair(b_dst, &p.map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
+          sfa_src += 2048;
+          sfb_src0 += 2048;
+          sfb_src1 += 2048;
+          atoms_left -= 4;
+          kbyte += 128;
+          stage_smem += Cfg::STAGE_BYTES;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+            stage_smem = smem_base;
+          }
+        }
+      }
+      if (!ok || *abort_ptr != 0) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = nvf4_instr_desc(256, 256);
+      constexpr uint32_t kHiOperand = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kStage16 = Cfg::STAGE_BYTES >> 4;
+      const uint32_t lo_a0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
+      const uint32_t lo_b0 = lo_a0 + (Cfg::A_BYTES >> 4);
+      const uint32_t full0 = smem_u32(&bar_full[0]);
+      const uint32_t empty0 = smem_u32(&bar_empty[0]);
+      const uint32_t scales0 = smem_u32(&bar_scales[0]);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t stage16 = 0;
+      uint32_t t_sf = tmem_base + Cfg::SF_COL;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long t = first_tile; ok && t < tiles; t += pairs) {
+        if (!mbar_wait_cluster(smem_u32(&bar_acc_empty), acc_phase ^ 1u, abort_ptr)) {
+          report_failure(p, abort_ptr, kStatusMmaAccumTimeout);
+          break;
+        }
+        tc_fence_after_sync();
+        int atoms_left = pd.sf_kb;
+        uint32_t accumulate = 0;
+        for (int kt = 0; kt < pd.k_tiles; ++kt) {
+          if (!mbar_wait_cluster(full0 + 8 * stage, phase, abort_ptr) ||
+              !mbar_wait_cluster(scales0 + 8 * stage, phase, abort_ptr)) {
+            report_failure(p, abort_ptr, kStatusMmaInputTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t lo_a = lo_a0 + stage16;
+          const uint32_t lo_b = lo_b0 + stage16;
+          const int mmas = min(4, atoms_left);
+          for (int j = 0; j < mmas; ++j) {
+            tc_mma_nvf4_pair(tmem_base, pack_desc(lo_a + 2 * j, kHiOperand),
+                             pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
+                             t_sf + 16 + 8 * j, j > 0 ? 1u : accumulate);
+          }
+          accumulate = 1;
+          atoms_left -= 4;
+          tc_commit_pair(empty0 + 8 * stage, 3);
+          stage16 += kStage16;
+          t_sf += Cfg::SF_STAGE_COLS;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+            stage16 = 0;
+            t_sf = tmem_base + Cfg::SF_COL;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(smem_u32(&bar_acc_full), 3);
+        acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ scale movers
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
+    const uint32_t leader_scales0 = cluster_map_shared(smem_u32(&bar_scales[0]), 0);
+    const uint32_t row_off = static_cast<uint32_t>(lane) * 16u;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
+    uint32_t t_sf = tmem_base + lane_base + Cfg::SF_COL;
+    bool ok = true;
+    for (long long t = first_tile; ok && t < tiles; t += pairs) {
+      int atoms_left = pd.sf_kb;
+      for (int kt = 0; kt < pd.k_tiles; ++kt) {
+        if (!mbar_wait(sf_full0 + 8 * stage, phase, abort_ptr)) {
+          report_failure(p, abort_ptr, kStatusScaleTimeout);
+          ok = false;
+          break;
+        }
+        const int atoms = min(4, atoms_left);
+        for (int j = 0; j < atoms; ++j) {
+          tmem_store_4(t_sf + 4 * j, ld_shared_v4(sf_smem + 512 * j + row_off));
+          tmem_store_4(t_sf + 16 + 8 * j,
+                       ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 512 * j + row_off));
+          tmem_store_4(t_sf + 16 + 8 * j + 4,
+                       ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 + 512 * j + row_off));
+        }
+        tmem_store_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_scales0 + 8 * stage);
+        atoms_left -= 4;
+        sf_smem += Cfg::STAGE_BYTES;
+        t_sf += Cfg::SF_STAGE_COLS;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+          sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
+          t_sf = tmem_base + lane_base + Cfg::SF_COL;
+        }
+      }
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
+    const uint32_t leader_acc_empty = cluster_map_shared(smem_u32(&bar_acc_empty), 0);
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    uint32_t acc_phase = 0;
+    for (long long t = first_tile; t < tiles; t += pairs) {
+      int batch, m_tile, n_tile;
+      decode(t, batch, m_tile, n_tile);
+      if (!mbar_wait(smem_u32(&bar_acc_full), acc_phase, abort_ptr)) {
+        report_failure(p, abort_ptr, kStatusEpilogueTimeout);
+        break;
+      }
+      tc_fence_after_sync();
+      const int grow = m_tile * 256 + static_cast<int>(rank) * 128 + row;
+      const int n0 = n_tile * 256;
+      OutT* out_row = reinterpret_cast<OutT*>(pd.d) +
+                      (static_cast<long long>(batch) * pd.m + grow) * pd.n;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t r1[32];
+        float v[32];
+        tmem_load_32(taddr + c * 32, r1);
+        tmem_load_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * alpha;
+        if (c == 7) {
+          tc_fence_before_sync();
+          mbar_arrive_cluster(leader_acc_empty);
+        }
+        if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+      }
+      acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while the pair is in use
+  if (warp == 1) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace nvfp4

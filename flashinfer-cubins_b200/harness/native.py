@@ -44,7 +44,8 @@ class NativeError(RuntimeError):
 
 
 class Config(ctypes.Structure):
-    _fields_ = [("tile_n", ctypes.c_int), ("schedule", ctypes.c_int), ("ctas", ctypes.c_int)]
+    _fields_ = [("tile_n", ctypes.c_int), ("schedule", ctypes.c_int), ("ctas", ctypes.c_int),
+                ("pair", ctypes.c_int)]
 
 
 class PlanInfo(ctypes.Structure):
@@ -168,10 +169,10 @@ class Plan:
         self._handle = ctypes.c_void_p(handle)
 
     @staticmethod
-    def _config(tile_n: int = 0, schedule: int = 0, ctas: int = 0):
-        if not (tile_n or schedule or ctas):
+    def _config(tile_n: int = 0, schedule: int = 0, ctas: int = 0, pair: int = 0):
+        if not (tile_n or schedule or ctas or pair):
             return None
-        return ctypes.byref(Config(tile_n, schedule, ctas))
+        return ctypes.byref(Config(tile_n, schedule, ctas, pair))
 
     @classmethod
     def dense(cls, device: int, out_kind: int, m: int, n: int, k: int, l: int, **config):  # noqa: E741

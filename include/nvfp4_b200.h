@@ -53,6 +53,8 @@ typedef struct nvfp4_config {
                    through the workspace), 3 = cluster split-K (partials through peer
                    shared memory; dense and dual GEMM with fewer tiles than SMs only) */
   int ctas;     /* persistent grid size, at most the SM count */
+  int pair;     /* dense GEMM: 1 = 256 x 256 tiles on pairs of CTAs (tcgen05.mma
+                   cta_group::2), -1 = never, 0 = automatic */
 } nvfp4_config;
 
 /* What a plan decided; filled by nvfp4_plan_info. */

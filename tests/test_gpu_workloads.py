@@ -228,6 +228,43 @@ def test_cluster_split_k(m, n, k, l, tile_n):  # noqa: E741
         plan.destroy()
 
 
+@pytest.mark.parametrize("m,n,k,l", [(256, 256, 256, 1), (300, 520, 608, 2), (512, 768, 2080, 1),
+                                     (129, 264, 96, 1), (1024, 2048, 1024, 1)])
+@pytest.mark.parametrize("out_kind", (native.OUT_F16, native.OUT_F32))
+def test_pair_kernel(m, n, k, l, out_kind):  # noqa: E741
+    """The 2-CTA kernel (256 x 256 tiles, tcgen05.mma.cta_group::2), forced on shapes with
+    partial tiles in M, N and K, batches, and more tiles than one wave of pairs would hold
+    is not needed: bit-exact with integer scales, within tolerance otherwise."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    dtype = torch.float16 if out_kind == native.OUT_F16 else torch.float32
+    for scales, exact in (("int0_3", True), ("unit", False)):
+        case = CaseSpec("pair", {"m": m, "n": n, "k": k, "l": l, "scales": scales,
+                                 "alpha": 0.5}, 51)
+        inputs = workload.get_inputs(case)
+        a, b, sfa, sfb, alpha = inputs
+        plan = native.Plan.dense(0, out_kind, m, n, k, l, pair=1)
+        info = plan.info()
+        assert info["tile_m"] == 256 and info["tile_n"] == 256 and info["ctas"] % 2 == 0, info
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        d = torch.full((l, m, n), float("nan"), dtype=dtype, device=dev)
+        plan.launch_dense(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                          alpha.data_ptr(), d.data_ptr(), ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        from harness.workloads.quantization import fp4_matmul
+        from harness.workloads.nvfp4_gemm import from_task_scales
+        ref = fp4_matmul(a, b, from_task_scales(sfa, m, k // 16), from_task_scales(sfb, n, k // 16),
+                         alpha=0.5, out_dtype=dtype)
+        if exact:
+            assert torch.equal(d.permute(1, 2, 0), ref)
+        else:
+            torch.testing.assert_close(d.permute(1, 2, 0), ref, rtol=1e-3, atol=1e-3)
+        plan.destroy()
+
+
 @pytest.mark.parametrize("schedule", (1, 2, 3))
 def test_dual_gemm_under_every_schedule(schedule):
     """The fused dual GEMM with whole tiles, the workspace fix-up and the cluster
