@@ -180,15 +180,12 @@ class ClockSampler:
     def summary(self) -> dict:
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
-        # "Under load": the upper half of the clock samples (the GPU idles between phases).
-        clocks = sorted(s[0] for s in self.samples)
-        loaded = clocks[len(clocks) // 2:]
-        seen = 0
-        for _, _, reasons in self.samples:
-            seen |= reasons
-        names = [name for name, bit in self.REASONS.items() if seen & bit]
-        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": self.max_mhz,
-                "reasons": names, "samples": len(self.samples)}
+        # "Under load": samples taken while NVML reported the GPU at least half busy (all
+        # samples if none was: the timed regions are shorter than NVML's averaging window).
+        loaded = [s[0] for s in self.samples if s[1] >= 50] or [s[0] for s in self.samples]
+        return {"sm_mhz": statistics.median(loaded), "sm_min_mhz": min(loaded),
+                "sm_max_mhz": self.max_mhz, "reasons": names, "samples": len(self.samples),
+                "samples_under_load": len(loaded)}
 
 
 # -- CPU baseline (the oracle port) ---------------------------------------------------------

@@ -123,6 +123,9 @@ size_t round_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
 
 enum PlanKind { kDense = 0, kDual = 1, kGrouped = 2 };
 
+// Whether large dense GEMMs use the 2-CTA kernel without being asked to.
+constexpr bool kPairByDefault = false;
+
 using KernelFn = void (*)(const KernelParams);
 
 struct KernelChoice {
@@ -466,7 +469,7 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
     const bool explicit_tile = (config != nullptr && config->tile_n > 0) ||
                                env_int("NVFP4_TILE_N", 0) > 0;
-    plan->pair = want_pair > 0 || (want_pair == 0 && !explicit_tile && pair_tiles >= sms);
+    plan->pair = want_pair > 0 || (want_pair == 0 && !explicit_tile && pair_tiles >= sms && kPairByDefault);
     if (plan->pair) {
       plan->tile_n = 256;
       plan->out_tile_n = 256;

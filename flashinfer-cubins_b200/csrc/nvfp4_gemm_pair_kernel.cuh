@@ -206,9 +206,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           bulk_load(sfb_dst, sfb_src0, sf_bytes, sf_bar, pol);
           if (sfb1_valid) bulk_load(sfb_dst + 2048, sfb_src1, sf_bytes, sf_bar, pol);
           // The leader arms its full barrier for the A and B bytes of both CTAs.
-          if (leader) mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
-          tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
-          tma_load_3d_pair(b_dst, &p.map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
+          if (NVFP4_PROBE_FLAG(p, 2)) {
+            if (leader) mbar_arrive(smem_u32(&bar_full[stage]));
+          } else {
+            if (leader) {
+              mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
+            }
+            tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
+            tma_load_3d_pair(b_dst, &p.map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
+          }
           sfa_src += 2048;
           sfb_src0 += 2048;
           sfb_src1 += 2048;
@@ -244,7 +250,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
       uint32_t acc_phase = 0;
       bool ok = true;
       for (long long t = first_tile; ok && t < tiles; t += pairs) {
-        if (!mbar_wait_cluster(smem_u32(&bar_acc_empty), acc_phase ^ 1u, abort_ptr)) {
+        if (!mbar_wait(smem_u32(&bar_acc_empty), acc_phase ^ 1u, abort_ptr)) {
           report_failure(p, abort_ptr, kStatusMmaAccumTimeout);
           break;
         }
@@ -252,8 +258,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         int atoms_left = pd.sf_kb;
         uint32_t accumulate = 0;
         for (int kt = 0; kt < pd.k_tiles; ++kt) {
-          if (!mbar_wait_cluster(full0 + 8 * stage, phase, abort_ptr) ||
-              !mbar_wait_cluster(scales0 + 8 * stage, phase, abort_ptr)) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr) ||
+              !mbar_wait(scales0 + 8 * stage, phase, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusMmaInputTimeout);
             ok = false;
             break;
@@ -261,7 +267,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           tc_fence_after_sync();
           const uint32_t lo_a = lo_a0 + stage16;
           const uint32_t lo_b = lo_b0 + stage16;
-          const int mmas = min(4, atoms_left);
+          const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
           for (int j = 0; j < mmas; ++j) {
             tc_mma_nvf4_pair(tmem_base, pack_desc(lo_a + 2 * j, kHiOperand),
                              pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
@@ -304,17 +310,34 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           break;
         }
         const int atoms = min(4, atoms_left);
-        for (int j = 0; j < atoms; ++j) {
-          tmem_store_4(t_sf + 4 * j, ld_shared_v4(sf_smem + 512 * j + row_off));
-          tmem_store_4(t_sf + 16 + 8 * j,
-                       ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 512 * j + row_off));
-          tmem_store_4(t_sf + 16 + 8 * j + 4,
-                       ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 + 512 * j + row_off));
+        if (atoms == 4) {
+          // All twelve loads first, then the twelve stores: the loads overlap.
+          uint4 va[4], vb0[4], vb1[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            va[j] = ld_shared_v4(sf_smem + 512 * j + row_off);
+            vb0[j] = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 512 * j + row_off);
+            vb1[j] = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 + 512 * j + row_off);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            tmem_store_4(t_sf + 4 * j, va[j]);
+            tmem_store_4(t_sf + 16 + 8 * j, vb0[j]);
+            tmem_store_4(t_sf + 16 + 8 * j + 4, vb1[j]);
+          }
+        } else {
+          for (int j = 0; j < atoms; ++j) {
+            tmem_store_4(t_sf + 4 * j, ld_shared_v4(sf_smem + 512 * j + row_off));
+            tmem_store_4(t_sf + 16 + 8 * j,
+                         ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 512 * j + row_off));
+            tmem_store_4(t_sf + 16 + 8 * j + 4,
+                         ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 + 512 * j + row_off));
+          }
         }
         tmem_store_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(leader_scales0 + 8 * stage);
+        if (lane == 0) mbar_arrive_peer(leader_scales0 + 8 * stage);
         atoms_left -= 4;
         sf_smem += Cfg::STAGE_BYTES;
         t_sf += Cfg::SF_STAGE_COLS;
@@ -346,19 +369,54 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
       const int n0 = n_tile * 256;
       OutT* out_row = reinterpret_cast<OutT*>(pd.d) +
                       (static_cast<long long>(batch) * pd.m + grow) * pd.n;
-#pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
-        uint32_t r1[32];
-        float v[32];
-        tmem_load_32(taddr + c * 32, r1);
-        tmem_load_wait();
+      if constexpr (sizeof(OutT) == 2) {
+        // Read the whole row out of tensor memory first (packed to FP16: 128 registers),
+        // hand the accumulator back to the MMA issuer, then store: the next tile's MMAs
+        // start while this tile is still being written.
+        uint32_t packed[8][16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * alpha;
-        if (c == 7) {
-          tc_fence_before_sync();
-          mbar_arrive_cluster(leader_acc_empty);
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r1[32];
+          tmem_load_32(taddr + c * 32, r1);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            __half2 h = __floats2half2_rn(__uint_as_float(r1[2 * i]) * alpha,
+                                          __uint_as_float(r1[2 * i + 1]) * alpha);
+            packed[c][i] = *reinterpret_cast<uint32_t*>(&h);
+          }
         }
-        if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+        tc_fence_before_sync();
+        mbar_arrive_peer(leader_acc_empty);
+        if (grow < pd.m) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = n0 + c * 32 + 8 * g;
+              if (col < pd.n) {
+                *reinterpret_cast<uint4*>(out_row + col) = make_uint4(
+                    packed[c][4 * g], packed[c][4 * g + 1], packed[c][4 * g + 2],
+                    packed[c][4 * g + 3]);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r1[32];
+          float v[32];
+          tmem_load_32(taddr + c * 32, r1);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * alpha;
+          if (c == 7) {
+            tc_fence_before_sync();
+            mbar_arrive_peer(leader_acc_empty);
+          }
+          if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+        }
       }
       acc_phase ^= 1u;
     }

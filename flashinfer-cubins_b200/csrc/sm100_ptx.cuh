@@ -276,6 +276,13 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
                : "memory");
 }
 
+// Arrive on a peer CTA's mbarrier without cluster-scope release: for signals that order
+// only tcgen05 work (already fenced with tcgen05.fence) or nothing at all. Much cheaper
+// than the releasing form.
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
