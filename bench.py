@@ -183,6 +183,10 @@ class ClockSampler:
         # "Under load": samples taken while NVML reported the GPU at least half busy (all
         # samples if none was: the timed regions are shorter than NVML's averaging window).
         loaded = [s[0] for s in self.samples if s[1] >= 50] or [s[0] for s in self.samples]
+        seen = 0
+        for _, _, reasons in self.samples:
+            seen |= reasons
+        names = [name for name, bit in self.REASONS.items() if seen & bit]
         return {"sm_mhz": statistics.median(loaded), "sm_min_mhz": min(loaded),
                 "sm_max_mhz": self.max_mhz, "reasons": names, "samples": len(self.samples),
                 "samples_under_load": len(loaded)}
