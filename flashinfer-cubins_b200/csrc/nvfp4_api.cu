@@ -854,6 +854,39 @@ int nvfp4_pack_scales(const void* scales, void* packed, int rows, int cols, int 
   return 0;
 }
 
+int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
+                   int batches, void* stream) {
+  if (x == nullptr || packed == nullptr || scales == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  }
+  if (x_kind != NVFP4_IN_F32 && x_kind != NVFP4_IN_BF16) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "unknown input kind %d", x_kind);
+  }
+  if (rows < 1 || k < 16 || batches < 1 || k % 16 != 0) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "unsupported tensor rows=%d k=%d batches=%d", rows, k,
+                batches);
+  }
+  if (!aligned(x, 16) || !aligned(packed, 8) || !aligned(scales, 16)) {
+    return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
+  }
+  const long long total = static_cast<long long>(batches) * ceil_div(rows, 128) * 128 *
+                          ceil_div(k / 16, 4) * 4;
+  const int threads = 256;
+  const long long blocks = std::min<long long>((total + threads - 1) / threads, 148 * 32);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (x_kind == NVFP4_IN_F32) {
+    quantize_nvfp4_kernel<float><<<static_cast<unsigned int>(blocks), threads, 0, s>>>(
+        static_cast<const float*>(x), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales),
+        rows, k, batches);
+  } else {
+    quantize_nvfp4_kernel<__nv_bfloat16><<<static_cast<unsigned int>(blocks), threads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(packed),
+        static_cast<uint8_t*>(scales), rows, k, batches);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
 int nvfp4_silu_product(const float* h1, const float* h2, void* out, int64_t size, void* stream) {
   if (h1 == nullptr || h2 == nullptr || out == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");

@@ -1,10 +1,12 @@
-// The two small kernels around the NVFP4 dual GEMM: the scale relayout into the
-// blocked 128x4 layout and the silu gate over FP32 intermediates. Both are plain
-// bandwidth kernels: 16-byte accesses, grid-stride loops.
+// The small bandwidth kernels around the NVFP4 GEMMs: the scale relayout into the blocked
+// 128x4 layout, the FP32/BF16 -> NVFP4 quantiser that writes blocked scales directly, and the
+// silu gate over FP32 intermediates. 16-byte accesses, grid-stride loops.
 #pragma once
 
 #include <cstdint>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 namespace nvfp4 {
@@ -49,6 +51,84 @@ __global__ void pack_scales_kernel(const uint8_t* __restrict__ scales,
     }
     *reinterpret_cast<uint4*>(packed + line * 16) =
         make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
+// Round-to-nearest-even E2M1 code of v (saturating at +-6; values that round to zero
+// get code 0 whatever their sign).
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+  const float m = fabsf(v);
+  uint32_t code = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) + (m > 2.5f) +
+                  (m >= 3.5f) + (m > 5.0f);
+  if (v < 0.0f && code != 0) code |= 8u;
+  return code;
+}
+
+// FP32/BF16 [batches][rows][k] -> packed E2M1 [batches][rows][k/2] and UE4M3 scales in the
+// blocked layout [batches][rb][cb][32][4][4] (zero padded), one thread per 16-element block
+// of the padded scale grid: scale = e4m3(amax / 6) (round to nearest even, saturating),
+// element = E2M1 rounding of x / scale, zero scale -> zero codes.
+template <typename In>
+__global__ void quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
+                                      uint8_t* __restrict__ scales, int rows, int k,
+                                      int batches) {
+  const int cols = k / 16;
+  const int rb = (rows + 127) / 128;
+  const int cb = (cols + 3) / 4;
+  const long long padded_cols = static_cast<long long>(cb) * 4;
+  const long long total = static_cast<long long>(batches) * rb * 128 * padded_cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % padded_cols);
+    long long rest = i / padded_cols;
+    const int r = static_cast<int>(rest % (rb * 128));
+    const int batch = static_cast<int>(rest / (rb * 128));
+    const long long atom = (static_cast<long long>(batch) * rb + r / 128) * cb + c / 4;
+    uint8_t* scale_out = scales + atom * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4 + c % 4;
+    if (r >= rows || c >= cols) {
+      *scale_out = 0;
+      continue;
+    }
+    const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
+    float v[16];
+    if constexpr (sizeof(In) == 4) {
+      const float4* src = reinterpret_cast<const float4*>(x + element);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 t = src[q];
+        v[4 * q] = t.x;
+        v[4 * q + 1] = t.y;
+        v[4 * q + 2] = t.z;
+        v[4 * q + 3] = t.w;
+      }
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(x + element);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint4 t = src[q];
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[8 * q + 2 * j] = __uint_as_float(w[j] << 16);
+          v[8 * q + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    const uint8_t scale_bits = static_cast<uint8_t>(
+        __nv_cvt_float_to_fp8(fminf(__fdiv_rn(amax, 6.0f), 448.0f), __NV_SATFINITE, __NV_E4M3));
+    *scale_out = scale_bits;
+    const float scale = __half2float(__half(__nv_cvt_fp8_to_halfraw(scale_bits, __NV_E4M3)));
+    uint32_t words[2] = {0u, 0u};
+    if (scale > 0.0f) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        words[j / 8] |= e2m1_code(__fdiv_rn(v[j], scale)) << (4 * (j % 8));
+      }
+    }
+    *reinterpret_cast<uint2*>(packed + element / 2) = make_uint2(words[0], words[1]);
   }
 }
 

@@ -102,6 +102,9 @@ _PROTOTYPES = {
     "nvfp4_pack_scales": (
         ctypes.c_int, [_P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
     ),
+    "nvfp4_quantize": (
+        ctypes.c_int, [_P, ctypes.c_int, _P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
+    ),
     "nvfp4_silu_product": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P]),
 }
 
@@ -260,6 +263,15 @@ class Plan:
 
 def pack_scales(scales: int, packed: int, rows: int, cols: int, batches: int, stream: int) -> None:
     check(load().nvfp4_pack_scales(scales, packed, rows, cols, batches, stream))
+
+
+IN_F32 = 0
+IN_BF16 = 1
+
+
+def quantize(x: int, x_kind: int, packed: int, scales: int, rows: int, k: int, batches: int,
+             stream: int) -> None:
+    check(load().nvfp4_quantize(x, x_kind, packed, scales, rows, k, batches, stream))
 
 
 def silu_product(h1: int, h2: int, out: int, size: int, stream: int) -> None:

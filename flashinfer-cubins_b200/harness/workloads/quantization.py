@@ -191,3 +191,26 @@ def quantize_nvfp4(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     if squeeze:
         return packed[..., 0], scales[..., 0]
     return packed, scales
+
+
+def quantize_nvfp4_native(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``quantize_nvfp4`` on the GPU by the library's kernel (``nvfp4_quantize``): FP32 or
+    BF16 ``(rows, k, l)`` (a view of contiguous ``(l, rows, k)``) on a CUDA device ->
+    packed E2M1 ``(rows, k/2, l)`` and the scales already in the blocked layout, as a
+    contiguous ``(l, rb, cb, 32, 4, 4)`` tensor. Same bytes as ``quantize_nvfp4`` followed
+    by ``to_blocked_scales``, in one pass over ``x``."""
+    from .. import native
+
+    if x.dim() != 3 or not x.permute(2, 0, 1).is_contiguous() or x.device.type != "cuda":
+        raise ValueError("expected a CUDA (rows, k, l) view of contiguous (l, rows, k) storage")
+    if x.dtype not in (torch.float32, torch.bfloat16) or x.shape[1] % SF_VEC:
+        raise ValueError("expected FP32 or BF16 with k a multiple of 16")
+    rows, k, batches = x.shape
+    packed = torch.empty((batches, rows, k // 2), dtype=torch.uint8, device=x.device)
+    blocked = torch.empty((batches, ceil_div(rows, SF_ROWS), ceil_div(k // SF_VEC, SF_COLS), 32, 4, 4),
+                          dtype=torch.float8_e4m3fn, device=x.device)
+    with torch.cuda.device(x.device):
+        native.quantize(x.data_ptr(), native.IN_F32 if x.dtype == torch.float32 else native.IN_BF16,
+                        packed.data_ptr(), blocked.data_ptr(), rows, k, batches,
+                        torch.cuda.current_stream(x.device).cuda_stream)
+    return packed.permute(1, 2, 0), blocked

@@ -172,6 +172,21 @@ int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int
 int nvfp4_pack_scales(const void* scales, void* packed, int rows, int cols, int batches,
                       void* stream);
 
+/* Input kinds of nvfp4_quantize. */
+#define NVFP4_IN_F32 0
+#define NVFP4_IN_BF16 1
+
+/* FP32 or BF16 x[batches][rows][k] -> NVFP4: packed E2M1 [batches][rows][k/2] and UE4M3
+ * scales written straight into the blocked layout (zero padded). Per 16-element K block
+ * scale = e4m3(amax / 6) (round to nearest even, saturating) and each element is the
+ * round-to-nearest-even E2M1 code of x / scale; a zero scale gives zero codes. The step
+ * before the GEMMs (the reference takes pre-quantised inputs); follows the reference's
+ * NVFP4 convention (harness/workloads/batched_gemm/trtllm.py:530-547, formats.py:57-82)
+ * and replaces a separate relayout pass (impls/nvfp4_dual_gemm/kernels/pack_scales.cu:9-19).
+ * Requires k % 16 == 0; x 16-byte aligned. */
+int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
+                   int batches, void* stream);
+
 /* out[i] = half(silu(h1[i]) * h2[i]) over `size` FP32 elements. Replaces the
  * silu_product kernel (impls/nvfp4_dual_gemm/kernels/silu_product.cu:7-9,
  * harness/workloads/nvfp4_dual_gemm.py:352-367). */

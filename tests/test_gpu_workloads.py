@@ -332,3 +332,30 @@ def test_native_rejects_misaligned_and_wrong_plans():
         native.Plan.dense(0, native.OUT_F16, 128, 128, 128, 1, tile_n=96)
     assert native.device_supported(0)
     plan.destroy()
+
+
+@pytest.mark.parametrize("rows,k,batches", [(128, 256, 1), (200, 96, 2), (1, 32, 1), (1000, 4096, 1)])
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
+def test_quantiser_kernel_matches_torch_quantiser_bytes(rows, k, batches, dtype):
+    """FP32/BF16 -> packed E2M1 + blocked UE4M3 scales in one kernel: byte-identical to the
+    torch quantiser (pinned against the reference's convention) followed by the relayout,
+    including zero blocks, saturating scales, ties and the zero padding of partial atoms."""
+    from harness.workloads import quantization as q
+    g = torch.Generator().manual_seed(rows + k)
+    x = torch.randn(batches, rows, k, generator=g)
+    x[0, 0, :16] = 0.0
+    if rows > 1:
+        x[0, 1, :16] *= 4000.0
+        x[0, rows - 1, -16:] = torch.linspace(-6, 6, 16)
+    x = x.to(dtype).cuda().permute(1, 2, 0)
+    packed, blocked = q.quantize_nvfp4_native(x)
+    torch.cuda.synchronize()
+    want_packed, want_scales = q.quantize_nvfp4(x.float())
+    assert torch.equal(packed, want_packed)
+    assert torch.equal(blocked.view(torch.uint8), q.to_blocked_scales(want_scales).view(torch.uint8))
+    # And the oracle agrees on the FP32 path.
+    if dtype == torch.float32:
+        host = x.permute(2, 0, 1).contiguous().cpu().numpy()
+        o_packed, o_scales = o.quantize_nvfp4(host)
+        assert np.array_equal(packed.permute(2, 0, 1).cpu().numpy(), o_packed)
+        assert np.array_equal(blocked.view(torch.uint8).cpu().numpy(), o.to_blocked(o_scales))
