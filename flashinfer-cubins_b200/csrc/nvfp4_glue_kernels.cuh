@@ -133,7 +133,7 @@ __global__ void quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restr
 }
 
 __device__ __forceinline__ float silu_gate(float a, float b) {
-  return a / (1.0f + expf(-a)) * b;
+  return a * __frcp_rn(1.0f + __expf(-a)) * b;
 }
 
 // out[i] = half(silu(h1[i]) * h2[i]); eight elements per thread when the arrays are
