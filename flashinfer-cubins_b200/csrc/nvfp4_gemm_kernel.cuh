@@ -224,11 +224,16 @@ __device__ __forceinline__ void report_failure(const KernelParams& p, volatile i
   atomicCAS(p.status, 0, code);
 }
 
-// x * sigmoid(x) with the fast exponential and reciprocal: about 2 ulp of FP32, far inside
-// one FP16 rounding of the result, and no slow path when exp(-x) overflows to infinity
-// (IEEE division by infinity goes through a subroutine that cost ~20 us per tile here).
+// x * sigmoid(x) on the special-function unit alone: ex2.approx and rcp.approx, about
+// 2 ulp of FP32, far inside one FP16 rounding of the result. Neither has a slow path:
+// the IEEE division and the correctly rounded reciprocal both branch to a subroutine
+// when exp(-x) overflows to infinity, which cost ~20 us per 128x128 tile here.
+// x -> -inf gives x * rcp(inf) = -0.
 __device__ __forceinline__ float silu_f32(float x) {
-  return x * __frcp_rn(1.0f + __expf(-x));
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
 }
 
 // Stores 32 consecutive output columns of one row in 16-byte pieces (8-byte pieces of
@@ -782,7 +787,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             tmem_load_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              v[i] = silu_f32(__uint_as_float(r1[i]) * alpha) * (__uint_as_float(r2[i]) * alpha);
+              v[i] = NVFP4_PROBE_FLAG(p, 10)
+                         ? __uint_as_float(r1[i]) + __uint_as_float(r2[i])
+                         : silu_f32(__uint_as_float(r1[i]) * alpha) * (__uint_as_float(r2[i]) * alpha);
             }
           } else {
             tmem_load_wait();
@@ -793,7 +800,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bar_acc_empty[acc]));
           }
-          if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+          if (grow < pd.m && !NVFP4_PROBE_FLAG(p, 11)) {
+            store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+          }
         }
       } else if (p.split > 1) {
         cluster_reduce<Cfg>(p, pd, s, taddr, smem_base, smem_u32(&bar_peer_ready),

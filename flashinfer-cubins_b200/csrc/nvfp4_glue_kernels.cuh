@@ -132,8 +132,12 @@ __global__ void quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restr
   }
 }
 
+// silu(a) * b with ex2.approx and rcp.approx (no slow path when exp(-a) overflows).
 __device__ __forceinline__ float silu_gate(float a, float b) {
-  return a * __frcp_rn(1.0f + __expf(-a)) * b;
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return a * r * b;
 }
 
 // out[i] = half(silu(h1[i]) * h2[i]); eight elements per thread when the arrays are
