@@ -203,7 +203,11 @@ struct GemmConfig {
   static constexpr int SFB_BYTES = 4 * 512 * SFB_BLOCKS;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;  // 1 KiB alignment slack + static
+#ifdef NVFP4_FORCE_STAGES  // timing experiments only
+  static constexpr int STAGES = NVFP4_FORCE_STAGES;
+#else
   static constexpr int STAGES = const_min(8, SMEM_BUDGET / STAGE_BYTES);
+#endif
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
   static constexpr int ACC_BUFS = BN <= 128 ? 2 : 1;
   static constexpr int SFB_COLS = const_max(4, BN / 32);  // columns per k-block
@@ -497,15 +501,20 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   grid_dependency_wait();
   grid_launch_dependents();
 
-  if (warp == 0) {
+  if (NVFP4_PROBE_FLAG(p, 12)) {
+    // timing experiment: prologue and teardown only
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
+    // The whole warp runs the loop (waits included); one elected lane issues the copies.
+    {
       const uint64_t pol_a = l2_policy_evict_last();
       const uint64_t pol_b = p.b_streams ? l2_policy_evict_first() : l2_policy_evict_last();
       if constexpr (!Cfg::GROUPED) {
-        prefetch_tensormap(&p.map_a);
-        prefetch_tensormap(&p.map_b);
-        if constexpr (Cfg::DUAL) prefetch_tensormap(&p.map_b2);
+        if (elect_one()) {
+          prefetch_tensormap(&p.map_a);
+          prefetch_tensormap(&p.map_b);
+          if constexpr (Cfg::DUAL) prefetch_tensormap(&p.map_b2);
+        }
       }
       WorkIter<Cfg::GROUPED> it(p);
       Segment s;
@@ -557,28 +566,34 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           // Scales first, on their own barrier: they are small, land early, and the
           // scale movers can put them into tensor memory while A and B are still in
           // flight.
-          if (!NVFP4_PROBE_FLAG(p, 5)) {
-            mbar_expect_tx(sf_bar, sf_bytes * (1u + sfb_valid));
-            bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol_a);
+          if (elect_one()) {
+            if (!NVFP4_PROBE_FLAG(p, 5)) {
+              mbar_expect_tx(sf_bar, sf_bytes * (1u + sfb_valid));
+              bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol_a);
 #pragma unroll
-            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-              if (sfb_src[i] != nullptr) {
-                bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, sf_bar, pol_b);
-                sfb_src[i] += 2048;
+              for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+                if (sfb_src[i] != nullptr) {
+                  bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, sf_bar, pol_b);
+                }
               }
+            } else if (!NVFP4_PROBE_FLAG(p, 17)) {
+              mbar_arrive(sf_bar);
             }
-          } else {
-            mbar_arrive(sf_bar);
+            if (!probe_no_ab) {
+              mbar_expect_tx(bar, ab_bytes);
+              tma_load_3d(a_dst, map_a, bar, kbyte, m0, s.batch, pol_a);
+              tma_load_3d(b_dst, map_b, bar, kbyte, n0, s.batch, pol_b);
+              if constexpr (Cfg::DUAL) {
+                tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kbyte, n0, s.batch, pol_b);
+              }
+            } else {
+              mbar_arrive(bar);
+            }
           }
-          if (!probe_no_ab) {
-            mbar_expect_tx(bar, ab_bytes);
-            tma_load_3d(a_dst, map_a, bar, kbyte, m0, s.batch, pol_a);
-            tma_load_3d(b_dst, map_b, bar, kbyte, n0, s.batch, pol_b);
-            if constexpr (Cfg::DUAL) {
-              tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kbyte, n0, s.batch, pol_b);
-            }
-          } else {
-            mbar_arrive(bar);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+            if (sfb_src[i] != nullptr) sfb_src[i] += 2048;
           }
           sfa_src += 2048;
           atoms_left -= 4;
@@ -598,7 +613,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop; one elected lane (the same one every time, since a
+    // commit covers the instructions of the thread that issues it) issues the MMAs.
+    {
       constexpr uint32_t idesc = nvf4_instr_desc(128, BN);
       // Descriptor words that never change: the high half (stride between eight-row
       // groups 1024 bytes, version, 128-byte swizzle) and, per stage, the low half
@@ -633,35 +650,43 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         int atoms_left = pd.sf_kb - 4 * s.k0;
         uint32_t accumulate = 0;
         for (int kt = s.k0; kt < s.k1; ++kt) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr) ||
-              !mbar_wait(scales0 + 8 * stage, phase, abort_ptr)) {
+          const bool got_full = mbar_wait(full0 + 8 * stage, phase, abort_ptr);
+          if (!got_full ||
+              (!NVFP4_PROBE_FLAG(p, 17) && !mbar_wait(scales0 + 8 * stage, phase, abort_ptr))) {
             report_failure(p, abort_ptr, kStatusMmaInputTimeout);
             ok = false;
             break;
           }
-          tc_fence_after_sync();
+          if (!NVFP4_PROBE_FLAG(p, 15)) tc_fence_after_sync();
           const uint32_t lo_a = lo_a0 + stage16;
           const uint32_t lo_b = lo_b0 + stage16;
           const uint32_t t_sfb = t_sf + 16 + sfb_half;
-          if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 1)) {
+          if (elect_one()) {
+            if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 1)) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
-                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
-                          t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
+              for (int j = 0; j < 4; ++j) {
+                tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
+                            pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
+                            t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
+              }
+            } else {
+              // K tail: fewer than four 64-wide blocks left (or a timing experiment).
+              const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
+              for (int j = 0; j < mmas; ++j) {
+                tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
+                            pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
+                            t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
+              }
             }
-          } else {
-            // K tail: fewer than four 64-wide blocks left (or a timing experiment).
-            const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
-            for (int j = 0; j < mmas; ++j) {
-              tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
-                          pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
-                          t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
+            if (NVFP4_PROBE_FLAG(p, 14)) {
+              mbar_arrive(empty0 + 8 * stage);
+            } else {
+              tc_commit(empty0 + 8 * stage);
             }
           }
+          __syncwarp();
           accumulate = 1;
           atoms_left -= 4;
-          tc_commit(empty0 + 8 * stage);
           stage16 += kStage16;
           t_sf += Cfg::SF_STAGE_COLS;
           if (++stage == STAGES) {
@@ -672,7 +697,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           }
         }
         if (!ok) break;
-        tc_commit(smem_u32(&bar_acc_full[acc]));
+        if (elect_one()) tc_commit(smem_u32(&bar_acc_full[acc]));
+        __syncwarp();
         if (++acc == ACC_BUFS) {
           acc = 0;
           acc_phase ^= 1u;
@@ -696,7 +722,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     uint32_t sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
     uint32_t t_sf = tmem_base + lane_base + Cfg::SF_COL;
     bool ok = true;
-    while (ok && it.next(s)) {
+    while (ok && !NVFP4_PROBE_FLAG(p, 17) && it.next(s)) {
       int atoms_left = it.pd.sf_kb - 4 * s.k0;
       for (int kt = s.k0; kt < s.k1; ++kt) {
         if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
@@ -704,7 +730,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           ok = false;
           break;
         }
-        const int atoms = min(4, atoms_left);
+        const int atoms = NVFP4_PROBE_FLAG(p, 13) ? 0 : min(4, atoms_left);
         if (atoms == 4) {
           uint4 va[4];
           uint4 vb[4][Cfg::SFB_BLOCKS];
@@ -716,13 +742,15 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
               vb[j][i] = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 * i + 512 * j + row_off);
             }
           }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            tmem_store_4(t_sf + 4 * j, va[j]);
-#pragma unroll
-            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-              tmem_store_4(t_sf + 16 + j * Cfg::SFB_COLS + 4 * i, vb[j][i]);
-            }
+          // The stage's columns are contiguous (A: k-block j at 4j; B: k-block j, atom i
+          // at 16 + j * SFB_COLS + 4i), so whole 16-column stores cover them: the cost of
+          // a tensor-memory store is per instruction, not per column.
+          tmem_store_16(t_sf, va[0], va[1], va[2], va[3]);
+          if constexpr (Cfg::SFB_BLOCKS == 1) {
+            tmem_store_16(t_sf + 16, vb[0][0], vb[1][0], vb[2][0], vb[3][0]);
+          } else {
+            tmem_store_16(t_sf + 16, vb[0][0], vb[0][1], vb[1][0], vb[1][1]);
+            tmem_store_16(t_sf + 32, vb[2][0], vb[2][1], vb[3][0], vb[3][1]);
           }
         } else {
           for (int j = 0; j < atoms; ++j) {
@@ -734,8 +762,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             }
           }
         }
-        tmem_store_wait();
-        tc_fence_before_sync();
+        if (!NVFP4_PROBE_FLAG(p, 16)) tmem_store_wait();
+        if (!NVFP4_PROBE_FLAG(p, 15)) tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(scales0 + 8 * stage);
         atoms_left -= 4;
@@ -748,6 +776,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           t_sf = tmem_base + lane_base + Cfg::SF_COL;
         }
       }
+    }
+    if (warp == 6 && lane == 0) {
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------------ epilogue

@@ -23,6 +23,21 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// True in exactly one lane of a fully converged warp (the same lane every time). The
+// single-issuer roles run their loops with the whole warp and wrap only the issuing
+// instructions in this, which keeps addresses and loop state in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
@@ -59,28 +74,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Longest time any role waits on one barrier phase before it gives up.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// Longest wait on one barrier phase before a role gives up, in polls: a failed poll
+// returns after ~20 clocks, so 2^27 polls are on the order of a second.
+constexpr uint32_t kWaitLimitSpins = 1u << 27;
 
 // Bounded wait for the phase with the given parity. `abort_flag` is a word in
 // shared memory that any role sets when it gives up, so that the others stop
-// waiting soon after. Returns false when the wait was abandoned.
+// waiting soon after. Returns false when the wait was abandoned. The loop is kept
+// this small on purpose: the single-lane roles run it once per pipeline step, and
+// every extra exit or counter in it showed up as 100-200 clocks per step.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag) {
-#pragma unroll 1
-  for (int i = 0; i < 128; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-  }
-  const uint64_t t0 = global_timer_ns();
-#pragma unroll 1
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      if (mbar_try_wait(bar, parity)) return true;
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3FFu) == 0u) {
+      if (*abort_flag != 0 || spins >= kWaitLimitSpins) return false;
     }
-    if (*abort_flag != 0) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
+  return true;
 }
 
 // ---------------------------------------------------------------------------
@@ -230,6 +241,16 @@ __device__ __forceinline__ void tmem_store_4(uint32_t addr, uint4 v) {
                : "memory");
 }
 
+// Warp-collective: sixteen consecutive 32-bit columns of this thread's lane.
+__device__ __forceinline__ void tmem_store_16(uint32_t addr, uint4 a, uint4 b, uint4 c, uint4 d) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(addr),
+      "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w), "r"(c.x),
+      "r"(c.y), "r"(c.z), "r"(c.w), "r"(d.x), "r"(d.y), "r"(d.z), "r"(d.w)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_store_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -300,16 +321,13 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // Bounded wait (see mbar_wait) that also acquires peer CTAs' writes.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag) {
-  const uint64_t t0 = global_timer_ns();
-#pragma unroll 1
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      if (mbar_try_wait_cluster(bar, parity)) return true;
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 0x3FFu) == 0u) {
+      if (*abort_flag != 0 || spins >= kWaitLimitSpins) return false;
     }
-    if (*abort_flag != 0) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
+  return true;
 }
 
 // All threads of every CTA in the cluster.
