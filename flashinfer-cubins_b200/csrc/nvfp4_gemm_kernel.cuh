@@ -449,12 +449,13 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   using OutT = typename Cfg::OutT;
 
   extern __shared__ uint8_t dyn_smem[];
+  // A stage is full when A and B have landed (the producer's arrive + transaction bytes)
+  // and the four scale movers have put its scales into tensor memory: five arrivals.
   __shared__ alignas(8) uint64_t bar_full[STAGES];
   __shared__ alignas(8) uint64_t bar_empty[STAGES];
   __shared__ alignas(8) uint64_t bar_acc_full[ACC_BUFS];
   __shared__ alignas(8) uint64_t bar_acc_empty[ACC_BUFS];
   __shared__ alignas(8) uint64_t bar_sf_full[STAGES];  // a stage's scale atoms have landed
-  __shared__ alignas(8) uint64_t bar_scales[STAGES];   // ... and are in tensor memory
   __shared__ alignas(8) uint64_t bar_peer_ready;  // every peer's pipeline memory is free
   __shared__ alignas(8) uint64_t bar_peer_data;   // every peer's partial columns have arrived
   __shared__ uint32_t tmem_base_slot;
@@ -468,10 +469,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_full[s]), 5);
       mbar_init(smem_u32(&bar_empty[s]), 1);
       mbar_init(smem_u32(&bar_sf_full[s]), 1);
-      mbar_init(smem_u32(&bar_scales[s]), 4);
     }
 #pragma unroll
     for (int a = 0; a < ACC_BUFS; ++a) {
@@ -576,7 +576,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                   bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, sf_bar, pol_b);
                 }
               }
-            } else if (!NVFP4_PROBE_FLAG(p, 17)) {
+            } else {
               mbar_arrive(sf_bar);
             }
             if (!probe_no_ab) {
@@ -627,7 +627,6 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       const uint32_t lo_b0 = lo_a0 + (Cfg::A_BYTES >> 4);
       const uint32_t full0 = smem_u32(&bar_full[0]);
       const uint32_t empty0 = smem_u32(&bar_empty[0]);
-      const uint32_t scales0 = smem_u32(&bar_scales[0]);
       WorkIter<Cfg::GROUPED> it(p);
       Segment s;
       int stage = 0;
@@ -650,14 +649,12 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         int atoms_left = pd.sf_kb - 4 * s.k0;
         uint32_t accumulate = 0;
         for (int kt = s.k0; kt < s.k1; ++kt) {
-          const bool got_full = mbar_wait(full0 + 8 * stage, phase, abort_ptr);
-          if (!got_full ||
-              (!NVFP4_PROBE_FLAG(p, 17) && !mbar_wait(scales0 + 8 * stage, phase, abort_ptr))) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusMmaInputTimeout);
             ok = false;
             break;
           }
-          if (!NVFP4_PROBE_FLAG(p, 15)) tc_fence_after_sync();
+          tc_fence_after_sync();
           const uint32_t lo_a = lo_a0 + stage16;
           const uint32_t lo_b = lo_b0 + stage16;
           const uint32_t t_sfb = t_sf + 16 + sfb_half;
@@ -678,11 +675,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                             t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
               }
             }
-            if (NVFP4_PROBE_FLAG(p, 14)) {
-              mbar_arrive(empty0 + 8 * stage);
-            } else {
-              tc_commit(empty0 + 8 * stage);
-            }
+            tc_commit(empty0 + 8 * stage);
           }
           __syncwarp();
           accumulate = 1;
@@ -712,8 +705,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     // into the stage's scale columns: lane i takes the atom's 16-byte row i, which holds
     // the scales of rows i, 32+i, 64+i, 96+i for one 64-wide K block = four columns.
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t full0 = smem_u32(&bar_sf_full[0]);
-    const uint32_t scales0 = smem_u32(&bar_scales[0]);
+    const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
+    const uint32_t full0 = smem_u32(&bar_full[0]);
     const uint32_t row_off = static_cast<uint32_t>(lane) * 16u;
     WorkIter<Cfg::GROUPED> it(p);
     Segment s;
@@ -722,10 +715,10 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     uint32_t sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
     uint32_t t_sf = tmem_base + lane_base + Cfg::SF_COL;
     bool ok = true;
-    while (ok && !NVFP4_PROBE_FLAG(p, 17) && it.next(s)) {
+    while (ok && it.next(s)) {
       int atoms_left = it.pd.sf_kb - 4 * s.k0;
       for (int kt = s.k0; kt < s.k1; ++kt) {
-        if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
+        if (!mbar_wait(sf_full0 + 8 * stage, phase, abort_ptr)) {
           report_failure(p, abort_ptr, kStatusScaleTimeout);
           ok = false;
           break;
@@ -762,10 +755,10 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             }
           }
         }
-        if (!NVFP4_PROBE_FLAG(p, 16)) tmem_store_wait();
-        if (!NVFP4_PROBE_FLAG(p, 15)) tc_fence_before_sync();
+        tmem_store_wait();
+        tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(scales0 + 8 * stage);
+        if (lane == 0) mbar_arrive(full0 + 8 * stage);
         atoms_left -= 4;
         sf_smem += Cfg::STAGE_BYTES;
         t_sf += Cfg::SF_STAGE_COLS;
