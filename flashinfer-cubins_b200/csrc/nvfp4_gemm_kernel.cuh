@@ -202,7 +202,9 @@ struct GemmConfig {
   static constexpr int SFA_BYTES = 4 * 512;
   static constexpr int SFB_BYTES = 4 * 512 * SFB_BLOCKS;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-  static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;  // 1 KiB alignment slack + static
+  // 227 KiB per CTA less 1 KiB alignment slack, the barriers, and the epilogue warps'
+  // 8 KiB of staging for coalesced stores (both static).
+  static constexpr int SMEM_BUDGET = 227 * 1024 - 2048 - 8192;
 #ifdef NVFP4_FORCE_STAGES  // timing experiments only
   static constexpr int STAGES = NVFP4_FORCE_STAGES;
 #else
@@ -283,6 +285,74 @@ __device__ __forceinline__ void store_row_chunk(OutT* row_ptr, int col0, int n,
         float4 q = make_float4(v[4 * g + 0], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         *reinterpret_cast<float4*>(row_ptr + col0 + 4 * g) = q;
       }
+    }
+  }
+}
+
+// Coalesced form of the same store for a whole warp. Each lane holds 64 bytes of its own
+// row (words w); stored directly, one warp instruction would touch 32 different rows, and
+// the load/store unit handles one row per clock. The warp instead passes the 32 x 64-byte
+// block through 2 KiB of shared memory (16-byte pieces XOR-swizzled by row pair, so both
+// the row-wise writes and the 8-row reads are free of bank conflicts) and writes it out
+// eight rows per instruction, four lanes per 64-byte run. `block` points at the block's
+// first row at column 0; `col` is the first of its columns; rows at or beyond
+// `rows_valid` and pieces at or beyond column `n` are dropped. Needs rows of D 16-byte
+// aligned (n a multiple of 16 / sizeof(OutT)).
+template <typename OutT>
+__device__ __forceinline__ void store_block_coalesced(uint32_t stage, const uint32_t (&w)[16],
+                                                      OutT* block, int col, int n,
+                                                      int rows_valid, int lane) {
+  constexpr int kPieceElems = 16 / static_cast<int>(sizeof(OutT));
+  const uint32_t own = stage + static_cast<uint32_t>(lane) * 64u;
+  const uint32_t own_swizzle = (static_cast<uint32_t>(lane) >> 1) & 3u;
+#pragma unroll
+  for (uint32_t q = 0; q < 4; ++q) {
+    st_shared_v4(own + ((q ^ own_swizzle) << 4), w[4 * q], w[4 * q + 1], w[4 * q + 2],
+                 w[4 * q + 3]);
+  }
+  __syncwarp();
+  const int sub = lane >> 2;
+  const uint32_t piece = static_cast<uint32_t>(lane) & 3u;
+  const uint32_t src = stage + static_cast<uint32_t>(sub) * 64u +
+                       ((piece ^ ((static_cast<uint32_t>(sub) >> 1) & 3u)) << 4);
+  const int piece_col = col + static_cast<int>(piece) * kPieceElems;
+  OutT* dst = block + static_cast<long long>(sub) * n + piece_col;
+  const long long step = 8ll * n;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 v = ld_shared_v4(src + static_cast<uint32_t>(j) * 512u);
+    if (8 * j + sub < rows_valid && piece_col < n) *reinterpret_cast<uint4*>(dst + j * step) = v;
+  }
+  __syncwarp();
+}
+
+// 32 output columns of the warp's 32 rows: coalesced when the rows of D are 16-byte
+// aligned, row by row otherwise. `v` is this lane's row; `block` as above; `row_ptr`
+// this lane's own row at column 0; `row_ok` whether that row exists.
+template <typename OutT>
+__device__ __forceinline__ void store_warp_chunk(uint32_t stage, OutT* block, OutT* row_ptr,
+                                                 bool row_ok, int col0, int n, int rows_valid,
+                                                 int lane, const float (&v)[32]) {
+  constexpr int kPieceElems = 16 / static_cast<int>(sizeof(OutT));
+  if (n % kPieceElems != 0) {
+    if (row_ok) store_row_chunk<OutT>(row_ptr, col0, n, v);
+    return;
+  }
+  if constexpr (sizeof(OutT) == 2) {
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    store_block_coalesced<OutT>(stage, w, block, col0, n, rows_valid, lane);
+  } else {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[16 * half + i]);
+      store_block_coalesced<OutT>(stage, w, block, col0 + 16 * half, n, rows_valid, lane);
     }
   }
 }
@@ -458,6 +528,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   __shared__ alignas(8) uint64_t bar_sf_full[STAGES];  // a stage's scale atoms have landed
   __shared__ alignas(8) uint64_t bar_peer_ready;  // every peer's pipeline memory is free
   __shared__ alignas(8) uint64_t bar_peer_data;   // every peer's partial columns have arrived
+  __shared__ alignas(16) uint8_t epi_stage[4][2048];  // per epilogue warp: 32 rows x 64 bytes
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int epi_last_flag;
@@ -796,6 +867,10 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       const int n0 = s.n_tile * Cfg::OUT_BN;
       OutT* out_row = reinterpret_cast<OutT*>(pd.d) +
                       (static_cast<long long>(s.batch) * pd.m + grow) * pd.n;
+      // First row of this warp's 32 rows, and how many of them exist.
+      OutT* out_block = out_row - static_cast<long long>(lane) * pd.n;
+      const int rows_valid = pd.m - (grow - lane);
+      const uint32_t stage_smem = smem_u32(&epi_stage[quarter][0]);
       const bool whole = (s.k0 == 0 && s.k1 == pd.k_tiles);
 
       if (whole) {
@@ -823,8 +898,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bar_acc_empty[acc]));
           }
-          if (grow < pd.m && !NVFP4_PROBE_FLAG(p, 11)) {
-            store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+          if (!NVFP4_PROBE_FLAG(p, 11)) {
+            store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
+                                   rows_valid, lane, v);
           }
         }
       } else if (p.split > 1) {
@@ -905,7 +981,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                 v[i] = s1[i] * alpha;
               }
             }
-            if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+            store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
+                                   rows_valid, lane, v);
           }
         }
         tc_fence_before_sync();
