@@ -242,11 +242,11 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
   if (schedule == 3 && split < 2) schedule = 0;
   if (schedule != 1 && schedule != 2 && schedule != 3) {
     // Pick the schedule with the smallest estimated time. Measured on B200: a k-tile step
-    // of one CTA takes about 0.5 us with 128-column tiles (0.8 us with 256) once the
+    // of one CTA takes about 0.4 us with 128-column tiles (0.55 us with 256) once the
     // pipeline is full, whatever the schedule; finishing split tiles through the
     // workspace costs about 8 us at the end of the kernel, through a cluster's shared
     // memory about 2.5 us.
-    const double step_us = plan->tile_n > 128 ? 0.8 : 0.5;
+    const double step_us = plan->tile_n > 128 ? 0.55 : 0.4;
     const double k_per_tile = static_cast<double>(units) / static_cast<double>(tiles);
     const long long waves = (tiles + sms - 1) / sms;
     const double t_whole = static_cast<double>(waves) * k_per_tile * step_us;

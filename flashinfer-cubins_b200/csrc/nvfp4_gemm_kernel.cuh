@@ -419,7 +419,9 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
                                                uint32_t staging, uint32_t bar_ready,
                                                uint32_t bar_data, volatile int* abort_ptr,
                                                float alpha, int row, int epi_tid, int grow,
-                                               typename Cfg::OutT* out_row) {
+                                               typename Cfg::OutT* out_row,
+                                               typename Cfg::OutT* out_block, int rows_valid,
+                                               uint32_t store_stage) {
   using OutT = typename Cfg::OutT;
   // The dual GEMM keeps two accumulators side by side (h1 in columns [0, OUT_BN), h2 in
   // [OUT_BN, 2 * OUT_BN)); an owner of output columns needs both halves of them.
@@ -506,7 +508,13 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
         v[i] = sum[0][i] * alpha;
       }
     }
-    if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+    if constexpr (Cfg::DUAL) {
+      // Two accumulators are live here; the staged store on top of them spills.
+      if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+    } else {
+      store_warp_chunk<OutT>(store_stage, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
+                             rows_valid, row & 31, v);
+    }
   }
 }
 
@@ -903,10 +911,10 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                                    rows_valid, lane, v);
           }
         }
-      } else if (p.split > 1) {
+      } else if (!Cfg::GROUPED && p.split > 1) {  // grouped plans never split in clusters
         cluster_reduce<Cfg>(p, pd, s, taddr, smem_base, smem_u32(&bar_peer_ready),
                             smem_u32(&bar_peer_data), abort_ptr, alpha, row, epi_tid, grow,
-                            out_row);
+                            out_row, out_block, rows_valid, stage_smem);
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bar_acc_empty[acc]));
       } else {
