@@ -14,10 +14,13 @@
 //               (cp.async.bulk.tensor ... .cta_group::2), which the leader arms for the
 //               bytes of both.
 //   warps 6-9   scale movers: this CTA's scale atoms -> this CTA's tensor memory; the
-//               peer's movers arrive on the leader's barrier through shared::cluster.
+//               movers of both CTAs arrive on the leader's full barrier (shared::cluster),
+//               so a stage is full after nine arrivals: the leader's producer + 8 movers.
 //   warp 1      leader CTA only: issues the MMAs (M = 256, N = 256, K = 64 each); its
 //               tcgen05.commit is multicast to both CTAs' barriers.
-//   warps 2-5   epilogue: each CTA stores its own 128 rows of the tile.
+//   warps 2-5   epilogue: each CTA stores its own 128 rows of the tile, coalesced through
+//               shared memory as in the single-CTA kernel.
+// The producer and MMA warps run their loops with all lanes and elect one to issue.
 // Tiles are dealt round-robin to the pairs (data parallel, persistent). The accumulator
 // (256 columns) is single-buffered; 5 stages of 38 KB.
 #pragma once
@@ -101,12 +104,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
   using OutT = typename Cfg::OutT;
 
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ alignas(8) uint64_t bar_full[STAGES];     // used in the leader: A/B of both CTAs
+  __shared__ alignas(8) uint64_t bar_full[STAGES];     // leader: A/B + scales of both CTAs
   __shared__ alignas(8) uint64_t bar_empty[STAGES];    // each CTA: stage may be refilled
   __shared__ alignas(8) uint64_t bar_sf_full[STAGES];  // each CTA: own scale atoms landed
-  __shared__ alignas(8) uint64_t bar_scales[STAGES];   // leader: scales of both CTAs in TMEM
   __shared__ alignas(8) uint64_t bar_acc_full;         // each CTA: tile accumulated
   __shared__ alignas(8) uint64_t bar_acc_empty;        // leader: both epilogues have drained
+  __shared__ alignas(16) uint8_t epi_stage[4][2048];   // per epilogue warp: 32 rows x 64 bytes
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -119,10 +122,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_full[s]), 9);
       mbar_init(smem_u32(&bar_empty[s]), 1);
       mbar_init(smem_u32(&bar_sf_full[s]), 1);
-      mbar_init(smem_u32(&bar_scales[s]), 8);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
     mbar_init(smem_u32(&bar_acc_empty), 256);
@@ -161,10 +163,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
+    {
       const uint64_t pol = l2_policy_evict_last();
-      prefetch_tensormap(&p.map_a);
-      prefetch_tensormap(&p.map_b);
+      if (elect_one()) {
+        prefetch_tensormap(&p.map_a);
+        prefetch_tensormap(&p.map_b);
+      }
       const uint32_t leader_full0 = cluster_map_shared(smem_u32(&bar_full[0]), 0);
       const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
       const uint32_t empty0 = smem_u32(&bar_empty[0]);
@@ -201,20 +205,24 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           const uint32_t sfa_dst = b_dst + Cfg::B_BYTES;
           const uint32_t sfb_dst = sfa_dst + Cfg::SFA_BYTES;
           const uint32_t sf_bar = sf_full0 + 8 * stage;
-          mbar_expect_tx(sf_bar, sf_bytes * ((sfa_valid ? 1u : 0u) + 1u + (sfb1_valid ? 1u : 0u)));
-          if (sfa_valid) bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol);
-          bulk_load(sfb_dst, sfb_src0, sf_bytes, sf_bar, pol);
-          if (sfb1_valid) bulk_load(sfb_dst + 2048, sfb_src1, sf_bytes, sf_bar, pol);
-          // The leader arms its full barrier for the A and B bytes of both CTAs.
-          if (NVFP4_PROBE_FLAG(p, 2)) {
-            if (leader) mbar_arrive(smem_u32(&bar_full[stage]));
-          } else {
-            if (leader) {
-              mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
+          if (elect_one()) {
+            mbar_expect_tx(sf_bar,
+                           sf_bytes * ((sfa_valid ? 1u : 0u) + 1u + (sfb1_valid ? 1u : 0u)));
+            if (sfa_valid) bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol);
+            bulk_load(sfb_dst, sfb_src0, sf_bytes, sf_bar, pol);
+            if (sfb1_valid) bulk_load(sfb_dst + 2048, sfb_src1, sf_bytes, sf_bar, pol);
+            // The leader arms its full barrier for the A and B bytes of both CTAs.
+            if (NVFP4_PROBE_FLAG(p, 2)) {
+              if (leader) mbar_arrive(smem_u32(&bar_full[stage]));
+            } else {
+              if (leader) {
+                mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
+              }
+              tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
+              tma_load_3d_pair(b_dst, &p.map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
             }
-            tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
-            tma_load_3d_pair(b_dst, &p.map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
           }
+          __syncwarp();
           sfa_src += 2048;
           sfb_src0 += 2048;
           sfb_src1 += 2048;
@@ -234,7 +242,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader)
-    if (lane == 0 && leader) {
+    if (leader) {
       constexpr uint32_t idesc = nvf4_instr_desc(256, 256);
       constexpr uint32_t kHiOperand = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t kStage16 = Cfg::STAGE_BYTES >> 4;
@@ -242,7 +250,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
       const uint32_t lo_b0 = lo_a0 + (Cfg::A_BYTES >> 4);
       const uint32_t full0 = smem_u32(&bar_full[0]);
       const uint32_t empty0 = smem_u32(&bar_empty[0]);
-      const uint32_t scales0 = smem_u32(&bar_scales[0]);
       int stage = 0;
       uint32_t phase = 0;
       uint32_t stage16 = 0;
@@ -258,8 +265,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         int atoms_left = pd.sf_kb;
         uint32_t accumulate = 0;
         for (int kt = 0; kt < pd.k_tiles; ++kt) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr) ||
-              !mbar_wait(scales0 + 8 * stage, phase, abort_ptr)) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusMmaInputTimeout);
             ok = false;
             break;
@@ -267,15 +273,27 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           tc_fence_after_sync();
           const uint32_t lo_a = lo_a0 + stage16;
           const uint32_t lo_b = lo_b0 + stage16;
-          const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
-          for (int j = 0; j < mmas; ++j) {
-            tc_mma_nvf4_pair(tmem_base, pack_desc(lo_a + 2 * j, kHiOperand),
-                             pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
-                             t_sf + 16 + 8 * j, j > 0 ? 1u : accumulate);
+          if (elect_one()) {
+            if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 1)) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                tc_mma_nvf4_pair(tmem_base, pack_desc(lo_a + 2 * j, kHiOperand),
+                                 pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
+                                 t_sf + 16 + 8 * j, j > 0 ? 1u : accumulate);
+              }
+            } else {
+              const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
+              for (int j = 0; j < mmas; ++j) {
+                tc_mma_nvf4_pair(tmem_base, pack_desc(lo_a + 2 * j, kHiOperand),
+                                 pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
+                                 t_sf + 16 + 8 * j, j > 0 ? 1u : accumulate);
+              }
+            }
+            tc_commit_pair(empty0 + 8 * stage, 3);
           }
+          __syncwarp();
           accumulate = 1;
           atoms_left -= 4;
-          tc_commit_pair(empty0 + 8 * stage, 3);
           stage16 += kStage16;
           t_sf += Cfg::SF_STAGE_COLS;
           if (++stage == STAGES) {
@@ -286,7 +304,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           }
         }
         if (!ok) break;
-        tc_commit_pair(smem_u32(&bar_acc_full), 3);
+        if (elect_one()) tc_commit_pair(smem_u32(&bar_acc_full), 3);
+        __syncwarp();
         acc_phase ^= 1u;
       }
     }
@@ -294,7 +313,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
     // ------------------------------------------------------------------ scale movers
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
-    const uint32_t leader_scales0 = cluster_map_shared(smem_u32(&bar_scales[0]), 0);
+    const uint32_t leader_full0 = cluster_map_shared(smem_u32(&bar_full[0]), 0);
     const uint32_t row_off = static_cast<uint32_t>(lane) * 16u;
     int stage = 0;
     uint32_t phase = 0;
@@ -319,12 +338,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
             vb0[j] = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 512 * j + row_off);
             vb1[j] = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 + 512 * j + row_off);
           }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            tmem_store_4(t_sf + 4 * j, va[j]);
-            tmem_store_4(t_sf + 16 + 8 * j, vb0[j]);
-            tmem_store_4(t_sf + 16 + 8 * j + 4, vb1[j]);
-          }
+          // 48 contiguous columns: A's k-blocks at 4j, B's at 16 + 8j (+4 for atom row 1).
+          tmem_store_16(t_sf, va[0], va[1], va[2], va[3]);
+          tmem_store_16(t_sf + 16, vb0[0], vb1[0], vb0[1], vb1[1]);
+          tmem_store_16(t_sf + 32, vb0[2], vb1[2], vb0[3], vb1[3]);
         } else {
           for (int j = 0; j < atoms; ++j) {
             tmem_store_4(t_sf + 4 * j, ld_shared_v4(sf_smem + 512 * j + row_off));
@@ -337,7 +354,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         tmem_store_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_peer(leader_scales0 + 8 * stage);
+        if (lane == 0) mbar_arrive_peer(leader_full0 + 8 * stage);
         atoms_left -= 4;
         sf_smem += Cfg::STAGE_BYTES;
         t_sf += Cfg::SF_STAGE_COLS;
@@ -369,6 +386,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
       const int n0 = n_tile * 256;
       OutT* out_row = reinterpret_cast<OutT*>(pd.d) +
                       (static_cast<long long>(batch) * pd.m + grow) * pd.n;
+      OutT* out_block = out_row - static_cast<long long>(lane) * pd.n;
+      const int rows_valid = pd.m - (grow - lane);
+      const uint32_t stage_smem = smem_u32(&epi_stage[quarter][0]);
       if constexpr (sizeof(OutT) == 2) {
         // Read the whole row out of tensor memory first (packed to FP16: 128 registers),
         // hand the accumulator back to the MMA issuer, then store: the next tile's MMAs
@@ -388,19 +408,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         }
         tc_fence_before_sync();
         mbar_arrive_peer(leader_acc_empty);
-        if (grow < pd.m) {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = n0 + c * 32 + 8 * g;
-              if (col < pd.n) {
-                *reinterpret_cast<uint4*>(out_row + col) = make_uint4(
-                    packed[c][4 * g], packed[c][4 * g + 1], packed[c][4 * g + 2],
-                    packed[c][4 * g + 3]);
-              }
-            }
-          }
+        for (int c = 0; c < 8; ++c) {
+          store_block_coalesced<OutT>(stage_smem, packed[c], out_block, n0 + c * 32, pd.n,
+                                      rows_valid, lane);
         }
       } else {
 #pragma unroll 1
@@ -415,7 +426,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
             tc_fence_before_sync();
             mbar_arrive_peer(leader_acc_empty);
           }
-          if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
+          store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
+                                 rows_valid, lane, v);
         }
       }
       acc_phase ^= 1u;
