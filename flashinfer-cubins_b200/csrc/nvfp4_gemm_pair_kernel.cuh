@@ -328,7 +328,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           ok = false;
           break;
         }
-        const int atoms = min(4, atoms_left);
+        const int atoms = NVFP4_PROBE_FLAG(p, 13) ? 0 : min(4, atoms_left);
+        if (NVFP4_PROBE_FLAG(p, 14)) {  // timing experiment: signal before the work
+          __syncwarp();
+          if (lane == 0) mbar_arrive_peer(leader_full0 + 8 * stage);
+        }
         if (atoms == 4) {
           // All twelve loads first, then the twelve stores: the loads overlap.
           uint4 va[4], vb0[4], vb1[4];
@@ -354,7 +358,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         tmem_store_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_peer(leader_full0 + 8 * stage);
+        if (lane == 0 && !NVFP4_PROBE_FLAG(p, 14)) mbar_arrive_peer(leader_full0 + 8 * stage);
         atoms_left -= 4;
         sf_smem += Cfg::STAGE_BYTES;
         t_sf += Cfg::SF_STAGE_COLS;
