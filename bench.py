@@ -56,7 +56,7 @@ L2_BYTES = 126 << 20
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-shape launch, from the ncu
 # capture summarised in profiles/nvfp4_gemm_decode_m128_n7168_k16384.md.
-DECODE_DRAM_TRAFFIC_BYTES = 68_225_024
+DECODE_DRAM_TRAFFIC_BYTES = 68_483_328
 
 
 def algorithmic_work(kind: str, shape: dict) -> tuple[float, float]:
