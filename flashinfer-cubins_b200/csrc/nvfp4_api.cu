@@ -157,6 +157,12 @@ KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
       case 128: return make_choice<GemmConfig<128, false, __half, true>>();
       case 256: return make_choice<GemmConfig<256, false, __half, true>>();
     }
+  } else if (out_kind == NVFP4_OUT_FP4) {
+    switch (tile_n) {
+      case 64: return make_choice<GemmConfig<64, false, Fp4Out, false>>();
+      case 128: return make_choice<GemmConfig<128, false, Fp4Out, false>>();
+      case 256: return make_choice<GemmConfig<256, false, Fp4Out, false>>();
+    }
   } else if (out_kind == NVFP4_OUT_F16) {
     switch (tile_n) {
       case 64: return make_choice<GemmConfig<64, false, __half, false>>();
@@ -437,13 +443,28 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
                       int l, const nvfp4_config* config) {
   if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
   *out = nullptr;
-  if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32) {
+  if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32 && out_kind != NVFP4_OUT_FP4) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "unknown output kind %d", out_kind);
+  }
+  if (out_kind == NVFP4_OUT_FP4 && (kind != kDense || n % 64 != 0)) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE,
+                "NVFP4 output needs a dense GEMM with n a multiple of 64 (whole scale atoms)");
   }
   // The fused dual GEMM also takes n % 8 == 4 (8-byte aligned FP16 rows), because its
   // FP32-output stage does.
   if (int rc = check_dense_shape(m, n, k, l, (out_kind == NVFP4_OUT_F16 && kind != kDual) ? 2 : 4)) {
     return rc;
+  }
+  // The NVFP4-output epilogue quantises whole rows of a finished tile: such plans keep
+  // every tile's K in one CTA (data parallel, single-CTA kernel).
+  nvfp4_config whole_tiles = {};
+  if (out_kind == NVFP4_OUT_FP4) {
+    if (config != nullptr) whole_tiles = *config;
+    if (whole_tiles.pair > 0 || whole_tiles.schedule > 1) {
+      return fail(NVFP4_E_INVALID_ARGUMENT, "NVFP4 output supports the data-parallel schedule only");
+    }
+    whole_tiles.schedule = 1;
+    config = &whole_tiles;
   }
   int sms = 0;
   if (int rc = check_device(device, &sms)) return rc;
@@ -468,6 +489,7 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     const long long pair_tiles = static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, 256) * l;
     int want_pair = config != nullptr ? config->pair : 0;
     if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
+    if (out_kind == NVFP4_OUT_FP4) want_pair = -1;
     const bool explicit_choice =
         (config != nullptr && (config->tile_n > 0 || config->schedule > 0 || config->ctas > 0)) ||
         env_int("NVFP4_TILE_N", 0) > 0 || env_int("NVFP4_SCHEDULE", 0) > 0 ||
@@ -610,21 +632,23 @@ int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info) {
   return 0;
 }
 
-int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
-                      const void* sfb, const float* alpha, void* d, void* workspace,
-                      void* stream) {
-  if (plan == nullptr || plan->kind != kDense) {
-    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dense GEMM plan");
-  }
+}  // extern "C"
+
+namespace {
+
+// The dense launch behind nvfp4_gemm_launch and nvfp4_gemm_launch_fp4 (`sfd` is null for
+// the former).
+int launch_dense(nvfp4_plan* plan, const void* a, const void* b, const void* sfa, const void* sfb,
+                 const float* alpha, void* d, void* sfd, void* workspace, void* stream) {
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || alpha == nullptr ||
       d == nullptr || workspace == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
   }
   if (!aligned(a, 16) || !aligned(b, 16) || !aligned(sfa, 16) || !aligned(sfb, 16) ||
-      !aligned(d, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
+      !aligned(d, 16) || !aligned(sfd, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
-  const void* now[8] = {a, b, nullptr, sfa, sfb, nullptr, alpha, d};
+  const void* now[8] = {a, b, nullptr, sfa, sfb, sfd, alpha, d};
   if (!plan->params_valid || plan->bound_ws != workspace ||
       std::memcmp(now, plan->bound, sizeof(now)) != 0) {
     ProblemDesc& pd = plan->problems[0];
@@ -639,6 +663,7 @@ int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void
     pd.sfb = static_cast<const uint8_t*>(sfb);
     pd.sfb2 = nullptr;
     pd.d = d;
+    pd.sfd = static_cast<uint8_t*>(sfd);
     kp.dense = pd;
     kp.alpha = alpha;
     fill_common_params(plan, kp, workspace);
@@ -647,6 +672,29 @@ int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void
     plan->params_valid = true;
   }
   return launch_plan(plan, plan->params, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                      const void* sfb, const float* alpha, void* d, void* workspace,
+                      void* stream) {
+  if (plan == nullptr || plan->kind != kDense || plan->out_kind == NVFP4_OUT_FP4) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dense GEMM plan with FP16 or FP32 output");
+  }
+  return launch_dense(plan, a, b, sfa, sfb, alpha, d, nullptr, workspace, stream);
+}
+
+int nvfp4_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                          const void* sfb, const float* alpha, void* d_packed, void* d_scales,
+                          void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kDense || plan->out_kind != NVFP4_OUT_FP4) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dense GEMM plan with NVFP4 output");
+  }
+  if (d_scales == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  return launch_dense(plan, a, b, sfa, sfb, alpha, d_packed, d_scales, workspace, stream);
 }
 
 // ---------------------------------------------------------------------------------------

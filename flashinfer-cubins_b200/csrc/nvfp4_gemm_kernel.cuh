@@ -36,6 +36,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "nvfp4_glue_kernels.cuh"
 #include "sm100_ptx.cuh"
 
 namespace nvfp4 {
@@ -51,7 +52,7 @@ struct alignas(16) ProblemDesc {
   int k_tiles;           // ceil(k / 256)
   int sf_kb;             // scale atoms along K: ceil(k / 64)
   int sf_mb, sf_nb;      // scale atom rows: ceil(m / 128), ceil(n / 128)
-  int pad0, pad1;
+  uint8_t* sfd;          // NVFP4 output: blocked UE4M3 scales of D (rows m, one per 16 columns)
   long long tile_begin;  // first global tile index of this problem
   long long unit_begin;  // first global (tile, k-tile) unit of this problem
 };
@@ -188,12 +189,17 @@ constexpr int const_pow2_at_least(int v) {
   return r;
 }
 
+// Output type tag: D quantised to NVFP4 in the epilogue (packed E2M1 + blocked UE4M3 scales,
+// one scale per 16 consecutive columns of a row), ready to be the A operand of the next GEMM.
+struct Fp4Out {};
+
 template <int BN_, bool DUAL_, typename OutT_, bool GROUPED_>
 struct GemmConfig {
   static constexpr int BN = BN_;  // MMA N; for the dual GEMM both B tiles side by side
   static constexpr bool DUAL = DUAL_;
   static constexpr bool GROUPED = GROUPED_;
   using OutT = OutT_;
+  static constexpr bool FP4_OUT = sizeof(OutT_) == 1;  // Fp4Out is the only one-byte tag
   static constexpr int BM = 128;
   static constexpr int OUT_BN = DUAL ? BN / 2 : BN;  // output columns per tile
   static constexpr int A_BYTES = BM * 128;           // 128 rows x 256 E2M1
@@ -930,7 +936,66 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       const uint32_t stage_smem = smem_u32(&epi_stage[quarter][0]);
       const bool whole = (s.k0 == 0 && s.k1 == pd.k_tiles);
 
-      if (whole) {
+      if constexpr (Cfg::FP4_OUT) {
+        // NVFP4 output (whole tiles only: such plans are data parallel). Per row and 16
+        // columns: scale = e4m3(amax / 6), codes = E2M1(v / scale) - the arithmetic of
+        // quantize_nvfp4_kernel, so the bytes equal quantising the FP32 result afterwards.
+        // A thread owns one row: 32 columns give 16 packed bytes, 64 columns give four
+        // scale bytes that are contiguous in the blocked layout.
+        uint8_t* d_row = static_cast<uint8_t*>(pd.d) +
+                         (static_cast<long long>(s.batch) * pd.m + grow) * (pd.n / 2);
+        const int sf_cb = (pd.n + 63) / 64;
+        uint8_t* sf_row = pd.sfd +
+                          (static_cast<long long>(s.batch) * pd.sf_mb + s.m_tile) * sf_cb * 512 +
+                          (row % 32) * 16 + ((row / 32) % 4) * 4;
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+          uint32_t scale_word = 0;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c = 2 * c2 + half;
+            uint32_t r1[32];
+            tmem_load_32(taddr + c * 32, r1);
+            tmem_load_wait();
+            if (c == BN / 32 - 1) {
+              tc_fence_before_sync();
+              mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+            }
+            uint32_t words[4];
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+              float amax = 0.0f;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                r1[16 * blk + i] = __float_as_uint(__uint_as_float(r1[16 * blk + i]) * alpha);
+                amax = fmaxf(amax, fabsf(__uint_as_float(r1[16 * blk + i])));
+              }
+              const uint32_t bits = nvfp4_scale_bits(amax);
+              const float scale = nvfp4_scale_value(bits);
+              scale_word |= bits << (8 * (2 * half + blk));
+              uint32_t w0 = 0, w1 = 0;
+              if (scale > 0.0f) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  w0 |= e2m1_code(__fdiv_rn(__uint_as_float(r1[16 * blk + i]), scale)) << (4 * i);
+                  w1 |= e2m1_code(__fdiv_rn(__uint_as_float(r1[16 * blk + 8 + i]), scale))
+                        << (4 * i);
+                }
+              }
+              words[2 * blk] = w0;
+              words[2 * blk + 1] = w1;
+            }
+            if (grow < pd.m && n0 + c * 32 < pd.n) {
+              *reinterpret_cast<uint4*>(d_row + (n0 + c * 32) / 2) =
+                  make_uint4(words[0], words[1], words[2], words[3]);
+            }
+          }
+          if (grow < pd.m && n0 + c2 * 64 < pd.n) {
+            *reinterpret_cast<uint32_t*>(sf_row + static_cast<long long>((n0 + c2 * 64) / 64) * 512) =
+                scale_word;
+          }
+        }
+      } else if (whole) {
 #pragma unroll 1
         for (int c = 0; c < Cfg::OUT_BN / 32; ++c) {
           uint32_t r1[32];

@@ -64,6 +64,18 @@ __device__ __forceinline__ uint32_t e2m1_code(float v) {
   return code;
 }
 
+// UE4M3 bits of the scale of a 16-element block with the given absolute maximum:
+// amax / 6 rounded to nearest even, saturating at 448.
+__device__ __forceinline__ uint32_t nvfp4_scale_bits(float amax) {
+  return static_cast<uint32_t>(
+      __nv_cvt_float_to_fp8(fminf(__fdiv_rn(amax, 6.0f), 448.0f), __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float nvfp4_scale_value(uint32_t bits) {
+  return __half2float(
+      __half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(bits), __NV_E4M3)));
+}
+
 // FP32/BF16 [batches][rows][k] -> packed E2M1 [batches][rows][k/2] and UE4M3 scales in the
 // blocked layout [batches][rb][cb][32][4][4] (zero padded), one thread per 16-element block
 // of the padded scale grid: scale = e4m3(amax / 6) (round to nearest even, saturating),
@@ -117,10 +129,9 @@ __global__ void quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restr
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    const uint8_t scale_bits = static_cast<uint8_t>(
-        __nv_cvt_float_to_fp8(fminf(__fdiv_rn(amax, 6.0f), 448.0f), __NV_SATFINITE, __NV_E4M3));
-    *scale_out = scale_bits;
-    const float scale = __half2float(__half(__nv_cvt_fp8_to_halfraw(scale_bits, __NV_E4M3)));
+    const uint32_t scale_bits = nvfp4_scale_bits(amax);
+    *scale_out = static_cast<uint8_t>(scale_bits);
+    const float scale = nvfp4_scale_value(scale_bits);
     uint32_t words[2] = {0u, 0u};
     if (scale > 0.0f) {
 #pragma unroll

@@ -31,6 +31,7 @@ E_SCRATCH_TOO_LARGE = -7
 
 OUT_F16 = 0
 OUT_F32 = 1
+OUT_FP4 = 2
 
 SCHEDULE_NAMES = {1: "data_parallel", 2: "stream_k", 3: "cluster_split_k"}
 
@@ -89,6 +90,7 @@ _PROTOTYPES = {
     "nvfp4_plan_init_workspace": (ctypes.c_int, [_P, _P, _P]),
     "nvfp4_plan_info_get": (ctypes.c_int, [_P, ctypes.POINTER(PlanInfo)]),
     "nvfp4_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "nvfp4_gemm_launch_fp4": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_gemm_launch_static": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_static_scratch_bytes": (ctypes.c_size_t, []),
     "nvfp4_dual_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
@@ -221,6 +223,11 @@ class Plan:
 
     def launch_dense(self, a, b, sfa, sfb, alpha, d, workspace, stream) -> None:
         check(load().nvfp4_gemm_launch(self.handle, a, b, sfa, sfb, alpha, d, workspace, stream))
+
+    def launch_dense_fp4(self, a, b, sfa, sfb, alpha, d_packed, d_scales, workspace, stream) -> None:
+        """Dense launch of a plan made with ``OUT_FP4``: D quantised to NVFP4 in the epilogue."""
+        check(load().nvfp4_gemm_launch_fp4(
+            self.handle, a, b, sfa, sfb, alpha, d_packed, d_scales, workspace, stream))
 
     def launch_dense_static(self, a, b, sfa, sfb, alpha, d, stream) -> None:
         """Dense launch on the library's built-in scratch array: for callers that may

@@ -214,3 +214,45 @@ def quantize_nvfp4_native(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
                         packed.data_ptr(), blocked.data_ptr(), rows, k, batches,
                         torch.cuda.current_stream(x.device).cuda_stream)
     return packed.permute(1, 2, 0), blocked
+
+
+_FP4_OUT_PLANS: dict = {}
+
+
+def fp4_matmul_quantized_native(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor,
+                                sfb: torch.Tensor, alpha: torch.Tensor
+                                ) -> tuple[torch.Tensor, torch.Tensor]:
+    """``alpha * A @ B^T`` quantised to NVFP4 in the GEMM's epilogue (``nvfp4_gemm_launch_fp4``):
+    the same bytes as ``quantize_nvfp4_native`` applied to the FP32 product, without writing
+    the product to memory. ``a`` ``(m, k/2, l)`` and ``b`` ``(n, k/2, l)`` are packed E2M1
+    views of contiguous ``(l, rows, k/2)`` storage, ``sfa`` / ``sfb`` their scales in the
+    blocked layout (any shape, contiguous), ``alpha`` a one-element FP32 CUDA tensor.
+    Returns packed D ``(m, n/2, l)`` and D's blocked scales ``(l, ceil(m/128), n/64, 32, 4, 4)``;
+    ``n`` must be a multiple of 64. Rows of the last scale atom row beyond ``m`` are zero."""
+    from .. import native
+
+    m, half_k, batches = a.shape
+    n = b.shape[0]
+    if a.device.type != "cuda" or n % 64 or b.shape[1] != half_k or b.shape[2] != batches:
+        raise ValueError("expected CUDA operands with equal k and l, and n a multiple of 64")
+    for t in (a, b):
+        if t.dtype != torch.uint8 or not t.permute(2, 0, 1).is_contiguous():
+            raise ValueError("expected packed uint8 (rows, k/2, l) views of (l, rows, k/2) storage")
+    device = a.device
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, m, n, 2 * half_k, batches)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        if key not in _FP4_OUT_PLANS:
+            plan = native.Plan.dense(index, native.OUT_FP4, m, n, 2 * half_k, batches)
+            workspace = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=device)
+            plan.init_workspace(workspace.data_ptr(), stream)
+            _FP4_OUT_PLANS[key] = (plan, workspace)
+        plan, workspace = _FP4_OUT_PLANS[key]
+        packed = torch.empty((batches, m, n // 2), dtype=torch.uint8, device=device)
+        scales = torch.zeros((batches, ceil_div(m, SF_ROWS), n // 64, 32, 4, 4),
+                             dtype=torch.uint8, device=device)
+        plan.launch_dense_fp4(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                              alpha.data_ptr(), packed.data_ptr(), scales.data_ptr(),
+                              workspace.data_ptr(), stream)
+    return packed.permute(1, 2, 0), scales.view(torch.float8_e4m3fn)

@@ -45,6 +45,7 @@ extern "C" {
 /* Output/element kinds of a plan. */
 #define NVFP4_OUT_F16 0 /* nvfp4_gemm: FP16 D (harness/workloads/nvfp4_gemm.py:511-530) */
 #define NVFP4_OUT_F32 1 /* nvfp4_dual_gemm_gemm: FP32 D (nvfp4_dual_gemm.py:172-188) */
+#define NVFP4_OUT_FP4 2 /* D quantised to NVFP4 in the epilogue; launched by nvfp4_gemm_launch_fp4 */
 
 /* Optional tuning overrides; zero/negative fields mean "choose automatically". */
 typedef struct nvfp4_config {
@@ -122,6 +123,18 @@ int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info);
 int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                       const void* sfb, const float* alpha, void* d, void* workspace,
                       void* stream);
+
+/* Dense GEMM whose output is quantised to NVFP4 in the epilogue, so that it can be the A
+ * operand of the next GEMM without an FP16 round trip (plan created with NVFP4_OUT_FP4;
+ * n % 64 == 0; data-parallel schedule). The reference has no such kernel on this path: its
+ * NVFP4 convention for a quantised tensor (scale = e4m3(amax / 6) per 16 elements, RNE
+ * E2M1 codes, blocked scales: harness/workloads/quantization.py:66-116 and 39-63) is what
+ * the bytes follow. `d_packed` is [l][m][n/2] bytes, `d_scales` the blocked layout
+ * [l][ceil(m/128)][n/64][32][4][4]; rows beyond m in the last atom row are not written.
+ * The result equals nvfp4_quantize applied to the FP32 product alpha * A * B^T. */
+int nvfp4_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                          const void* sfb, const float* alpha, void* d_packed, void* d_scales,
+                          void* workspace, void* stream);
 
 /* The dense launch for callers that must not allocate device memory where they call
  * this library (a runtime whose own pool owns all of HBM, a plugin under a foreign

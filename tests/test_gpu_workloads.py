@@ -359,3 +359,82 @@ def test_quantiser_kernel_matches_torch_quantiser_bytes(rows, k, batches, dtype)
         o_packed, o_scales = o.quantize_nvfp4(host)
         assert np.array_equal(packed.permute(2, 0, 1).cpu().numpy(), o_packed)
         assert np.array_equal(blocked.view(torch.uint8).cpu().numpy(), o.to_blocked(o_scales))
+
+
+def _fp4_out_inputs(m, n, k, batches, scales, seed):
+    from harness.workloads import quantization as q
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    g = torch.Generator(device=workload.device).manual_seed(seed)
+    a, sa = q.make_fp4(workload, g, m, k, batches, scales=scales)
+    b, sb = q.make_fp4(workload, g, n, k, batches, scales=scales)
+    return a, b, sa, sb
+
+
+@pytest.mark.parametrize("m,n,k,batches", [(128, 256, 512, 1), (200, 192, 96, 2), (1, 64, 32, 1),
+                                           (384, 1024, 1024, 1)])
+@pytest.mark.parametrize("tile_n", (0, 64, 256))
+def test_gemm_with_nvfp4_output_equals_quantised_fp32_product(m, n, k, batches, tile_n):
+    """Dense GEMM whose epilogue quantises D to NVFP4: with integer scales every FP32 sum is
+    exact, so packed codes and blocked scale bytes must equal the oracle's quantiser applied
+    to the oracle's FP32 product, byte for byte (alpha a power of two)."""
+    from harness.workloads import quantization as q
+    a, b, sa, sb = _fp4_out_inputs(m, n, k, batches, "int0_3", seed=m + n + k)
+    alpha = torch.tensor([0.015625], dtype=torch.float32, device=a.device)
+    sfa, sfb = q.to_blocked_scales(sa), q.to_blocked_scales(sb)
+    if tile_n:
+        plan = native.Plan.dense(0, native.OUT_FP4, m, n, k, batches, tile_n=tile_n)
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=a.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        plan.init_workspace(ws.data_ptr(), stream)
+        packed = torch.empty((batches, m, n // 2), dtype=torch.uint8, device=a.device)
+        blocked = torch.zeros((batches, -(-m // 128), n // 64, 32, 4, 4), dtype=torch.uint8,
+                              device=a.device)
+        plan.launch_dense_fp4(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                              alpha.data_ptr(), packed.data_ptr(), blocked.data_ptr(),
+                              ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        assert plan.info()["tile_n"] == tile_n and plan.info()["schedule"] == "data_parallel"
+        packed = packed.permute(1, 2, 0)
+    else:
+        packed, blocked = q.fp4_matmul_quantized_native(a, b, sfa, sfb, alpha)
+        blocked = blocked.view(torch.uint8)
+    torch.cuda.synchronize()
+    want_packed, want_scales = o.gemm_quantized(
+        storage(a), storage(b), storage(sa), storage(sb), alpha=0.015625)
+    assert np.array_equal(packed.permute(2, 0, 1).cpu().numpy(), want_packed)
+    assert np.array_equal(blocked.cpu().numpy(), o.to_blocked(want_scales))
+
+
+def test_gemm_with_nvfp4_output_feeds_the_next_gemm():
+    """Two chained GEMMs, D1 = A @ B1^T quantised in the epilogue, D2 = D1q @ B2^T: the
+    second GEMM consumes the first one's packed output and blocked scales as they are.
+    Checked against the oracle run on the same quantised intermediate (bit-exact inputs to
+    the second GEMM because the first has integer scales), at the reference's tolerance."""
+    from harness.workloads import quantization as q
+    m, n1, k1, n2 = 256, 512, 256, 384
+    a, b1, sa, sb1 = _fp4_out_inputs(m, n1, k1, 1, "int0_3", seed=7)
+    alpha1 = torch.tensor([0.0078125], dtype=torch.float32, device=a.device)
+    d1, sfd1 = q.fp4_matmul_quantized_native(a, b1, q.to_blocked_scales(sa),
+                                             q.to_blocked_scales(sb1), alpha1)
+    workload = get_workload("nvfp4_gemm").from_arch("sm_100a", device="cuda")
+    g = torch.Generator(device=workload.device).manual_seed(8)
+    b2, sb2 = q.make_fp4(workload, g, n2, n1, 1)
+    one = torch.ones(1, dtype=torch.float32, device=a.device)
+    sfd1_task = sfd1.permute(3, 4, 1, 5, 2, 0)
+    sfb2_task = q.to_blocked_scales(sb2).permute(3, 4, 1, 5, 2, 0)
+    (d2,) = workload.run((d1, b2, sfd1_task, sfb2_task, one))
+    torch.cuda.synchronize()
+    p1, s1 = o.gemm_quantized(storage(a), storage(b1), storage(sa), storage(sb1), alpha=0.0078125)
+    assert np.array_equal(d1.permute(2, 0, 1).cpu().numpy(), p1)
+    want = o.gemm(p1, storage(b2), s1, storage(sb2), 1.0, np.float16)
+    assert_matches_oracle(d2, want, "chained", exact=False)
+
+
+def test_nvfp4_output_plan_rejects_what_it_cannot_do():
+    with pytest.raises(ValueError):
+        native.Plan.dense(0, native.OUT_FP4, 128, 96, 64, 1)      # n not a multiple of 64
+    with pytest.raises(ValueError):
+        native.Plan.dense(0, native.OUT_FP4, 128, 128, 64, 1, schedule=2)
+    plan = native.Plan.dense(0, native.OUT_F16, 128, 128, 64, 1)
+    with pytest.raises(ValueError):
+        plan.launch_dense_fp4(256, 256, 256, 256, 256, 256, 256, 256, 0)

@@ -155,3 +155,22 @@ def test_quantiser_matches_reference_convention():
     batched, batched_scales = q.quantize_nvfp4(torch.from_numpy(data["x"]).reshape(48, 256, 1))
     assert tuple(batched.shape) == (48, 128, 1) and tuple(batched_scales.shape) == (48, 16, 1)
     assert batched.permute(2, 0, 1).is_contiguous()
+
+
+def test_oracle_quantised_gemm_is_the_torch_quantiser_of_the_torch_product():
+    """The oracle of the GEMM with NVFP4 output composes two pinned pieces (the FP32 product
+    and the quantiser); the harness's torch versions of both give the same bytes."""
+    g = torch.Generator().manual_seed(5)
+
+    class Host:
+        device = torch.device("cpu")
+
+    a, sa = q.make_fp4(Host, g, 64, 128, 2, scales="int0_3")
+    b, sb = q.make_fp4(Host, g, 128, 128, 2, scales="int0_3")
+    product = q.fp4_matmul(a, b, sa, sb, alpha=0.25, out_dtype=torch.float32)
+    want_packed, want_scales = q.quantize_nvfp4(product)
+    store = lambda t: np.ascontiguousarray(  # noqa: E731
+        (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).permute(2, 0, 1).numpy())
+    packed, scales = o.gemm_quantized(store(a), store(b), store(sa), store(sb), alpha=0.25)
+    assert np.array_equal(packed, store(want_packed))
+    assert np.array_equal(scales, store(want_scales))
