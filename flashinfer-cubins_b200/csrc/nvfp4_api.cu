@@ -163,6 +163,12 @@ KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
       case 128: return make_choice<GemmConfig<128, false, Fp4Out, false>>();
       case 256: return make_choice<GemmConfig<256, false, Fp4Out, false>>();
     }
+  } else if (out_kind == NVFP4_OUT_BF16) {
+    switch (tile_n) {
+      case 64: return make_choice<GemmConfig<64, false, __nv_bfloat16, false>>();
+      case 128: return make_choice<GemmConfig<128, false, __nv_bfloat16, false>>();
+      case 256: return make_choice<GemmConfig<256, false, __nv_bfloat16, false>>();
+    }
   } else if (out_kind == NVFP4_OUT_F16) {
     switch (tile_n) {
       case 64: return make_choice<GemmConfig<64, false, __half, false>>();
@@ -353,8 +359,9 @@ int default_tile_n(const nvfp4_config* config, int fallback) {
 
 int prepare_kernel(nvfp4_plan* plan) {
   if (plan->pair) {
-    plan->kernel = plan->out_kind == NVFP4_OUT_F16 ? make_pair_choice<PairConfig<__half>>()
-                                                   : make_pair_choice<PairConfig<float>>();
+    plan->kernel = plan->out_kind == NVFP4_OUT_F16    ? make_pair_choice<PairConfig<__half>>()
+                   : plan->out_kind == NVFP4_OUT_BF16 ? make_pair_choice<PairConfig<__nv_bfloat16>>()
+                                                      : make_pair_choice<PairConfig<float>>();
   } else {
     plan->kernel = select_kernel(plan->kind, plan->out_kind, plan->tile_n);
   }
@@ -443,7 +450,8 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
                       int l, const nvfp4_config* config) {
   if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
   *out = nullptr;
-  if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32 && out_kind != NVFP4_OUT_FP4) {
+  if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32 && out_kind != NVFP4_OUT_FP4 &&
+      out_kind != NVFP4_OUT_BF16) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "unknown output kind %d", out_kind);
   }
   if (out_kind == NVFP4_OUT_FP4 && (kind != kDense || n % 64 != 0)) {
@@ -452,7 +460,8 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
   }
   // The fused dual GEMM also takes n % 8 == 4 (8-byte aligned FP16 rows), because its
   // FP32-output stage does.
-  if (int rc = check_dense_shape(m, n, k, l, (out_kind == NVFP4_OUT_F16 && kind != kDual) ? 2 : 4)) {
+  const bool two_byte_rows = (out_kind == NVFP4_OUT_F16 || out_kind == NVFP4_OUT_BF16) && kind != kDual;
+  if (int rc = check_dense_shape(m, n, k, l, two_byte_rows ? 2 : 4)) {
     return rc;
   }
   // The NVFP4-output epilogue quantises whole rows of a finished tile: such plans keep

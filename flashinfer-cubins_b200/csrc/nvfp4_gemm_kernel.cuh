@@ -33,6 +33,7 @@
 
 #include <cstdint>
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -189,6 +190,11 @@ constexpr int const_pow2_at_least(int v) {
   return r;
 }
 
+template <typename T>
+inline constexpr bool kIsBf16 = false;
+template <>
+inline constexpr bool kIsBf16<__nv_bfloat16> = true;
+
 // Output type tag: D quantised to NVFP4 in the epilogue (packed E2M1 + blocked UE4M3 scales,
 // one scale per 16 consecutive columns of a row), ready to be the A operand of the next GEMM.
 struct Fp4Out {};
@@ -248,6 +254,18 @@ __device__ __forceinline__ float silu_f32(float x) {
   return x * r;
 }
 
+// Two FP32 values rounded to nearest even into one 32-bit word of the 16-bit output type.
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  if constexpr (sizeof(OutT) == 2 && !kIsBf16<OutT>) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
 // Stores 32 consecutive output columns of one row in 16-byte pieces (8-byte pieces of
 // FP16 when n is only a multiple of 4, whose rows are 8-byte aligned), dropping the
 // pieces that start at or beyond column n (n is a multiple of the piece width).
@@ -259,15 +277,11 @@ __device__ __forceinline__ void store_row_chunk(OutT* row_ptr, int col0, int n,
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         if (col0 + 8 * g < n) {
-          __half2 h0 = __floats2half2_rn(v[8 * g + 0], v[8 * g + 1]);
-          __half2 h1 = __floats2half2_rn(v[8 * g + 2], v[8 * g + 3]);
-          __half2 h2 = __floats2half2_rn(v[8 * g + 4], v[8 * g + 5]);
-          __half2 h3 = __floats2half2_rn(v[8 * g + 6], v[8 * g + 7]);
           uint4 q;
-          q.x = *reinterpret_cast<uint32_t*>(&h0);
-          q.y = *reinterpret_cast<uint32_t*>(&h1);
-          q.z = *reinterpret_cast<uint32_t*>(&h2);
-          q.w = *reinterpret_cast<uint32_t*>(&h3);
+          q.x = pack_pair<OutT>(v[8 * g + 0], v[8 * g + 1]);
+          q.y = pack_pair<OutT>(v[8 * g + 2], v[8 * g + 3]);
+          q.z = pack_pair<OutT>(v[8 * g + 4], v[8 * g + 5]);
+          q.w = pack_pair<OutT>(v[8 * g + 6], v[8 * g + 7]);
           *reinterpret_cast<uint4*>(row_ptr + col0 + 8 * g) = q;
         }
       }
@@ -275,11 +289,9 @@ __device__ __forceinline__ void store_row_chunk(OutT* row_ptr, int col0, int n,
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
         if (col0 + 4 * g < n) {
-          __half2 h0 = __floats2half2_rn(v[4 * g + 0], v[4 * g + 1]);
-          __half2 h1 = __floats2half2_rn(v[4 * g + 2], v[4 * g + 3]);
           uint2 q;
-          q.x = *reinterpret_cast<uint32_t*>(&h0);
-          q.y = *reinterpret_cast<uint32_t*>(&h1);
+          q.x = pack_pair<OutT>(v[4 * g + 0], v[4 * g + 1]);
+          q.y = pack_pair<OutT>(v[4 * g + 2], v[4 * g + 3]);
           *reinterpret_cast<uint2*>(row_ptr + col0 + 4 * g) = q;
         }
       }
@@ -348,8 +360,7 @@ __device__ __forceinline__ void store_warp_chunk(uint32_t stage, OutT* block, Ou
     uint32_t w[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-      w[i] = *reinterpret_cast<uint32_t*>(&h);
+      w[i] = pack_pair<OutT>(v[2 * i], v[2 * i + 1]);
     }
     store_block_coalesced<OutT>(stage, w, block, col0, n, rows_valid, lane);
   } else {

@@ -405,9 +405,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           tmem_load_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            __half2 h = __floats2half2_rn(__uint_as_float(r1[2 * i]) * alpha,
-                                          __uint_as_float(r1[2 * i + 1]) * alpha);
-            packed[c][i] = *reinterpret_cast<uint32_t*>(&h);
+            packed[c][i] = pack_pair<OutT>(__uint_as_float(r1[2 * i]) * alpha,
+                                           __uint_as_float(r1[2 * i + 1]) * alpha);
           }
         }
         tc_fence_before_sync();

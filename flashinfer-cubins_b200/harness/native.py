@@ -32,6 +32,7 @@ E_SCRATCH_TOO_LARGE = -7
 OUT_F16 = 0
 OUT_F32 = 1
 OUT_FP4 = 2
+OUT_BF16 = 3
 
 SCHEDULE_NAMES = {1: "data_parallel", 2: "stream_k", 3: "cluster_split_k"}
 

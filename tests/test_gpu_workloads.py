@@ -16,8 +16,8 @@ from oracle import nvfp4_oracle as o
 
 pytestmark = pytest.mark.gpu
 
-WORKLOADS = ("nvfp4_gemm", "nvfp4_dual_gemm_gemm", "nvfp4_dual_gemm", "nvfp4_group_gemm",
-             "nvfp4_dual_gemm_pack_scales", "nvfp4_dual_gemm_silu_product")
+WORKLOADS = ("nvfp4_gemm", "nvfp4_gemm_bf16", "nvfp4_dual_gemm_gemm", "nvfp4_dual_gemm",
+             "nvfp4_group_gemm", "nvfp4_dual_gemm_pack_scales", "nvfp4_dual_gemm_silu_product")
 
 
 @pytest.fixture(scope="module", autouse=True)
@@ -51,6 +51,14 @@ def oracle_check(workload, case, inputs, out):
     exact = integer_scaled(case, default)
     if workload.name == "nvfp4_gemm":
         assert_matches_oracle(out[0], oracle_dense(inputs), name, exact and case.params.get("alpha", 1.0) == 1.0)
+    elif workload.name == "nvfp4_gemm_bf16":
+        want = o.round_to_bf16_bits(oracle_dense(inputs, np.float32))
+        got = out[0].permute(2, 0, 1).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        if integer_scaled(case, "int0_3") and case.params.get("alpha", 1.0) == 1.0:
+            assert np.array_equal(got, want), f"{name}: not bit-identical to the oracle"
+        else:
+            np.testing.assert_allclose(o.bf16_bits_to_float(got), o.bf16_bits_to_float(want),
+                                       rtol=8e-3, atol=1e-3, err_msg=name)
     elif workload.name == "nvfp4_dual_gemm_gemm":
         a, b, sfa, sfb, alpha = inputs
         m, half_k, batches = a.shape
