@@ -45,8 +45,9 @@ extern "C" {
 /* Output/element kinds of a plan. */
 #define NVFP4_OUT_F16 0 /* nvfp4_gemm: FP16 D (harness/workloads/nvfp4_gemm.py:511-530) */
 #define NVFP4_OUT_F32 1 /* nvfp4_dual_gemm_gemm: FP32 D (nvfp4_dual_gemm.py:172-188) */
-#define NVFP4_OUT_BF16 3 /* BF16 D (the output type of FlashInfer's mm_fp4 path: harness/workloads/batched_gemm/__init__.py:3-7); launched by nvfp4_gemm_launch */
 #define NVFP4_OUT_FP4 2 /* D quantised to NVFP4 in the epilogue; launched by nvfp4_gemm_launch_fp4 */
+#define NVFP4_OUT_BF16 3 /* BF16 D, the output type of FlashInfer's mm_fp4 path
+                            (harness/workloads/batched_gemm/__init__.py:3-7); nvfp4_gemm_launch */
 
 /* Optional tuning overrides; zero/negative fields mean "choose automatically". */
 typedef struct nvfp4_config {

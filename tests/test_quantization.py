@@ -174,3 +174,13 @@ def test_oracle_quantised_gemm_is_the_torch_quantiser_of_the_torch_product():
     packed, scales = o.gemm_quantized(store(a), store(b), store(sa), store(sb), alpha=0.25)
     assert np.array_equal(packed, store(want_packed))
     assert np.array_equal(scales, store(want_scales))
+
+
+def test_oracle_bf16_rounding_matches_torch():
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal(200_000) * 10.0 ** rng.integers(-20, 20, 200_000)).astype(np.float32)
+    x[:6] = [np.inf, -np.inf, 0.0, -0.0, 1.00390625, 1.01171875]  # the last two are ties
+    want = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(o.round_to_bf16_bits(x), want)
+    assert np.array_equal(o.bf16_bits_to_float(want),
+                          torch.from_numpy(x).to(torch.bfloat16).float().numpy())
