@@ -198,6 +198,7 @@ struct nvfp4_plan {
   int ctas = 1;
   int split = 1;      // cluster size of schedule 3
   bool pair = false;  // 2-CTA kernel: 256 x 256 tiles, one cluster of two CTAs per tile
+  double estimate_us = 0.0;  // the time model's figure for the chosen schedule (mainloop + tail)
   KernelChoice kernel{};
   std::vector<ProblemDesc> problems;  // pointers filled at launch / bind
   long long total_tiles = 0, total_units = 0;
@@ -217,6 +218,39 @@ int env_int(const char* name, int fallback) {
   const char* v = std::getenv(name);
   if (v == nullptr || *v == '\0') return fallback;
   return std::atoi(v);
+}
+
+// Time of one k-tile step of one CTA in microseconds by tile width (see finish_schedule).
+double kStepUs(int tile_n) { return tile_n <= 64 ? 0.30 : tile_n <= 128 ? 0.38 : 0.52; }
+constexpr double kPairStepUs = 0.44;  // a CTA of a pair on its half of a 256 x 256 tile
+
+// How many clusters of `size` CTAs of this kernel the device can hold at once (0 if the
+// query fails). Clusters must fit inside one GPC, so this is less than SMs / size.
+int max_active_clusters(const KernelChoice& kernel, int size) {
+  if (kernel.fn == nullptr) return 0;
+  const void* fn = reinterpret_cast<const void*>(kernel.fn);
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kernel.smem_bytes) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = static_cast<unsigned int>(size);
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  cudaLaunchConfig_t launch = {};
+  launch.gridDim = dim3(static_cast<unsigned int>(size), 1, 1);
+  launch.blockDim = dim3(static_cast<unsigned int>(kernel.threads), 1, 1);
+  launch.dynamicSmemBytes = static_cast<size_t>(kernel.smem_bytes);
+  launch.attrs = &attribute;
+  launch.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, fn, &launch) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return clusters;
 }
 
 // Tile width, schedule and grid for a list of problems whose tile counts are already
@@ -247,36 +281,56 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
   if (plan->kind != kGrouped && plan->problems.size() == 1 && tiles < sms) {
     const int k_tiles = plan->problems[0].k_tiles;
     const int forced = env_int("NVFP4_SPLIT", 0);
+    const KernelChoice kernel = select_kernel(plan->kind, plan->out_kind, plan->tile_n);
     for (int s = 2; s <= 8; s *= 2) {
       if (tiles * s > sms || s > k_tiles || (plan->out_tile_n / s) % 32 != 0) break;
+      // All clusters must be resident at once, or the grid runs in two waves.
+      const int resident = max_active_clusters(kernel, s);
+      if (resident > 0 && tiles > resident) break;
       if (forced == 0 || s <= forced) split = s;
     }
   }
   if (schedule == 3 && split < 2) schedule = 0;
-  if (schedule != 1 && schedule != 2 && schedule != 3) {
-    // Pick the schedule with the smallest estimated time. Measured on B200: a k-tile step
-    // of one CTA takes about 0.4 us with 128-column tiles (0.55 us with 256) once the
-    // pipeline is full, whatever the schedule; finishing split tiles through the
-    // workspace costs about 8 us at the end of the kernel, through a cluster's shared
-    // memory about 2.5 us.
-    const double step_us = plan->tile_n > 128 ? 0.55 : 0.4;
+  {
+    // The time model (microseconds, without the per-launch constant). Measured on B200: a
+    // k-tile step of one CTA takes about 0.30 / 0.38 / 0.52 us with 64 / 128 / 256-column
+    // tiles once the pipeline is full (the shared-memory pipe: TMA writes + MMA operand
+    // reads + scale reads), whatever the schedule; a 256-column tile's epilogue (~1.2 us)
+    // is not overlapped because its accumulator is single-buffered; finishing split tiles
+    // through the workspace costs 8 us and up at the end of the kernel, through a
+    // cluster's shared memory 3.5 us and up (below).
+    const double step_us = kStepUs(plan->tile_n);
+    const double tile_tail_us = plan->tile_n > 128 ? 1.2 : 0.0;
     const double k_per_tile = static_cast<double>(units) / static_cast<double>(tiles);
     const long long waves = (tiles + sms - 1) / sms;
-    const double t_whole = static_cast<double>(waves) * k_per_tile * step_us;
+    const double t_whole = static_cast<double>(waves) * (k_per_tile * step_us + tile_tail_us);
     const long long sk_ctas = std::min<long long>(sms, std::max<long long>(tiles, units / 4));
-    const double t_stream = static_cast<double>(units) / static_cast<double>(sk_ctas) * step_us + 8.0;
+    // The workspace fix-up moves whole FP32 tiles: about 8 us with 128-column tiles, far
+    // more with 256 (measured ~35 us on the decode shape).
+    const double fixup_us = plan->tile_n > 128 ? 32.0 : 8.0;
+    const double t_stream =
+        static_cast<double>(units) / static_cast<double>(sk_ctas) * step_us + fixup_us;
     double t_cluster = 1e30;
     if (split >= 2) {
       const int k_tiles = plan->problems[0].k_tiles;
-      t_cluster = static_cast<double>((k_tiles + split - 1) / split) * step_us + 2.5;
+      // Against a data-parallel launch of the same tiles a cluster launch measured 2.4-5 us
+      // dearer for pairs and more for larger clusters and wider tiles (cluster launch and
+      // barriers, the exchange itself, fewer idle SMs for the next launch's prologue).
+      const double exchange_us = (split == 2 ? 3.5 : split == 4 ? 5.0 : 8.0) *
+                                 (plan->tile_n > 128 ? 1.5 : 1.0);
+      t_cluster = static_cast<double>((k_tiles + split - 1) / split) * step_us + tile_tail_us +
+                  exchange_us;
     }
-    schedule = 1;
-    double best = t_whole;
-    if (t_stream < best && units > tiles) {
-      schedule = 2;
-      best = t_stream;
+    if (schedule != 1 && schedule != 2 && schedule != 3) {
+      schedule = 1;
+      double best = t_whole;
+      if (t_stream < best && units > tiles) {
+        schedule = 2;
+        best = t_stream;
+      }
+      if (t_cluster < best) schedule = 3;
     }
-    if (t_cluster < best) schedule = 3;
+    plan->estimate_us = schedule == 1 ? t_whole : schedule == 2 ? t_stream : t_cluster;
   }
   if (ctas <= 0) {
     if (schedule == 1) {
@@ -487,14 +541,26 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     plan->tile_n = 256;
     plan->out_tile_n = 128;
   } else {
-    // 256-column tiles once they still give every SM at least two tiles: half the A
-    // re-reads and a single-buffered accumulator pay off only when tiles are plentiful.
-    const long long wide_tiles =
-        static_cast<long long>(ceil_div(m, 128)) * ceil_div(n, 256) * l;
-    plan->tile_n = default_tile_n(config, wide_tiles >= 2ll * sms ? 256 : 128);
-    plan->out_tile_n = plan->tile_n;
-    // Pairs of CTAs on 256 x 256 tiles (tcgen05.mma.cta_group::2) once there are at least
-    // two such tiles per pair of SMs: each CTA then loads only half of every B tile.
+    // Tile width: the one whose best schedule the time model puts first, unless the
+    // caller names one. Pairs of CTAs on 256 x 256 tiles (tcgen05.mma.cta_group::2, each
+    // CTA loads only half of every B tile) compete in the same model.
+    plan->problems.resize(1);
+    int chosen = default_tile_n(config, 0);
+    double chosen_us = 1e30;
+    if (chosen == 0) {
+      for (int tile_n : {64, 128, 256}) {
+        plan->tile_n = tile_n;
+        plan->out_tile_n = tile_n;
+        fill_problem(&plan->problems[0], m, n, k, l, tile_n);
+        finish_schedule(plan, config);
+        if (plan->estimate_us < chosen_us) {
+          chosen_us = plan->estimate_us;
+          chosen = tile_n;
+        }
+      }
+    }
+    plan->tile_n = chosen;
+    plan->out_tile_n = chosen;
     const long long pair_tiles = static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, 256) * l;
     int want_pair = config != nullptr ? config->pair : 0;
     if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
@@ -503,8 +569,11 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
         (config != nullptr && (config->tile_n > 0 || config->schedule > 0 || config->ctas > 0)) ||
         env_int("NVFP4_TILE_N", 0) > 0 || env_int("NVFP4_SCHEDULE", 0) > 0 ||
         env_int("NVFP4_CTAS", 0) > 0;
-    plan->pair = want_pair > 0 || (want_pair == 0 && !explicit_choice &&
-                                   pair_tiles >= 2ll * sms && kPairByDefault);
+    const long long pair_waves = (pair_tiles + sms / 2 - 1) / (sms / 2);
+    const double pair_us =
+        static_cast<double>(pair_waves) * (ceil_div(k, 256) * kPairStepUs + 1.2);
+    plan->pair = want_pair > 0 || (want_pair == 0 && !explicit_choice && kPairByDefault &&
+                                   pair_tiles >= sms / 4 && pair_us < chosen_us);
     if (plan->pair) {
       plan->tile_n = 256;
       plan->out_tile_n = 256;

@@ -453,8 +453,12 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
       if (peer != rank) mbar_arrive_cluster(cluster_map_shared(bar_ready, peer));
     }
   }
-  // 2. Wait until every peer has said the same.
-  if (!mbar_wait_cluster(bar_ready, 0, abort_ptr)) {
+  // 2. Wait until every peer has said the same (one lane polls for its warp).
+  const int lane = row & 31;
+  int ready = 1;
+  if (lane == 0) ready = mbar_wait_cluster(bar_ready, 0, abort_ptr) ? 1 : 0;
+  ready = __shfl_sync(0xFFFFFFFFu, ready, 0);
+  if (!ready) {
     report_failure(p, abort_ptr, kStatusClusterTimeout);
     return;
   }
@@ -479,10 +483,24 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
         }
       }
     }
-    mbar_arrive_cluster(cluster_map_shared(bar_data, peer));
   }
-  // 4. Wait for every peer's columns.
-  if (!mbar_wait_cluster(bar_data, 0, abort_ptr)) {
+  // One lane per warp signals every peer: the warp's stores are ordered before the lane's
+  // fence by the __syncwarp, the fence makes them visible at cluster scope before the
+  // (relaxed) arrives. A releasing arrive per thread and peer - 128 x (split - 1) remote
+  // operations that each wait for the thread's stores - cost several microseconds for
+  // clusters of four.
+  __syncwarp();
+  if (lane == 0) {
+    fence_acq_rel_cluster();
+    for (int peer = 0; peer < split; ++peer) {
+      if (peer != rank) mbar_arrive_peer(cluster_map_shared(bar_data, peer));
+    }
+  }
+  // 4. Wait for every peer's columns: one lane acquires for its warp.
+  int arrived = 1;
+  if (lane == 0) arrived = mbar_wait_cluster(bar_data, 0, abort_ptr) ? 1 : 0;
+  arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
+  if (!arrived) {
     report_failure(p, abort_ptr, kStatusClusterTimeout);
     return;
   }
@@ -580,7 +598,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     }
     const uint32_t peers = p.split > 1 ? static_cast<uint32_t>(p.split - 1) : 1u;
     mbar_init(smem_u32(&bar_peer_ready), peers);
-    mbar_init(smem_u32(&bar_peer_data), 128u * peers);
+    mbar_init(smem_u32(&bar_peer_data), 4u * peers);  // one arrival per epilogue warp and peer
     abort_flag = 0;
     epi_last_flag = 0;
     mbar_fence_init();

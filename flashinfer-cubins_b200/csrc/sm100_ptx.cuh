@@ -311,6 +311,13 @@ __device__ __forceinline__ void mbar_arrive_peer(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// Orders this thread's earlier writes (and, after a __syncwarp, its warp's) before its
+// later ones at cluster scope: one fence + relaxed arrives instead of a releasing arrive
+// per thread and peer.
+__device__ __forceinline__ void fence_acq_rel_cluster() {
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
