@@ -134,16 +134,19 @@ struct KernelChoice {
   int smem_bytes;
   int stages;
   int threads;
+  int stage_bytes;
 };
 
 template <class Cfg>
 KernelChoice make_choice() {
-  return KernelChoice{&nvfp4_gemm_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::STAGES, Cfg::THREADS};
+  return KernelChoice{&nvfp4_gemm_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::STAGES, Cfg::THREADS,
+                      Cfg::STAGE_BYTES};
 }
 
 template <class Cfg>
 KernelChoice make_pair_choice() {
-  return KernelChoice{&nvfp4_gemm_pair_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::STAGES, Cfg::THREADS};
+  return KernelChoice{&nvfp4_gemm_pair_kernel<Cfg>, Cfg::SMEM_BYTES, Cfg::STAGES, Cfg::THREADS,
+                      Cfg::STAGE_BYTES};
 }
 
 // kind, out_kind, tile_n -> kernel instantiation. Returns fn == nullptr if absent.
@@ -182,7 +185,7 @@ KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
       case 256: return make_choice<GemmConfig<256, false, float, false>>();
     }
   }
-  return KernelChoice{nullptr, 0, 0, 0};
+  return KernelChoice{nullptr, 0, 0, 0, 0};
 }
 
 }  // namespace
@@ -199,6 +202,8 @@ struct nvfp4_plan {
   int split = 1;      // cluster size of schedule 3
   bool pair = false;  // 2-CTA kernel: 256 x 256 tiles, one cluster of two CTAs per tile
   double estimate_us = 0.0;  // the time model's figure for the chosen schedule (mainloop + tail)
+  int ring_stages = 0;       // pipeline stages the kernel cycles through
+  int inbox_offset = -1;     // cluster split-K: byte offset of the peers' inbox, or -1
   KernelChoice kernel{};
   std::vector<ProblemDesc> problems;  // pointers filled at launch / bind
   long long total_tiles = 0, total_units = 0;
@@ -427,6 +432,20 @@ int prepare_kernel(nvfp4_plan* plan) {
   CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void*>(plan->kernel.fn),
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 plan->kernel.smem_bytes));
+  // Cluster split-K: set the last pipeline stages aside as the inbox for the peers' partial
+  // columns when at least four stages remain; peers then need no permission to write.
+  plan->ring_stages = plan->kernel.stages;
+  plan->inbox_offset = -1;
+  if (!plan->pair && plan->schedule == 3 && plan->split >= 2 && plan->split <= 4) {
+    const int halves = plan->kind == kDual ? 2 : 1;
+    const int portion = (plan->out_tile_n / plan->split / 32) * halves * 16384;
+    const int inbox = (plan->split - 1) * portion;
+    const int reserve = ceil_div(inbox, plan->kernel.stage_bytes);
+    if (plan->kernel.stages - reserve >= 4) {
+      plan->ring_stages = plan->kernel.stages - reserve;
+      plan->inbox_offset = plan->ring_stages * plan->kernel.stage_bytes;
+    }
+  }
   return 0;
 }
 
@@ -443,6 +462,8 @@ void fill_common_params(const nvfp4_plan* plan, KernelParams& kp, void* workspac
   kp.num_problems = static_cast<int>(plan->problems.size());
   kp.mode = plan->schedule == 1 ? kModeDataParallel : kModeStreamK;
   kp.split = plan->split;
+  kp.ring_stages = plan->ring_stages > 0 ? plan->ring_stages : plan->kernel.stages;
+  kp.inbox_offset = plan->inbox_offset;
   bool streams = true;
   for (const ProblemDesc& pd : plan->problems) {
     if (pd.tiles_m > 1) streams = false;
@@ -699,7 +720,7 @@ int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info) {
   info->tile_m = plan->pair ? 256 : 128;
   info->tile_n = plan->out_tile_n;
   info->tile_k = 256;
-  info->stages = plan->kernel.stages;
+  info->stages = plan->ring_stages > 0 ? plan->ring_stages : plan->kernel.stages;
   info->schedule = plan->schedule;
   info->ctas = plan->ctas;
   info->threads = plan->kernel.threads;

@@ -87,7 +87,11 @@ struct alignas(64) KernelParams {
   int probe;      // timing experiments only; ignored unless built with NVFP4_PROBE
   int split;      // > 1: CTAs of a cluster of this size split each tile's K (stream-K mode
                   // with grid = tiles * split) and reduce through peer shared memory
-  int pad0, pad1, pad2;
+  int ring_stages;   // pipeline stages in use (fewer than the kernel's when the top of the
+                     // pipeline memory is set aside as the cluster inbox)
+  int inbox_offset;  // byte offset of that inbox from the pipeline base, or -1: peers may then
+                     // write only after this CTA has told them its pipeline memory is free
+  int pad2;
 };
 
 // Timing experiments (results become wrong): compiled out of the product build.
@@ -447,6 +451,59 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
   const int rank = static_cast<int>(cluster_cta_rank());
   const int width = Cfg::OUT_BN / split;  // output columns per owner, a multiple of 32
   const int chunks = width / 32;
+  const int lane = row & 31;
+  const bool no_exchange = NVFP4_PROBE_FLAG(p, 18);  // timing experiment
+  // Bytes one CTA sends to one peer: the peer's columns of both accumulator halves, as
+  // float4 [chunk][half][column / 4][row].
+  const uint32_t portion = static_cast<uint32_t>(chunks * HALVES) * 16384u;
+  uint32_t inbox = staging;  // where peers' columns arrive
+  if (p.inbox_offset >= 0 && !no_exchange) {
+    // Inbox path: the top of the pipeline memory was never used by this launch's pipeline, so
+    // peers need no permission to write there. Every CTA puts the columns of each peer
+    // into its own (now idle) pipeline memory with plain stores and sends them with one
+    // bulk copy per peer, which counts its bytes on the peer's barrier: no remote store per
+    // thread, no cluster-scope fence, no round trip to ask whether the peer is ready.
+    inbox = staging + static_cast<uint32_t>(p.inbox_offset);
+    if (epi_tid == 0) mbar_expect_tx(bar_data, static_cast<uint32_t>(split - 1) * portion);
+    for (int peer = 0; peer < split; ++peer) {
+      if (peer == rank) continue;
+      const int out_slot = peer < rank ? peer : peer - 1;
+      const uint32_t outbox = staging + static_cast<uint32_t>(out_slot) * portion;
+#pragma unroll 1
+      for (int c = 0; c < chunks; ++c) {
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+          uint32_t r1[32];
+          tmem_load_32(taddr + h * Cfg::OUT_BN + peer * width + c * 32, r1);
+          tmem_load_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t index = ((c * HALVES + h) * 8 + q) * 128 + row;
+            st_shared_v4(outbox + index * 16u, r1[4 * q], r1[4 * q + 1], r1[4 * q + 2],
+                         r1[4 * q + 3]);
+          }
+        }
+      }
+    }
+    fence_proxy_async_shared();
+    named_barrier_sync(1, 128);
+    if (epi_tid == 0) {
+      for (int peer = 0; peer < split; ++peer) {
+        if (peer == rank) continue;
+        const int out_slot = peer < rank ? peer : peer - 1;
+        const int in_slot = rank < peer ? rank : rank - 1;  // my slot in the peer's inbox
+        bulk_copy_to_peer(cluster_map_shared(inbox + static_cast<uint32_t>(in_slot) * portion, peer),
+                          staging + static_cast<uint32_t>(out_slot) * portion, portion,
+                          cluster_map_shared(bar_data, peer));
+      }
+    }
+    // The bytes arrive through the async proxy and are counted on the barrier: the plain
+    // wait is the one every TMA consumer uses.
+    if (!mbar_wait(bar_data, 0, abort_ptr)) {
+      report_failure(p, abort_ptr, kStatusClusterTimeout);
+      return;
+    }
+  } else if (!no_exchange) {
   // 1. My pipeline memory is free: tell every peer it may write into it.
   if (epi_tid == 0) {
     for (int peer = 0; peer < split; ++peer) {
@@ -454,7 +511,6 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
     }
   }
   // 2. Wait until every peer has said the same (one lane polls for its warp).
-  const int lane = row & 31;
   int ready = 1;
   if (lane == 0) ready = mbar_wait_cluster(bar_ready, 0, abort_ptr) ? 1 : 0;
   ready = __shfl_sync(0xFFFFFFFFu, ready, 0);
@@ -504,6 +560,7 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
     report_failure(p, abort_ptr, kStatusClusterTimeout);
     return;
   }
+  }
   // 5. Own columns: add in rank order, finish, store.
   const int n0 = s.n_tile * Cfg::OUT_BN + rank * width;
 #pragma unroll 1
@@ -525,7 +582,7 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const uint32_t index = (((slot * chunks + c) * HALVES + h) * 8 + q) * 128 + row;
-            const uint4 t = ld_shared_v4(staging + index * 16u);
+            const uint4 t = ld_shared_v4(inbox + index * 16u);
             sum[h][4 * q + 0] += __uint_as_float(t.x);
             sum[h][4 * q + 1] += __uint_as_float(t.y);
             sum[h][4 * q + 2] += __uint_as_float(t.z);
@@ -598,7 +655,9 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     }
     const uint32_t peers = p.split > 1 ? static_cast<uint32_t>(p.split - 1) : 1u;
     mbar_init(smem_u32(&bar_peer_ready), peers);
-    mbar_init(smem_u32(&bar_peer_data), 4u * peers);  // one arrival per epilogue warp and peer
+    // Inbox path: one local arrival (expect_tx) + the peers' bytes. Otherwise one arrival
+    // per epilogue warp and peer.
+    mbar_init(smem_u32(&bar_peer_data), p.inbox_offset >= 0 ? 1u : 4u * peers);
     abort_flag = 0;
     epi_last_flag = 0;
     mbar_fence_init();
@@ -609,10 +668,11 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   tc_fence_before_sync();
   __syncthreads();
   // Peers arrive on this CTA's barriers, so they must be initialised cluster-wide.
-  if (p.split > 1) cluster_sync_all();
+  if (p.split > 1 && !NVFP4_PROBE_FLAG(p, 19)) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
+  const int ring = p.ring_stages;  // <= STAGES
   // Everything above touched only this CTA's shared and tensor memory, so under
   // programmatic dependent launch it overlaps the previous kernel's tail; nothing below
   // may read or write global memory before that kernel has finished.
@@ -717,7 +777,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           atoms_left -= 4;
           kbyte += 128;
           stage_smem += Cfg::STAGE_BYTES;
-          if (++stage == STAGES) {
+          if (++stage == ring) {
             stage = 0;
             phase ^= 1u;
             stage_smem = smem_base;
@@ -800,7 +860,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           atoms_left -= 4;
           stage16 += kStage16;
           t_sf += Cfg::SF_STAGE_COLS;
-          if (++stage == STAGES) {
+          if (++stage == ring) {
             stage = 0;
             phase ^= 1u;
             stage16 = 0;
@@ -868,7 +928,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         atoms_left -= 4;
         stage16 += kStage16;
         t_cp += Cfg::SF_STAGE_COLS;
-        if (++stage == STAGES) {
+        if (++stage == ring) {
           stage = 0;
           phase ^= 1u;
           stage16 = 0;
@@ -925,7 +985,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         atoms_left -= 4;
         sf_smem += Cfg::STAGE_BYTES;
         t_sf += Cfg::SF_STAGE_COLS;
-        if (++stage == STAGES) {
+        if (++stage == ring) {
           stage = 0;
           phase ^= 1u;
           sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
@@ -1149,7 +1209,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   tc_fence_before_sync();
   __syncthreads();
   // No CTA of a cluster leaves while a peer could still write into its shared memory.
-  if (p.split > 1) cluster_sync_all();
+  if (p.split > 1 && !NVFP4_PROBE_FLAG(p, 19)) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
     __syncwarp();

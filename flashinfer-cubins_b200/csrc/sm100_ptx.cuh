@@ -135,6 +135,25 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       : "memory");
 }
 
+// Bulk copy from this CTA's shared memory into a peer CTA's (both shared::cluster
+// addresses for the destination side), completion counted in bytes on the peer's mbarrier.
+// Addresses 16-byte aligned, size a multiple of 16 bytes. The source must have been
+// written before a fence.proxy.async by the writing threads.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t peer_dst, uint32_t src, uint32_t bytes,
+                                                  uint32_t peer_bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(peer_dst),
+      "r"(src), "r"(bytes), "r"(peer_bar)
+      : "memory");
+}
+
+// Makes this thread's earlier generic-proxy writes to shared memory visible to the async
+// proxy (bulk copies, TMA).
+__device__ __forceinline__ void fence_proxy_async_shared() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------
 // Tensor memory
 // ---------------------------------------------------------------------------
