@@ -221,11 +221,7 @@ struct GemmConfig {
   // 227 KiB per CTA less 1 KiB alignment slack, the barriers, and the epilogue warps'
   // 8 KiB of staging for coalesced stores (both static).
   static constexpr int SMEM_BUDGET = 227 * 1024 - 2048 - 8192;
-#ifdef NVFP4_FORCE_STAGES  // timing experiments only
-  static constexpr int STAGES = NVFP4_FORCE_STAGES;
-#else
   static constexpr int STAGES = const_min(8, SMEM_BUDGET / STAGE_BYTES);
-#endif
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
   static constexpr int ACC_BUFS = BN <= 128 ? 2 : 1;
   static constexpr int SFB_COLS = const_max(4, BN / 32);  // columns per k-block
@@ -640,11 +636,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
-#ifdef NVFP4_SF_CP
-      mbar_init(smem_u32(&bar_full[s]), 2);
-#else
       mbar_init(smem_u32(&bar_full[s]), 5);
-#endif
       mbar_init(smem_u32(&bar_empty[s]), 1);
       mbar_init(smem_u32(&bar_sf_full[s]), 1);
     }
@@ -893,51 +885,6 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     uint32_t sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
     uint32_t t_sf = tmem_base + lane_base + Cfg::SF_COL;
     bool ok = true;
-#ifdef NVFP4_SF_CP
-    // Experiment: one warp issues tcgen05.cp (shared -> tensor memory, broadcast to the four
-    // lane quarters by the hardware) instead of four warps going through registers.
-    if (warp != 6) ok = false;
-    constexpr uint32_t kHiScale = (128u >> 4) | (1u << 14);
-    constexpr uint32_t kStage16 = Cfg::STAGE_BYTES >> 4;
-    const uint32_t lo_sfa0 = (smem_base + Cfg::A_BYTES + Cfg::B_BYTES) >> 4;
-    uint32_t stage16 = 0;
-    uint32_t t_cp = tmem_base + Cfg::SF_COL;
-    while (ok && it.next(s)) {
-      int atoms_left = it.pd.sf_kb - 4 * s.k0;
-      for (int kt = s.k0; kt < s.k1; ++kt) {
-        if (!mbar_wait(sf_full0 + 8 * stage, phase, abort_ptr)) {
-          report_failure(p, abort_ptr, kStatusScaleTimeout);
-          ok = false;
-          break;
-        }
-        const int atoms = min(4, atoms_left);
-        if (elect_one()) {
-          const uint32_t lo_sfa = lo_sfa0 + stage16;
-          const uint32_t lo_sfb = lo_sfa + (Cfg::SFA_BYTES >> 4);
-          for (int j = 0; j < atoms; ++j) {
-            tc_copy_32x128b_x4(t_cp + 4 * j, pack_desc(lo_sfa + 32 * j, kHiScale));
-#pragma unroll
-            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-              tc_copy_32x128b_x4(t_cp + 16 + j * Cfg::SFB_COLS + 4 * i,
-                                 pack_desc(lo_sfb + 128 * i + 32 * j, kHiScale));
-            }
-          }
-          tc_commit(full0 + 8 * stage);
-        }
-        __syncwarp();
-        atoms_left -= 4;
-        stage16 += kStage16;
-        t_cp += Cfg::SF_STAGE_COLS;
-        if (++stage == ring) {
-          stage = 0;
-          phase ^= 1u;
-          stage16 = 0;
-          t_cp = tmem_base + Cfg::SF_COL;
-        }
-      }
-    }
-    ok = false;
-#endif
     while (ok && it.next(s)) {
       int atoms_left = it.pd.sf_kb - 4 * s.k0;
       for (int kt = s.k0; kt < s.k1; ++kt) {
