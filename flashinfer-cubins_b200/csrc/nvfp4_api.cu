@@ -152,7 +152,11 @@ KernelChoice make_pair_choice() {
 // kind, out_kind, tile_n -> kernel instantiation. Returns fn == nullptr if absent.
 KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
   if (kind == kDual) {
-    return make_choice<GemmConfig<256, true, __half, false>>();
+    switch (tile_n) {
+      case 128: return make_choice<GemmConfig<128, true, __half, false>>();
+      case 256: return make_choice<GemmConfig<256, true, __half, false>>();
+    }
+    return KernelChoice{nullptr, 0, 0, 0, 0};
   }
   if (kind == kGrouped) {
     switch (tile_n) {
@@ -559,8 +563,25 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
   plan->out_kind = out_kind;
   plan->sm_count = sms;
   if (kind == kDual) {
-    plan->tile_n = 256;
-    plan->out_tile_n = 128;
+    // The MMA is as wide as both B tiles together: 2 x 128 columns, or 2 x 64 when that
+    // fills the SMs better (its accumulator is double-buffered and it needs no K split).
+    plan->problems.resize(1);
+    int chosen = default_tile_n(config, 0);
+    if (chosen == 0) {
+      double chosen_us = 1e30;
+      for (int tile_n : {128, 256}) {
+        plan->tile_n = tile_n;
+        plan->out_tile_n = tile_n / 2;
+        fill_problem(&plan->problems[0], m, n, k, l, tile_n / 2);
+        finish_schedule(plan, config);
+        if (plan->estimate_us < chosen_us) {
+          chosen_us = plan->estimate_us;
+          chosen = tile_n;
+        }
+      }
+    }
+    plan->tile_n = chosen;
+    plan->out_tile_n = chosen / 2;
   } else {
     // Tile width: the one whose best schedule the time model puts first, unless the
     // caller names one. Pairs of CTAs on 256 x 256 tiles (tcgen05.mma.cta_group::2, each
@@ -885,8 +906,12 @@ int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, cons
     ProblemDesc& pd = plan->problems[0];
     KernelParams& kp = plan->params;
     if (int rc = encode_operand_map(&kp.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
-    if (int rc = encode_operand_map(&kp.map_b, b1, pd.n, pd.k, pd.batches, 128)) return rc;
-    if (int rc = encode_operand_map(&kp.map_b2, b2, pd.n, pd.k, pd.batches, 128)) return rc;
+    if (int rc = encode_operand_map(&kp.map_b, b1, pd.n, pd.k, pd.batches, plan->out_tile_n)) {
+      return rc;
+    }
+    if (int rc = encode_operand_map(&kp.map_b2, b2, pd.n, pd.k, pd.batches, plan->out_tile_n)) {
+      return rc;
+    }
     pd.sfa = static_cast<const uint8_t*>(sfa);
     pd.sfb = static_cast<const uint8_t*>(sfb1);
     pd.sfb2 = static_cast<const uint8_t*>(sfb2);

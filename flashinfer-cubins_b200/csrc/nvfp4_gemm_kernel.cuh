@@ -214,7 +214,12 @@ struct GemmConfig {
   static constexpr int OUT_BN = DUAL ? BN / 2 : BN;  // output columns per tile
   static constexpr int A_BYTES = BM * 128;           // 128 rows x 256 E2M1
   static constexpr int B_BYTES = BN * 128;
-  static constexpr int SFB_BLOCKS = (BN + 127) / 128;  // 128-row scale atoms per k-block
+  // 128-row scale atoms per k-block: the dual GEMM always reads one atom of each B (a
+  // 64-row tile uses half of it).
+  static constexpr int SFB_BLOCKS = DUAL ? 2 : (BN + 127) / 128;
+  // Dual GEMM on 64-column output tiles: the MMA's 128 scale columns are the tile's half
+  // of B1's atom followed by the same half of B2's atom.
+  static constexpr bool NARROW_DUAL = DUAL && BN == 128;
   static constexpr int SFA_BYTES = 4 * 512;
   static constexpr int SFB_BYTES = 4 * 512 * SFB_BLOCKS;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
@@ -231,7 +236,7 @@ struct GemmConfig {
   static constexpr int TMEM_COLS = const_pow2_at_least(SF_COL + STAGES * SF_STAGE_COLS);
   static constexpr int THREADS = 320;
   static_assert(BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
-  static_assert(!DUAL || BN == 256, "dual GEMM uses two 128-column B tiles");
+  static_assert(!DUAL || BN == 256 || BN == 128, "dual GEMM uses two 128- or 64-column B tiles");
   static_assert(TMEM_COLS <= 512, "tensor memory exceeded");
   static_assert(STAGES >= 2, "pipeline too shallow");
 };
@@ -887,6 +892,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     bool ok = true;
     while (ok && it.next(s)) {
       int atoms_left = it.pd.sf_kb - 4 * s.k0;
+      const bool upper_half = (s.n_tile & 1) != 0;  // narrow dual: rows 64-127 of the atoms
       for (int kt = s.k0; kt < s.k1; ++kt) {
         if (!mbar_wait(sf_full0 + 8 * stage, phase, abort_ptr)) {
           report_failure(p, abort_ptr, kStatusScaleTimeout);
@@ -909,7 +915,16 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           // at 16 + j * SFB_COLS + 4i), so whole 16-column stores cover them: the cost of
           // a tensor-memory store is per instruction, not per column.
           tmem_store_16(t_sf, va[0], va[1], va[2], va[3]);
-          if constexpr (Cfg::SFB_BLOCKS == 1) {
+          if constexpr (Cfg::NARROW_DUAL) {
+            // Two of an atom row's four words belong to the tile's 64 rows of B.
+            uint4 w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              w[j] = upper_half ? make_uint4(vb[j][0].z, vb[j][0].w, vb[j][1].z, vb[j][1].w)
+                                : make_uint4(vb[j][0].x, vb[j][0].y, vb[j][1].x, vb[j][1].y);
+            }
+            tmem_store_16(t_sf + 16, w[0], w[1], w[2], w[3]);
+          } else if constexpr (Cfg::SFB_BLOCKS == 1) {
             tmem_store_16(t_sf + 16, vb[0][0], vb[1][0], vb[2][0], vb[3][0]);
           } else {
             tmem_store_16(t_sf + 16, vb[0][0], vb[0][1], vb[1][0], vb[1][1]);
@@ -918,10 +933,17 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         } else {
           for (int j = 0; j < atoms; ++j) {
             tmem_store_4(t_sf + 4 * j, ld_shared_v4(sf_smem + 512 * j + row_off));
+            if constexpr (Cfg::NARROW_DUAL) {
+              const uint4 b1 = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 512 * j + row_off);
+              const uint4 b2 = ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 + 512 * j + row_off);
+              tmem_store_4(t_sf + 16 + 4 * j, upper_half ? make_uint4(b1.z, b1.w, b2.z, b2.w)
+                                                         : make_uint4(b1.x, b1.y, b2.x, b2.y));
+            } else {
 #pragma unroll
-            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-              tmem_store_4(t_sf + 16 + j * Cfg::SFB_COLS + 4 * i,
-                           ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 * i + 512 * j + row_off));
+              for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+                tmem_store_4(t_sf + 16 + j * Cfg::SFB_COLS + 4 * i,
+                             ld_shared_v4(sf_smem + Cfg::SFA_BYTES + 2048 * i + 512 * j + row_off));
+              }
             }
           }
         }

@@ -273,10 +273,13 @@ def test_pair_kernel(m, n, k, l, out_kind):  # noqa: E741
         plan.destroy()
 
 
+@pytest.mark.parametrize("tile_n", (128, 256))
 @pytest.mark.parametrize("schedule", (1, 2, 3))
-def test_dual_gemm_under_every_schedule(schedule):
+def test_dual_gemm_under_every_schedule(schedule, tile_n):
     """The fused dual GEMM with whole tiles, the workspace fix-up and the cluster
-    reduction (both accumulator halves travel to the owner of the output columns)."""
+    reduction (both accumulator halves travel to the owner of the output columns), on
+    2 x 128-column and 2 x 64-column B tiles (the latter reads half a scale atom of each
+    B; n = 264 and 136 end in partial and odd-numbered 64-column tiles)."""
     from harness import CaseSpec
     workload = get_workload("nvfp4_dual_gemm")(None, device="cuda")
     dev = torch.device("cuda:0")
@@ -285,7 +288,7 @@ def test_dual_gemm_under_every_schedule(schedule):
         case = CaseSpec("dual", {"m": m, "n": n, "k": k, "l": l, "alpha": 0.25}, 31)
         inputs = workload.get_inputs(case)
         (ref,) = workload.get_reference(inputs)
-        plan = native.Plan.dual(0, m, n, k, l, schedule=schedule)
+        plan = native.Plan.dual(0, m, n, k, l, schedule=schedule, tile_n=tile_n)
         info = plan.info()
         if schedule == 3:
             assert info["schedule"] == "cluster_split_k", info
