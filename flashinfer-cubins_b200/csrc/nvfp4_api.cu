@@ -421,7 +421,9 @@ int default_tile_n(const nvfp4_config* config, int fallback) {
 }
 
 int prepare_kernel(nvfp4_plan* plan) {
-  if (plan->pair) {
+  if (plan->pair && plan->kind == kDual) {
+    plan->kernel = make_pair_choice<PairConfig<__half, true>>();
+  } else if (plan->pair) {
     plan->kernel = plan->out_kind == NVFP4_OUT_F16    ? make_pair_choice<PairConfig<__half>>()
                    : plan->out_kind == NVFP4_OUT_BF16 ? make_pair_choice<PairConfig<__nv_bfloat16>>()
                                                       : make_pair_choice<PairConfig<float>>();
@@ -529,6 +531,7 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
                       int l, const nvfp4_config* config) {
   if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
   *out = nullptr;
+  double chosen_us = 1e30;  // the time model's figure for the best single-CTA plan
   if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32 && out_kind != NVFP4_OUT_FP4 &&
       out_kind != NVFP4_OUT_BF16) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "unknown output kind %d", out_kind);
@@ -568,7 +571,6 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     plan->problems.resize(1);
     int chosen = default_tile_n(config, 0);
     if (chosen == 0) {
-      double chosen_us = 1e30;
       for (int tile_n : {128, 256}) {
         plan->tile_n = tile_n;
         plan->out_tile_n = tile_n / 2;
@@ -588,7 +590,6 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     // CTA loads only half of every B tile) compete in the same model.
     plan->problems.resize(1);
     int chosen = default_tile_n(config, 0);
-    double chosen_us = 1e30;
     if (chosen == 0) {
       for (int tile_n : {64, 128, 256}) {
         plan->tile_n = tile_n;
@@ -603,7 +604,13 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     }
     plan->tile_n = chosen;
     plan->out_tile_n = chosen;
-    const long long pair_tiles = static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, 256) * l;
+  }
+  {
+    // The 2-CTA kernel: 256 x 256 output tiles (dual: 256 x 128, B1 in one CTA and B2 in
+    // the other).
+    const int pair_out_n = kind == kDual ? 128 : 256;
+    const long long pair_tiles =
+        static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, pair_out_n) * l;
     int want_pair = config != nullptr ? config->pair : 0;
     if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
     if (out_kind == NVFP4_OUT_FP4) want_pair = -1;
@@ -618,7 +625,7 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
                                    pair_tiles >= sms / 4 && pair_us < chosen_us);
     if (plan->pair) {
       plan->tile_n = 256;
-      plan->out_tile_n = 256;
+      plan->out_tile_n = pair_out_n;
     }
   }
   plan->problems.resize(1);
@@ -626,7 +633,8 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
   if (plan->pair) {
     // One schedule only: pair tiles dealt round-robin to the pairs of SMs.
     ProblemDesc& pd = plan->problems[0];
-    const long long pair_tiles = static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, 256) * l;
+    const long long pair_tiles =
+        static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, plan->out_tile_n) * l;
     pd.tiles_m = ceil_div(m, 256);
     pd.tile_begin = 0;
     pd.unit_begin = 0;

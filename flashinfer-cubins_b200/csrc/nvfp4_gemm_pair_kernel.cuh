@@ -79,9 +79,13 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map,
       : "memory");
 }
 
-template <typename OutT_>
+// DUAL: the pair's 256 B rows are a 128-row tile of B1 (loaded by the leader) and the same
+// rows of B2 (loaded by the peer); the epilogue writes silu(h1) * h2 for 128 output columns.
+template <typename OutT_, bool DUAL_ = false>
 struct PairConfig {
   using OutT = OutT_;
+  static constexpr bool DUAL = DUAL_;
+  static constexpr int OUT_N = DUAL ? 128 : 256;  // output columns per tile
   static constexpr int TILE_M = 256, TILE_N = 256;
   static constexpr int A_BYTES = 128 * 128;       // this CTA's 128 rows x 256 E2M1
   static constexpr int B_BYTES = 128 * 128;       // this CTA's half of the B tile
@@ -143,7 +147,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
 
   const ProblemDesc& pd = p.dense;
   const int pair_tiles_m = (pd.m + 255) / 256;
-  const int pair_tiles_n = (pd.n + 255) / 256;
+  const int pair_tiles_n = (pd.n + Cfg::OUT_N - 1) / Cfg::OUT_N;
   const long long tiles = static_cast<long long>(pair_tiles_m) * pair_tiles_n * pd.batches;
   const long long pairs = gridDim.x / 2;
   const long long first_tile = blockIdx.x / 2;
@@ -168,6 +172,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
       if (elect_one()) {
         prefetch_tensormap(&p.map_a);
         prefetch_tensormap(&p.map_b);
+        if constexpr (Cfg::DUAL) prefetch_tensormap(&p.map_b2);
       }
       const uint32_t leader_full0 = cluster_map_shared(smem_u32(&bar_full[0]), 0);
       const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
@@ -180,16 +185,23 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         int batch, m_tile, n_tile;
         decode(t, batch, m_tile, n_tile);
         const int m0 = m_tile * 256 + static_cast<int>(rank) * 128;
-        const int n0 = n_tile * 256 + static_cast<int>(rank) * 128;
+        // Rows of B this CTA loads: its half of the 256-row tile, or (dual) the tile's 128
+        // rows of its own B.
+        const int n0 = Cfg::DUAL ? n_tile * 128 : n_tile * 256 + static_cast<int>(rank) * 128;
+        const void* map_b = (Cfg::DUAL && rank == 1) ? static_cast<const void*>(&p.map_b2)
+                                                     : static_cast<const void*>(&p.map_b);
         const int mb = m_tile * 2 + static_cast<int>(rank);  // this CTA's SFA atom row
-        const int nb = n_tile * 2;                            // first of the tile's SFB atom rows
+        const int nb = Cfg::DUAL ? n_tile : n_tile * 2;       // first of the tile's SFB atom rows
         const bool sfa_valid = mb < pd.sf_mb;
         const uint8_t* sfa_src =
             pd.sfa + (static_cast<long long>(batch) * pd.sf_mb + mb) * pd.sf_kb * 512;
         const uint8_t* sfb_src0 =
             pd.sfb + (static_cast<long long>(batch) * pd.sf_nb + nb) * pd.sf_kb * 512;
-        const uint8_t* sfb_src1 = sfb_src0 + static_cast<long long>(pd.sf_kb) * 512;
-        const bool sfb1_valid = nb + 1 < pd.sf_nb;
+        // Second scale atom row: the next 128 rows of B, or (dual) the same rows of B2.
+        const uint8_t* sfb_src1 =
+            Cfg::DUAL ? pd.sfb2 + (static_cast<long long>(batch) * pd.sf_nb + nb) * pd.sf_kb * 512
+                      : sfb_src0 + static_cast<long long>(pd.sf_kb) * 512;
+        const bool sfb1_valid = Cfg::DUAL || nb + 1 < pd.sf_nb;
         int atoms_left = pd.sf_kb;
         int kbyte = 0;
         for (int kt = 0; kt < pd.k_tiles; ++kt) {
@@ -219,7 +231,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
                 mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
               }
               tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
-              tma_load_3d_pair(b_dst, &p.map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
+              tma_load_3d_pair(b_dst, map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
             }
           }
           __syncwarp();
@@ -387,13 +399,53 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
       }
       tc_fence_after_sync();
       const int grow = m_tile * 256 + static_cast<int>(rank) * 128 + row;
-      const int n0 = n_tile * 256;
+      const int n0 = n_tile * Cfg::OUT_N;
       OutT* out_row = reinterpret_cast<OutT*>(pd.d) +
                       (static_cast<long long>(batch) * pd.m + grow) * pd.n;
       OutT* out_block = out_row - static_cast<long long>(lane) * pd.n;
       const int rows_valid = pd.m - (grow - lane);
       const uint32_t stage_smem = smem_u32(&epi_stage[quarter][0]);
-      if constexpr (sizeof(OutT) == 2) {
+      if constexpr (Cfg::DUAL) {
+        // h1 in columns [0, 128), h2 in [128, 256): gate, pack, hand the accumulator back,
+        // then store.
+        uint32_t packed[4][16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r1[32], r2[32];
+          tmem_load_32(taddr + c * 32, r1);
+          tmem_load_32(taddr + 128 + c * 32, r2);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            packed[c][i] = pack_pair<OutT>(
+                silu_f32(__uint_as_float(r1[2 * i]) * alpha) * (__uint_as_float(r2[2 * i]) * alpha),
+                silu_f32(__uint_as_float(r1[2 * i + 1]) * alpha) *
+                    (__uint_as_float(r2[2 * i + 1]) * alpha));
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive_peer(leader_acc_empty);
+        if ((pd.n & 7) == 0) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            store_block_coalesced<OutT>(stage_smem, packed[c], out_block, n0 + c * 32, pd.n,
+                                        rows_valid, lane);
+          }
+        } else if (grow < pd.m) {
+          // Rows of D only 8-byte aligned (n % 8 == 4): 8-byte pieces.
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const int col = n0 + c * 32 + 4 * g;
+              if (col < pd.n) {
+                *reinterpret_cast<uint2*>(out_row + col) =
+                    make_uint2(packed[c][2 * g], packed[c][2 * g + 1]);
+              }
+            }
+          }
+        }
+      } else if constexpr (sizeof(OutT) == 2) {
         // Read the whole row out of tensor memory first (packed to FP16: 128 registers),
         // hand the accumulator back to the MMA issuer, then store: the next tile's MMAs
         // start while this tile is still being written.

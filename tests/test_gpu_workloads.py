@@ -449,3 +449,27 @@ def test_nvfp4_output_plan_rejects_what_it_cannot_do():
     plan = native.Plan.dense(0, native.OUT_F16, 128, 128, 64, 1)
     with pytest.raises(ValueError):
         plan.launch_dense_fp4(256, 256, 256, 256, 256, 256, 256, 256, 0)
+
+
+@pytest.mark.parametrize("m,n,k,l", [(300, 264, 2080, 1), (512, 1024, 1024, 1), (130, 260, 512, 2)])
+def test_dual_gemm_on_cta_pairs(m, n, k, l):  # noqa: E741
+    """The fused dual GEMM on the 2-CTA kernel: the leader loads B1's tile, its peer B2's, one
+    256-column MMA per pair; partial tiles in M and N, a K tail, batches, and rows of D that
+    are only 8-byte aligned (n = 260)."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_dual_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    case = CaseSpec("dual_pair", {"m": m, "n": n, "k": k, "l": l, "alpha": 0.25}, 41)
+    inputs = workload.get_inputs(case)
+    (ref,) = workload.get_reference(inputs)
+    plan = native.Plan.dual(0, m, n, k, l, pair=1)
+    assert plan.info()["tile_m"] == 256, plan.info()
+    ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+    plan.init_workspace(ws.data_ptr(), stream)
+    d = torch.full((l, m, n), float("nan"), dtype=torch.float16, device=dev)
+    for _ in range(2):
+        plan.launch_dual(*(t.data_ptr() for t in inputs), d.data_ptr(), ws.data_ptr(), stream)
+    assert plan.status(ws.data_ptr(), stream) == 0
+    torch.testing.assert_close(d.permute(1, 2, 0), ref, rtol=1e-3, atol=1e-3)
+    plan.destroy()
