@@ -24,7 +24,8 @@ together exceed the 126 MB L2, so B is read from HBM every step.
   samples of the workload.
 
 With N > 1 (launched by torch.distributed.run) every rank holds its own N-shard of a
-GEMM whose N is N_gpus x 7168 (weak scaling, no collective on the data path).
+GEMM whose N is N_gpus x 7168 (weak scaling, no collective on the data path);
+``--scaling strong`` splits the workload's own N over the ranks instead.
 """
 
 from __future__ import annotations
@@ -294,6 +295,9 @@ def main() -> None:
     parser.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-graph", action="store_true")
+    parser.add_argument("--scaling", default="weak", choices=("weak", "strong"),
+                        help="weak: every rank runs the whole shape (global N = ranks x N); "
+                             "strong: the shape's N is split over the ranks")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -305,6 +309,12 @@ def main() -> None:
     if args.impl == "reference":
         reference_arm(args, kind, shape, rank)
         return
+    global_n = shape.get("n")
+    if args.scaling == "strong" and world > 1:
+        if kind == "grouped" or shape["n"] % (128 * world):
+            raise SystemExit("strong scaling needs a dense or dual shape whose N splits into "
+                             "multiples of 128 rows per rank")
+        shape = dict(shape, n=shape["n"] // world)
 
     import torch.distributed as dist
 
@@ -319,7 +329,7 @@ def main() -> None:
     flops, byts = algorithmic_work(kind, shape)
     set_bytes = byts  # operands + output of one set
     sets = max(3, int(2 * L2_BYTES // set_bytes) + 1)
-    sets = min(sets, 8)
+    sets = min(sets, 8 if args.scaling == "weak" else 32)
     cls = workload_class(kind)
     # One workload (and so one native plan with cached tensor maps) per operand set.
     workloads = [cls.from_arch("sm_100a", device=device) for _ in range(sets)]
@@ -436,11 +446,14 @@ def main() -> None:
             "metric": "nvfp4_gemm_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": elapsed_ms / args.steps, "us_per_call": per_call_us,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "nvfp4", "data": "synthetic",
             "config": {
                 "workload": f"nvfp4 {kind} GEMM {shape} l=1, fp16 out, per GPU"
-                            + (f" (global n = {world} x {shape.get('n')})" if world > 1 else ""),
+                            + (f" (global n = {world} x {shape.get('n')})"
+                               if world > 1 and args.scaling == "weak" else "")
+                            + (f" (global n = {global_n} split over {world} ranks)"
+                               if world > 1 and args.scaling == "strong" else ""),
                 "operand_sets": sets, "l2": f"{sets} operand sets of {set_bytes / 2**20:.0f} MiB "
                                             "rotate, larger than the 126 MB L2 together",
                 "timing": "cuda_graph_replay" if graph is not None else "direct_launches",

@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <climits>
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -314,11 +315,14 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
     const long long waves = (tiles + sms - 1) / sms;
     const double t_whole = static_cast<double>(waves) * (k_per_tile * step_us + tile_tail_us);
     const long long sk_ctas = std::min<long long>(sms, std::max<long long>(tiles, units / 4));
-    // The workspace fix-up moves whole FP32 tiles: about 8 us with 128-column tiles, far
-    // more with 256 (measured ~35 us on the decode shape).
-    const double fixup_us = plan->tile_n > 128 ? 32.0 : 8.0;
-    const double t_stream =
-        static_cast<double>(units) / static_cast<double>(sk_ctas) * step_us + fixup_us;
+    // The workspace fix-up moves whole FP32 tiles and the last CTA of a tile adds the
+    // others' partials one after the other: with 128-column tiles about 6 us for two
+    // contributors per tile and ~2.2 us for every further one (39 us measured with sixteen),
+    // four times that with 256-column tiles.
+    const double units_per_cta = static_cast<double>(units) / static_cast<double>(sk_ctas);
+    const double contributors = std::ceil(k_per_tile / units_per_cta) + 1.0;
+    const double fixup_us = (plan->tile_n > 128 ? 4.0 : 1.0) * (4.0 + 2.2 * (contributors - 1.0));
+    const double t_stream = units_per_cta * step_us + fixup_us;
     double t_cluster = 1e30;
     if (split >= 2) {
       const int k_tiles = plan->problems[0].k_tiles;
