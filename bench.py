@@ -438,9 +438,15 @@ def main() -> None:
         else:
             tf = flops / (per_call_us * 1e-6) / 1e12
             peak_tf = 9000.0
+            # The rate at which this GPU issues block-scaled FP4 MMAs with nothing else
+            # running (the library's own microbenchmark, after the timed region).
+            from harness import native
+            issue_tf = native.measure_mma_peak(local_rank, 4096)
             roofline = {"bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s",
                         "frac": tf / peak_tf, "traffic": None,
-                        "peak_source": "nominal dense FP4 (no measured FP4 peak on this pool)",
+                        "peak_source": "nominal dense FP4",
+                        "measured_mma_issue_tflops": issue_tf,
+                        "frac_of_measured_mma_issue": tf / issue_tf,
                         "algorithmic_flops_per_launch": flops}
         line = {
             "metric": "nvfp4_gemm_tflops", "value": value, "unit": "TFLOP/s",

@@ -843,6 +843,7 @@ int nvfp4_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b, const 
 
 constexpr size_t kStaticScratchBytes = 24u << 20;  // 24 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ int g_peak_status;  // status word of nvfp4_measure_mma_peak
 
 namespace {
 
@@ -1072,6 +1073,54 @@ int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int ro
         static_cast<uint8_t*>(scales), rows, k, batches);
   }
   CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int nvfp4_measure_mma_peak(int device, int iters, double* tflops) {
+  if (tflops == nullptr || iters < 1 || iters > (1 << 22)) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "bad arguments");
+  }
+  int sms = 0;
+  if (int rc = check_device(device, &sms)) return rc;
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(device));
+  void* status = nullptr;
+  CUDA_TRY(cudaGetSymbolAddress(&status, g_peak_status));
+  const int smem = 49 * 1024 + 1024;
+  CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void*>(&mma_issue_peak_kernel),
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  cudaStream_t stream = nullptr;
+  cudaEvent_t start = nullptr, stop = nullptr;
+  CUDA_TRY(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  cudaError_t error = cudaEventCreate(&start);
+  if (error == cudaSuccess) error = cudaEventCreate(&stop);
+  if (error == cudaSuccess) error = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  float best_ms = 0.0f;
+  for (int run = 0; run < 3 && error == cudaSuccess; ++run) {  // first run warms up
+    error = cudaEventRecord(start, stream);
+    if (error != cudaSuccess) break;
+    mma_issue_peak_kernel<<<sms, 128, smem, stream>>>(iters, static_cast<int*>(status));
+    error = cudaGetLastError();
+    if (error == cudaSuccess) error = cudaEventRecord(stop, stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(stop);
+    float ms = 0.0f;
+    if (error == cudaSuccess) error = cudaEventElapsedTime(&ms, start, stop);
+    if (run > 0 && (best_ms == 0.0f || ms < best_ms)) best_ms = ms;
+  }
+  int abandoned = 0;
+  if (error == cudaSuccess) {
+    error = cudaMemcpyAsync(&abandoned, status, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  }
+  if (error == cudaSuccess) error = cudaStreamSynchronize(stream);
+  if (start != nullptr) cudaEventDestroy(start);
+  if (stop != nullptr) cudaEventDestroy(stop);
+  cudaStreamDestroy(stream);
+  CUDA_TRY(error);
+  if (abandoned != 0 || best_ms <= 0.0f) {
+    return fail(NVFP4_E_DEVICE_TIMEOUT, "the measurement kernel abandoned its wait");
+  }
+  const double flops = 2.0 * 128.0 * 256.0 * 64.0 * 4.0 * iters * sms;
+  *tflops = flops / (static_cast<double>(best_ms) * 1e-3) / 1e12;
   return 0;
 }
 

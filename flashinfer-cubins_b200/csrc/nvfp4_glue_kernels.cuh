@@ -9,6 +9,8 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include "sm100_ptx.cuh"
+
 namespace nvfp4 {
 
 // scales: [batches][rows][cols] bytes. packed: [batches][rb][cb][32][4][4] bytes with
@@ -176,6 +178,58 @@ __global__ void silu_product_kernel(const float* __restrict__ h1, const float* _
   }
   for (long long i = groups * 8 + tid; i < size; i += nthreads) {
     out[i] = __float2half_rn(silu_gate(h1[i], h2[i]));
+  }
+}
+
+// Issue rate of the block-scaled FP4 MMA with nothing else going on: every CTA issues
+// `iters` x 4 tcgen05.mma (128 x 256 x 64, operands wherever shared memory happens to be
+// zero-filled, scales and accumulator in tensor memory) back to back and waits for the last.
+// The host divides the FLOPs by the elapsed time: the tensor pipe's rate at the clocks the
+// GPU really runs at, which is the denominator the GEMM kernels are compared with besides
+// the nominal figure. `status` gets 1 if the final wait was abandoned.
+__global__ void __launch_bounds__(128, 1) mma_issue_peak_kernel(int iters, int* status) {
+  extern __shared__ uint8_t peak_smem[];
+  __shared__ alignas(8) uint64_t done_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const uint32_t base = (smem_u32(peak_smem) + 1023u) & ~1023u;
+  for (uint32_t i = threadIdx.x; i < (48u * 1024u) / 16u; i += blockDim.x) {
+    st_shared_v4(base + i * 16u, 0u, 0u, 0u, 0u);
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&done_bar), 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (threadIdx.x < 32) tmem_alloc(smem_u32(&tmem_slot), 512);
+  fence_proxy_async_shared();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x < 32) {
+    constexpr uint32_t idesc = nvf4_instr_desc(128, 256);
+    constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    const uint32_t lo_a = ((base >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t lo_b = lo_a + (16384u >> 4);
+    if (elect_one()) {
+      for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          tc_mma_nvf4(tmem, pack_desc(lo_a + 2 * j, kHi), pack_desc(lo_b + 2 * j, kHi), idesc,
+                      tmem + 256 + 4 * j, tmem + 272 + 8 * j, 1u);
+        }
+      }
+      tc_commit(smem_u32(&done_bar));
+    }
+    __syncwarp();
+    if (!mbar_wait(smem_u32(&done_bar), 0, &abort_flag)) atomicExch(status, 1);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
   }
 }
 

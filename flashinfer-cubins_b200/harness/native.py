@@ -109,6 +109,7 @@ _PROTOTYPES = {
         ctypes.c_int, [_P, ctypes.c_int, _P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
     ),
     "nvfp4_silu_product": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P]),
+    "nvfp4_measure_mma_peak": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
 }
 
 _lock = threading.Lock()
@@ -280,6 +281,13 @@ IN_BF16 = 1
 def quantize(x: int, x_kind: int, packed: int, scales: int, rows: int, k: int, batches: int,
              stream: int) -> None:
     check(load().nvfp4_quantize(x, x_kind, packed, scales, rows, k, batches, stream))
+
+
+def measure_mma_peak(device: int, iters: int = 4096) -> float:
+    """TFLOP/s at which ``device`` issues block-scaled FP4 MMAs with nothing else running."""
+    value = ctypes.c_double(0.0)
+    check(load().nvfp4_measure_mma_peak(device, iters, ctypes.byref(value)))
+    return value.value
 
 
 def silu_product(h1: int, h2: int, out: int, size: int, stream: int) -> None:

@@ -207,6 +207,13 @@ int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int ro
  * harness/workloads/nvfp4_dual_gemm.py:352-367). */
 int nvfp4_silu_product(const float* h1, const float* h2, void* out, int64_t size, void* stream);
 
+/* Measures the issue rate of the block-scaled FP4 MMA on `device`: one CTA per SM issues
+ * `iters` x 4 tcgen05.mma (128 x 256 x 64) back to back from shared memory with nothing else
+ * running, and *tflops receives the aggregate TFLOP/s of the best of two timed launches. It
+ * is the measured denominator for the tensor-bound rooflines next to the nominal 9 PFLOP/s;
+ * the reference has no counterpart. Synchronous; uses its own stream. */
+int nvfp4_measure_mma_peak(int device, int iters, double* tflops);
+
 #ifdef __cplusplus
 }
 #endif

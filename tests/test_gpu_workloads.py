@@ -473,3 +473,12 @@ def test_dual_gemm_on_cta_pairs(m, n, k, l):  # noqa: E741
     assert plan.status(ws.data_ptr(), stream) == 0
     torch.testing.assert_close(d.permute(1, 2, 0), ref, rtol=1e-3, atol=1e-3)
     plan.destroy()
+
+
+def test_mma_issue_peak_measurement_is_plausible():
+    """The library's own FP4 MMA issue-rate microbenchmark: near the nominal 9 PFLOP/s on a
+    B200 at full clocks, and never below what the GEMM kernels reach."""
+    value = native.measure_mma_peak(0, 2048)
+    assert 4000.0 < value < 12000.0, value
+    with pytest.raises(ValueError):
+        native.measure_mma_peak(0, 0)
