@@ -152,6 +152,13 @@ KernelChoice make_pair_choice() {
 
 // kind, out_kind, tile_n -> kernel instantiation. Returns fn == nullptr if absent.
 KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
+  if (kind == kDual && out_kind == NVFP4_OUT_FP4) {
+    switch (tile_n) {
+      case 128: return make_choice<GemmConfig<128, true, Fp4Out, false>>();
+      case 256: return make_choice<GemmConfig<256, true, Fp4Out, false>>();
+    }
+    return KernelChoice{nullptr, 0, 0, 0, 0};
+  }
   if (kind == kDual) {
     switch (tile_n) {
       case 128: return make_choice<GemmConfig<128, true, __half, false>>();
@@ -215,7 +222,8 @@ struct nvfp4_plan {
   long long slot_floats = 0;
   size_t off_counters = 0, off_table = 0, off_maps = 0, off_partials = 0, ws_bytes = 0;
   // Last operands a dense/dual launch encoded maps for.
-  const void* bound[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  const void* bound[9] = {nullptr, nullptr, nullptr, nullptr, nullptr,
+                          nullptr, nullptr, nullptr, nullptr};
   void* bound_ws = nullptr;
   bool params_valid = false;
   KernelParams params{};
@@ -540,9 +548,9 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
       out_kind != NVFP4_OUT_BF16) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "unknown output kind %d", out_kind);
   }
-  if (out_kind == NVFP4_OUT_FP4 && (kind != kDense || n % 64 != 0)) {
+  if (out_kind == NVFP4_OUT_FP4 && n % 64 != 0) {
     return fail(NVFP4_E_UNSUPPORTED_SHAPE,
-                "NVFP4 output needs a dense GEMM with n a multiple of 64 (whole scale atoms)");
+                "NVFP4 output needs n to be a multiple of 64 (whole scale atoms)");
   }
   // The fused dual GEMM also takes n % 8 == 4 (8-byte aligned FP16 rows), because its
   // FP32-output stage does.
@@ -617,7 +625,7 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
         static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, pair_out_n) * l;
     int want_pair = config != nullptr ? config->pair : 0;
     if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
-    if (out_kind == NVFP4_OUT_FP4) want_pair = -1;
+    if (out_kind == NVFP4_OUT_FP4) want_pair = -1;  // whole tiles in one CTA, single-CTA kernel
     const bool explicit_choice =
         (config != nullptr && (config->tile_n > 0 || config->schedule > 0 || config->ctas > 0)) ||
         env_int("NVFP4_TILE_N", 0) > 0 || env_int("NVFP4_SCHEDULE", 0) > 0 ||
@@ -687,6 +695,11 @@ int nvfp4_gemm_plan_create(nvfp4_plan** plan, int device, int out_kind, int m, i
 int nvfp4_dual_gemm_plan_create(nvfp4_plan** plan, int device, int m, int n, int k, int l,
                                 const nvfp4_config* config) {
   return create_dense_like(plan, kDual, device, NVFP4_OUT_F16, m, n, k, l, config);
+}
+
+int nvfp4_dual_gemm_plan_create_fp4(nvfp4_plan** plan, int device, int m, int n, int k, int l,
+                                    const nvfp4_config* config) {
+  return create_dense_like(plan, kDual, device, NVFP4_OUT_FP4, m, n, k, l, config);
 }
 
 int nvfp4_group_gemm_plan_create(nvfp4_plan** out, int device, int groups, const int* mnk,
@@ -780,7 +793,7 @@ int launch_dense(nvfp4_plan* plan, const void* a, const void* b, const void* sfa
       !aligned(d, 16) || !aligned(sfd, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
-  const void* now[8] = {a, b, nullptr, sfa, sfb, sfd, alpha, d};
+  const void* now[9] = {a, b, nullptr, sfa, sfb, sfd, alpha, d, nullptr};
   if (!plan->params_valid || plan->bound_ws != workspace ||
       std::memcmp(now, plan->bound, sizeof(now)) != 0) {
     ProblemDesc& pd = plan->problems[0];
@@ -898,22 +911,25 @@ int nvfp4_gemm_launch_static(nvfp4_plan* plan, const void* a, const void* b, con
 
 size_t nvfp4_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
-int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
-                           const void* sfa, const void* sfb1, const void* sfb2,
-                           const float* alpha, void* d, void* workspace, void* stream) {
-  if (plan == nullptr || plan->kind != kDual) {
-    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dual GEMM plan");
-  }
+}  // extern "C"
+
+namespace {
+
+// The launch behind nvfp4_dual_gemm_launch and nvfp4_dual_gemm_launch_fp4 (`sfd` null for
+// the former).
+int launch_dual(nvfp4_plan* plan, const void* a, const void* b1, const void* b2, const void* sfa,
+                const void* sfb1, const void* sfb2, const float* alpha, void* d, void* sfd,
+                void* workspace, void* stream) {
   if (a == nullptr || b1 == nullptr || b2 == nullptr || sfa == nullptr || sfb1 == nullptr ||
       sfb2 == nullptr || alpha == nullptr || d == nullptr || workspace == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
   }
   if (!aligned(a, 16) || !aligned(b1, 16) || !aligned(b2, 16) || !aligned(sfa, 16) ||
-      !aligned(sfb1, 16) || !aligned(sfb2, 16) || !aligned(d, 8) || !aligned(alpha, 4) ||
-      !aligned(workspace, 256)) {
+      !aligned(sfb1, 16) || !aligned(sfb2, 16) || !aligned(d, sfd != nullptr ? 16 : 8) ||
+      !aligned(sfd, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
-  const void* now[8] = {a, b1, b2, sfa, sfb1, sfb2, alpha, d};
+  const void* now[9] = {a, b1, b2, sfa, sfb1, sfb2, alpha, d, sfd};
   if (!plan->params_valid || plan->bound_ws != workspace ||
       std::memcmp(now, plan->bound, sizeof(now)) != 0) {
     ProblemDesc& pd = plan->problems[0];
@@ -929,6 +945,7 @@ int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, cons
     pd.sfb = static_cast<const uint8_t*>(sfb1);
     pd.sfb2 = static_cast<const uint8_t*>(sfb2);
     pd.d = d;
+    pd.sfd = static_cast<uint8_t*>(sfd);
     kp.dense = pd;
     kp.alpha = alpha;
     fill_common_params(plan, kp, workspace);
@@ -937,6 +954,31 @@ int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, cons
     plan->params_valid = true;
   }
   return launch_plan(plan, plan->params, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+                           const void* sfa, const void* sfb1, const void* sfb2,
+                           const float* alpha, void* d, void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kDual || plan->out_kind == NVFP4_OUT_FP4) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dual GEMM plan with FP16 output");
+  }
+  return launch_dual(plan, a, b1, b2, sfa, sfb1, sfb2, alpha, d, nullptr, workspace, stream);
+}
+
+int nvfp4_dual_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+                               const void* sfa, const void* sfb1, const void* sfb2,
+                               const float* alpha, void* d_packed, void* d_scales,
+                               void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kDual || plan->out_kind != NVFP4_OUT_FP4) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a dual GEMM plan with NVFP4 output");
+  }
+  if (d_scales == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  return launch_dual(plan, a, b1, b2, sfa, sfb1, sfb2, alpha, d_packed, d_scales, workspace,
+                     stream);
 }
 
 int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* const* b,

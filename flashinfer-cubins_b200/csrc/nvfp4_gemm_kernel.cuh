@@ -1007,15 +1007,28 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                           (static_cast<long long>(s.batch) * pd.sf_mb + s.m_tile) * sf_cb * 512 +
                           (row % 32) * 16 + ((row / 32) % 4) * 4;
 #pragma unroll 1
-        for (int c2 = 0; c2 < BN / 64; ++c2) {
+        for (int c2 = 0; c2 < Cfg::OUT_BN / 64; ++c2) {
           uint32_t scale_word = 0;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             const int c = 2 * c2 + half;
             uint32_t r1[32];
             tmem_load_32(taddr + c * 32, r1);
-            tmem_load_wait();
-            if (c == BN / 32 - 1) {
+            if constexpr (Cfg::DUAL) {
+              uint32_t r2[32];
+              tmem_load_32(taddr + Cfg::OUT_BN + c * 32, r2);
+              tmem_load_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                r1[i] = __float_as_uint(silu_f32(__uint_as_float(r1[i]) * alpha) *
+                                        (__uint_as_float(r2[i]) * alpha));
+              }
+            } else {
+              tmem_load_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r1[i] = __float_as_uint(__uint_as_float(r1[i]) * alpha);
+            }
+            if (c == Cfg::OUT_BN / 32 - 1) {
               tc_fence_before_sync();
               mbar_arrive(smem_u32(&bar_acc_empty[acc]));
             }
@@ -1025,7 +1038,6 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
               float amax = 0.0f;
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                r1[16 * blk + i] = __float_as_uint(__uint_as_float(r1[16 * blk + i]) * alpha);
                 amax = fmaxf(amax, fabsf(__uint_as_float(r1[16 * blk + i])));
               }
               const uint32_t bits = nvfp4_scale_bits(amax);

@@ -81,6 +81,12 @@ _PROTOTYPES = {
         [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
          ctypes.c_int, ctypes.POINTER(Config)],
     ),
+    "nvfp4_dual_gemm_plan_create_fp4": (
+        ctypes.c_int,
+        [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+         ctypes.c_int, ctypes.POINTER(Config)],
+    ),
+    "nvfp4_dual_gemm_launch_fp4": (ctypes.c_int, [_P] * 12),
     "nvfp4_group_gemm_plan_create": (
         ctypes.c_int,
         [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
@@ -196,6 +202,14 @@ class Plan:
         return cls(handle.value)
 
     @classmethod
+    def dual_fp4(cls, device: int, m: int, n: int, k: int, l: int, **config):  # noqa: E741
+        """Fused dual GEMM whose gated output is quantised to NVFP4 in the epilogue."""
+        handle = _P()
+        check(load().nvfp4_dual_gemm_plan_create_fp4(
+            ctypes.byref(handle), device, m, n, k, l, cls._config(**config)))
+        return cls(handle.value)
+
+    @classmethod
     def grouped(cls, device: int, problems, **config):
         flat = [int(v) for problem in problems for v in problem]
         array = (ctypes.c_int * len(flat))(*flat)
@@ -240,6 +254,11 @@ class Plan:
     def launch_dual(self, a, b1, b2, sfa, sfb1, sfb2, alpha, d, workspace, stream) -> None:
         check(load().nvfp4_dual_gemm_launch(
             self.handle, a, b1, b2, sfa, sfb1, sfb2, alpha, d, workspace, stream))
+
+    def launch_dual_fp4(self, a, b1, b2, sfa, sfb1, sfb2, alpha, d_packed, d_scales, workspace,
+                        stream) -> None:
+        check(load().nvfp4_dual_gemm_launch_fp4(
+            self.handle, a, b1, b2, sfa, sfb1, sfb2, alpha, d_packed, d_scales, workspace, stream))
 
     def bind_groups(self, a, b, sfa, sfb, d, workspace, stream) -> None:
         def array(values):

@@ -138,6 +138,19 @@ int nvfp4_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b, const 
                           const void* sfb, const float* alpha, void* d_packed, void* d_scales,
                           void* workspace, void* stream);
 
+/* The fused dual GEMM with its gated output quantised to NVFP4 in the epilogue: gate/up
+ * projection -> packed E2M1 + blocked scales that the down projection's GEMM takes as its A
+ * operand. Same conventions as nvfp4_gemm_launch_fp4 (n % 64 == 0, data-parallel schedule,
+ * single-CTA kernel); silu is evaluated with ex2.approx / rcp.approx, so codes at E2M1
+ * rounding boundaries can differ from an exactly rounded silu. No counterpart in the
+ * reference. */
+int nvfp4_dual_gemm_plan_create_fp4(nvfp4_plan** plan, int device, int m, int n, int k, int l,
+                                    const nvfp4_config* config);
+int nvfp4_dual_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+                               const void* sfa, const void* sfb1, const void* sfb2,
+                               const float* alpha, void* d_packed, void* d_scales,
+                               void* workspace, void* stream);
+
 /* The dense launch for callers that must not allocate device memory where they call
  * this library (a runtime whose own pool owns all of HBM, a plugin under a foreign
  * allocator, a hot path that bans cudaMalloc because it synchronises the device). It has

@@ -482,3 +482,39 @@ def test_mma_issue_peak_measurement_is_plausible():
     assert 4000.0 < value < 12000.0, value
     with pytest.raises(ValueError):
         native.measure_mma_peak(0, 0)
+
+
+@pytest.mark.parametrize("m,n,k,l,tile_n", [(256, 512, 1024, 1, 0), (200, 192, 2080, 2, 128), (130, 320, 512, 1, 256)])
+def test_dual_gemm_with_nvfp4_output(m, n, k, l, tile_n):  # noqa: E741
+    """Gate/up dual GEMM quantised to NVFP4 in its epilogue. The kernel's silu uses
+    approximate exp and reciprocal, so codes may differ from the oracle's at E2M1 rounding
+    boundaries: nearly all bytes equal, and the dequantised tensors agree to well inside one
+    quantisation step of the tensor's scale."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_dual_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    case = CaseSpec("dual_fp4", {"m": m, "n": n, "k": k, "l": l, "alpha": 0.0625}, 51)
+    inputs = workload.get_inputs(case)
+    a, b1, b2, sfa, sfb1, sfb2, alpha = inputs
+    plan = native.Plan.dual_fp4(0, m, n, k, l, **({"tile_n": tile_n} if tile_n else {}))
+    ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+    plan.init_workspace(ws.data_ptr(), stream)
+    packed = torch.zeros((l, m, n // 2), dtype=torch.uint8, device=dev)
+    blocked = torch.zeros((l, -(-m // 128), n // 64, 32, 4, 4), dtype=torch.uint8, device=dev)
+    plan.launch_dual_fp4(*(t.data_ptr() for t in inputs), packed.data_ptr(), blocked.data_ptr(),
+                         ws.data_ptr(), stream)
+    assert plan.status(ws.data_ptr(), stream) == 0
+    sa = o.from_blocked(blocked_storage(sfa), m, k // 16)
+    s1 = o.from_blocked(blocked_storage(sfb1), n, k // 16)
+    s2 = o.from_blocked(blocked_storage(sfb2), n, k // 16)
+    want_packed, want_scales = o.dual_gemm_quantized(storage(a), storage(b1), storage(b2), sa, s1,
+                                                     s2, float(alpha.item()))
+    got_packed = packed.cpu().numpy()
+    got_scales = o.from_blocked(blocked.cpu().numpy(), m, n // 16)
+    assert (got_packed != want_packed).mean() < 5e-3
+    assert (got_scales != want_scales).mean() < 5e-3
+    got = o.dequant(got_packed, got_scales)
+    want = o.dequant(want_packed, want_scales)
+    assert np.linalg.norm(got - want) <= 2e-2 * np.linalg.norm(want)
+    plan.destroy()
