@@ -9,14 +9,17 @@
 // at byte ((r/128) * kb + c/4) * 512 + (r%32) * 16 + ((r/32)%4) * 4 + c%4, kb =
 // ceil(k/64) (the layout of harness/workloads/quantization.py:90-102 in the reference).
 //
-// Roles (320 threads): warp 0 lane 0 issues TMA loads into a ring of shared-memory
-// stages; warps 6-9 move each stage's scale atoms from shared memory into that stage's
-// columns of tensor memory (one warp per 32-lane quarter: a 512-byte atom is 32 rows of
-// 16 bytes, i.e. one ld.shared.v4 + one tcgen05.st.32x32b.x4 per warp, no reshuffle);
-// warp 1 lane 0 issues tcgen05.mma kind::mxf4nvf4 (128 x BN x 64 per instruction,
-// accumulators in tensor memory); warps 2-5 read finished accumulators (tcgen05.ld),
-// apply the epilogue and store. Keeping the scale copies off the MMA issue queue
-// matters: tcgen05.cp there cost about as much queue time as the MMAs themselves.
+// Roles (320 threads): warp 0 issues TMA loads into a ring of shared-memory stages;
+// warps 6-9 move each stage's scale atoms from shared memory into that stage's columns of
+// tensor memory (one warp per 32-lane quarter: a 512-byte atom is 32 rows of 16 bytes, i.e.
+// ld.shared.v4 per atom and tcgen05.st.32x32b.x16 per sixteen columns, no reshuffle) and
+// arrive on the stage's full barrier next to the producer; warp 1 issues tcgen05.mma
+// kind::mxf4nvf4 (128 x BN x 64 per instruction, accumulators in tensor memory); warps 2-5
+// read finished accumulators (tcgen05.ld), apply the epilogue and store through a small
+// swizzled staging buffer so that global stores are coalesced. Warps 0 and 1 run their
+// loops with all lanes and elect one lane for the issuing instructions. Keeping the scale
+// copies off the MMA issue queue matters: tcgen05.cp there cost about as much queue time
+// as the MMAs themselves.
 //
 // Work is a list of (tile, k-tile range) segments that every role derives from the
 // same counters: in data-parallel mode CTA c takes tiles c, c + grid, ...; in stream-K
@@ -24,7 +27,10 @@
 // ranges. A segment that does not cover its tile's whole K writes an FP32 partial to
 // the workspace; the last CTA to arrive at the tile (one atomic counter per tile, reset
 // by that CTA) adds the partials in segment order and finishes the tile, so results do
-// not depend on arrival order. No role waits on another CTA.
+// not depend on arrival order, and no CTA waits on another. With `split` > 1 the CTAs of a
+// thread-block cluster share one tile's K and exchange partial columns through shared
+// memory instead (cluster_reduce): there each CTA waits, bounded, for its cluster peers,
+// which the hardware schedules together.
 //
 // Every mbarrier wait is bounded; a role that gives up records a code in the status
 // word, raises the shared abort flag and falls through to the common exit where tensor
