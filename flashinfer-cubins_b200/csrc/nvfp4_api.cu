@@ -1105,14 +1105,26 @@ int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int ro
   const int threads = 256;
   const long long blocks = std::min<long long>((total + threads - 1) / threads, 148 * 32);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned int grid = static_cast<unsigned int>(blocks);
+  uint8_t* p8 = static_cast<uint8_t*>(packed);
+  uint8_t* s8 = static_cast<uint8_t*>(scales);
+  // 32-bit indices while the grid-stride loop cannot overflow them.
+  const bool narrow = total + static_cast<long long>(grid) * threads < INT_MAX;
   if (x_kind == NVFP4_IN_F32) {
-    quantize_nvfp4_kernel<float><<<static_cast<unsigned int>(blocks), threads, 0, s>>>(
-        static_cast<const float*>(x), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales),
-        rows, k, batches);
+    const float* in = static_cast<const float*>(x);
+    if (narrow) {
+      quantize_nvfp4_kernel<float, int><<<grid, threads, 0, s>>>(in, p8, s8, rows, k, batches);
+    } else {
+      quantize_nvfp4_kernel<float, long long><<<grid, threads, 0, s>>>(in, p8, s8, rows, k, batches);
+    }
   } else {
-    quantize_nvfp4_kernel<__nv_bfloat16><<<static_cast<unsigned int>(blocks), threads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(packed),
-        static_cast<uint8_t*>(scales), rows, k, batches);
+    const __nv_bfloat16* in = static_cast<const __nv_bfloat16*>(x);
+    if (narrow) {
+      quantize_nvfp4_kernel<__nv_bfloat16, int><<<grid, threads, 0, s>>>(in, p8, s8, rows, k, batches);
+    } else {
+      quantize_nvfp4_kernel<__nv_bfloat16, long long><<<grid, threads, 0, s>>>(in, p8, s8, rows, k,
+                                                                               batches);
+    }
   }
   CUDA_TRY(cudaGetLastError());
   return 0;

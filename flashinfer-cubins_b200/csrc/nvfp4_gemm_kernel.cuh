@@ -1051,11 +1051,11 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
               scale_word |= bits << (8 * (2 * half + blk));
               uint32_t w0 = 0, w1 = 0;
               if (scale > 0.0f) {
+                const E2m1Boundaries boundaries(scale);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                  w0 |= e2m1_code(__fdiv_rn(__uint_as_float(r1[16 * blk + i]), scale)) << (4 * i);
-                  w1 |= e2m1_code(__fdiv_rn(__uint_as_float(r1[16 * blk + 8 + i]), scale))
-                        << (4 * i);
+                  w0 |= boundaries.code(__uint_as_float(r1[16 * blk + i])) << (4 * i);
+                  w1 |= boundaries.code(__uint_as_float(r1[16 * blk + 8 + i])) << (4 * i);
                 }
               }
               words[2 * blk] = w0;

@@ -56,15 +56,32 @@ __global__ void pack_scales_kernel(const uint8_t* __restrict__ scales,
   }
 }
 
-// Round-to-nearest-even E2M1 code of v (saturating at +-6; values that round to zero
-// get code 0 whatever their sign).
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-  const float m = fabsf(v);
-  uint32_t code = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) + (m > 2.5f) +
-                  (m >= 3.5f) + (m > 5.0f);
-  if (v < 0.0f && code != 0) code |= 8u;
-  return code;
-}
+// The seven E2M1 rounding boundaries (ties to even: 0.25 -> 0, 0.75 -> 1, ...) times a block's
+// scale. A scale has four significant bits and a boundary three, so the products are exact,
+// and comparing x with them decides exactly as comparing the correctly rounded quotient
+// x / scale with the boundaries does (division is monotone and exact at the boundary) -
+// without sixteen IEEE divisions per block, which made the quantiser ALU-bound.
+struct E2m1Boundaries {
+  float b[7];
+  __device__ __forceinline__ explicit E2m1Boundaries(float scale) {
+    b[0] = 0.25f * scale;
+    b[1] = 0.75f * scale;
+    b[2] = 1.25f * scale;
+    b[3] = 1.75f * scale;
+    b[4] = 2.5f * scale;
+    b[5] = 3.5f * scale;
+    b[6] = 5.0f * scale;
+  }
+  // Round-to-nearest-even E2M1 code of x / scale (saturating at +-6; values that round to
+  // zero get code 0 whatever their sign).
+  __device__ __forceinline__ uint32_t code(float x) const {
+    const float m = fabsf(x);
+    uint32_t c = (m > b[0]) + (m >= b[1]) + (m > b[2]) + (m >= b[3]) + (m > b[4]) + (m >= b[5]) +
+                 (m > b[6]);
+    if (x < 0.0f && c != 0) c |= 8u;
+    return c;
+  }
+};
 
 // UE4M3 bits of the scale of a 16-element block with the given absolute maximum:
 // amax / 6 rounded to nearest even, saturating at 448.
@@ -82,19 +99,21 @@ __device__ __forceinline__ float nvfp4_scale_value(uint32_t bits) {
 // blocked layout [batches][rb][cb][32][4][4] (zero padded), one thread per 16-element block
 // of the padded scale grid: scale = e4m3(amax / 6) (round to nearest even, saturating),
 // element = E2M1 rounding of x / scale, zero scale -> zero codes.
-template <typename In>
+// `Index` is int when the padded scale grid has fewer than 2^31 entries (64-bit divisions
+// per thread would dominate the kernel), long long otherwise.
+template <typename In, typename Index>
 __global__ void quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
                                       uint8_t* __restrict__ scales, int rows, int k,
                                       int batches) {
   const int cols = k / 16;
   const int rb = (rows + 127) / 128;
   const int cb = (cols + 3) / 4;
-  const long long padded_cols = static_cast<long long>(cb) * 4;
-  const long long total = static_cast<long long>(batches) * rb * 128 * padded_cols;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+  const Index padded_cols = static_cast<Index>(cb) * 4;
+  const Index total = static_cast<Index>(batches) * rb * 128 * padded_cols;
+  for (Index i = blockIdx.x * static_cast<Index>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<Index>(gridDim.x) * blockDim.x) {
     const int c = static_cast<int>(i % padded_cols);
-    long long rest = i / padded_cols;
+    Index rest = i / padded_cols;
     const int r = static_cast<int>(rest % (rb * 128));
     const int batch = static_cast<int>(rest / (rb * 128));
     const long long atom = (static_cast<long long>(batch) * rb + r / 128) * cb + c / 4;
@@ -136,9 +155,10 @@ __global__ void quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restr
     const float scale = nvfp4_scale_value(scale_bits);
     uint32_t words[2] = {0u, 0u};
     if (scale > 0.0f) {
+      const E2m1Boundaries boundaries(scale);
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        words[j / 8] |= e2m1_code(__fdiv_rn(v[j], scale)) << (4 * (j % 8));
+        words[j / 8] |= boundaries.code(v[j]) << (4 * (j % 8));
       }
     }
     *reinterpret_cast<uint2*>(packed + element / 2) = make_uint2(words[0], words[1]);
