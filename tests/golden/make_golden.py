@@ -19,7 +19,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT")
+if not REFERENCE_ROOT or not Path(REFERENCE_ROOT, "harness").is_dir():
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference (it has a harness/ package)")
 sys.path.insert(0, REFERENCE_ROOT)
 
 from harness import get_workload  # noqa: E402  (the reference's package)
