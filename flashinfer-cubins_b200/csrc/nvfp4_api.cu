@@ -102,12 +102,11 @@ int encode_operand_map(CUtensorMap* map, const void* ptr, int rows, int k, int b
   EncodeTiledFn encode = nullptr;
   if (int rc = get_encoder(&encode)) return rc;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(k) / 2;
-  // Loads through the descriptor of a tensor smaller than 128 KiB are slow on this driver
-  // (the decode GEMM with 15 rows of A, 120 KiB: 23.3 us; with 16 rows, 128 KiB: 18.0 us;
-  // CUTLASS special-cases the same size for drivers up to 13.1). The batch extent is only a
-  // bound for coordinates, and the kernels never pass a batch index beyond the real count,
-  // so a small tensor is described with enough never-addressed batches to reach 128 KiB
-  // (15 rows: 18.1 us).
+  // Loads through the descriptor of a tensor smaller than 128 KiB are markedly slower on
+  // current drivers. The batch extent is only a bound for coordinates, and the kernels never
+  // pass a batch index beyond the real count (Segment::batch < ProblemDesc::batches; grouped
+  // problems pass 0), so a small tensor is described with enough never-addressed batches to
+  // reach 128 KiB.
   cuuint64_t declared_batches = static_cast<cuuint64_t>(batches);
   const cuuint64_t batch_bytes = row_bytes * static_cast<cuuint64_t>(rows);
   if (batch_bytes * declared_batches < 131072) {
@@ -227,17 +226,25 @@ struct nvfp4_plan {
   int ring_stages = 0;       // pipeline stages the kernel cycles through
   int inbox_offset = -1;     // cluster split-K: byte offset of the peers' inbox, or -1
   KernelChoice kernel{};
-  std::vector<ProblemDesc> problems;  // pointers filled at launch / bind
+  std::vector<ProblemDesc> problems;  // shapes and tile counts; operand pointers stay null
   long long total_tiles = 0, total_units = 0;
   long long slot_floats = 0;
   size_t off_counters = 0, off_table = 0, off_maps = 0, off_partials = 0, ws_bytes = 0;
-  // Last operands a dense/dual launch encoded maps for.
-  const void* bound[9] = {nullptr, nullptr, nullptr, nullptr, nullptr,
-                          nullptr, nullptr, nullptr, nullptr};
-  void* bound_ws = nullptr;
-  bool params_valid = false;
-  KernelParams params{};
-  std::vector<uint8_t> staging;  // grouped: table + maps as uploaded
+  // Everything above is fixed once the plan has been created. The only state a launch may
+  // touch is this cache of encoded kernel parameters (tensor maps are ~2 us each to encode),
+  // keyed by the operand and workspace addresses and guarded by `mutex`; a launch copies its
+  // entry out under the lock and launches from the copy, so concurrent launches of one plan
+  // from several threads and streams are safe.
+  struct BoundParams {
+    const void* key[10];
+    KernelParams params;
+    unsigned long long last_use;
+  };
+  static constexpr size_t kMaxBound = 16;
+  mutable std::mutex mutex;
+  mutable std::vector<BoundParams> bound;
+  mutable unsigned long long use_counter = 0;
+  mutable bool group_bound = false;  // grouped: a workspace has been bound at least once
 };
 
 namespace {
@@ -254,8 +261,13 @@ constexpr double kPairStepUs = 0.44;  // a CTA of a pair on its half of a 256 x 
 
 // How many clusters of `size` CTAs of this kernel the device can hold at once (0 if the
 // query fails). Clusters must fit inside one GPC, so this is less than SMs / size.
-int max_active_clusters(const KernelChoice& kernel, int size) {
+int max_active_clusters(int device, const KernelChoice& kernel, int size) {
   if (kernel.fn == nullptr) return 0;
+  DeviceGuard guard;
+  if (guard.enter(device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
   const void* fn = reinterpret_cast<const void*>(kernel.fn);
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kernel.smem_bytes) !=
       cudaSuccess) {
@@ -313,7 +325,7 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
     for (int s = 2; s <= 8; s *= 2) {
       if (tiles * s > sms || s > k_tiles || (plan->out_tile_n / s) % 32 != 0) break;
       // All clusters must be resident at once, or the grid runs in two waves.
-      const int resident = max_active_clusters(kernel, s);
+      const int resident = max_active_clusters(plan->device, kernel, s);
       if (resident > 0 && tiles > resident) break;
       if (forced == 0 || s <= forced) split = s;
     }
@@ -497,7 +509,39 @@ void fill_common_params(const nvfp4_plan* plan, KernelParams& kp, void* workspac
     if (pd.tiles_m > 1) streams = false;
   }
   kp.b_streams = streams ? 1 : 0;
-  kp.probe = env_int("NVFP4_PROBE_FLAGS", 0);
+  kp.pad1 = 0;
+}
+
+// The kernel parameters of a dense or dual launch on the operands named by `key`: taken from
+// the plan's cache, or built by `encode` and remembered (least recently used entry dropped
+// when the cache is full). `*out` is the caller's own copy.
+template <class Encode>
+int bound_params(const nvfp4_plan* plan, const void* const (&key)[10], Encode encode,
+                 KernelParams* out) {
+  std::lock_guard<std::mutex> lock(plan->mutex);
+  for (nvfp4_plan::BoundParams& entry : plan->bound) {
+    if (std::memcmp(entry.key, key, sizeof(key)) == 0) {
+      entry.last_use = ++plan->use_counter;
+      *out = entry.params;
+      return 0;
+    }
+  }
+  nvfp4_plan::BoundParams fresh{};
+  std::memcpy(fresh.key, key, sizeof(key));
+  if (int rc = encode(fresh.params)) return rc;
+  fresh.last_use = ++plan->use_counter;
+  *out = fresh.params;
+  if (plan->bound.size() < nvfp4_plan::kMaxBound) {
+    plan->bound.push_back(fresh);
+  } else {
+    auto oldest = std::min_element(plan->bound.begin(), plan->bound.end(),
+                                   [](const nvfp4_plan::BoundParams& x,
+                                      const nvfp4_plan::BoundParams& y) {
+                                     return x.last_use < y.last_use;
+                                   });
+    *oldest = fresh;
+  }
+  return 0;
 }
 
 int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream) {
@@ -531,6 +575,29 @@ int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream) {
   config.numAttrs = attributes;
   CUDA_TRY(cudaLaunchKernelExC(&config, reinterpret_cast<const void*>(plan->kernel.fn), args));
   return 0;
+}
+
+// SM count of the current device (the glue kernels run on whichever device the caller has
+// made current, like any runtime launch), remembered per device; 148 if the query fails.
+int current_sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+    cudaGetLastError();
+    return 148;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[device] == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        sms < 1) {
+      cudaGetLastError();
+      sms = 148;
+    }
+    cached[device] = sms;
+  }
+  return cached[device];
 }
 
 bool aligned(const void* p, uintptr_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
@@ -793,8 +860,9 @@ namespace {
 
 // The dense launch behind nvfp4_gemm_launch and nvfp4_gemm_launch_fp4 (`sfd` is null for
 // the former).
-int launch_dense(nvfp4_plan* plan, const void* a, const void* b, const void* sfa, const void* sfb,
-                 const float* alpha, void* d, void* sfd, void* workspace, void* stream) {
+int launch_dense(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+                 const void* sfb, const float* alpha, void* d, void* sfd, void* workspace,
+                 void* stream) {
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || alpha == nullptr ||
       d == nullptr || workspace == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
@@ -803,37 +871,38 @@ int launch_dense(nvfp4_plan* plan, const void* a, const void* b, const void* sfa
       !aligned(d, 16) || !aligned(sfd, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
-  const void* now[9] = {a, b, nullptr, sfa, sfb, sfd, alpha, d, nullptr};
-  if (!plan->params_valid || plan->bound_ws != workspace ||
-      std::memcmp(now, plan->bound, sizeof(now)) != 0) {
-    ProblemDesc& pd = plan->problems[0];
-    KernelParams& kp = plan->params;
-    if (int rc = encode_operand_map(&kp.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
-    if (int rc = encode_operand_map(&kp.map_b, b, pd.n, pd.k, pd.batches,
-                                    plan->pair ? 128 : plan->tile_n)) {
-      return rc;
-    }
-    kp.map_b2 = kp.map_b;
-    pd.sfa = static_cast<const uint8_t*>(sfa);
-    pd.sfb = static_cast<const uint8_t*>(sfb);
-    pd.sfb2 = nullptr;
-    pd.d = d;
-    pd.sfd = static_cast<uint8_t*>(sfd);
-    kp.dense = pd;
-    kp.alpha = alpha;
-    fill_common_params(plan, kp, workspace);
-    std::memcpy(plan->bound, now, sizeof(now));
-    plan->bound_ws = workspace;
-    plan->params_valid = true;
-  }
-  return launch_plan(plan, plan->params, stream);
+  const void* key[10] = {a, b, nullptr, sfa, sfb, sfd, alpha, d, nullptr, workspace};
+  KernelParams kp;
+  const int rc = bound_params(
+      plan, key,
+      [&](KernelParams& fresh) {
+        ProblemDesc pd = plan->problems[0];
+        if (int rc = encode_operand_map(&fresh.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
+        if (int rc = encode_operand_map(&fresh.map_b, b, pd.n, pd.k, pd.batches,
+                                        plan->pair ? 128 : plan->tile_n)) {
+          return rc;
+        }
+        fresh.map_b2 = fresh.map_b;
+        pd.sfa = static_cast<const uint8_t*>(sfa);
+        pd.sfb = static_cast<const uint8_t*>(sfb);
+        pd.sfb2 = nullptr;
+        pd.d = d;
+        pd.sfd = static_cast<uint8_t*>(sfd);
+        fresh.dense = pd;
+        fresh.alpha = alpha;
+        fill_common_params(plan, fresh, workspace);
+        return 0;
+      },
+      &kp);
+  if (rc != 0) return rc;
+  return launch_plan(plan, kp, stream);
 }
 
 }  // namespace
 
 extern "C" {
 
-int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+int nvfp4_gemm_launch(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                       const void* sfb, const float* alpha, void* d, void* workspace,
                       void* stream) {
   if (plan == nullptr || plan->kind != kDense || plan->out_kind == NVFP4_OUT_FP4) {
@@ -842,7 +911,7 @@ int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void
   return launch_dense(plan, a, b, sfa, sfb, alpha, d, nullptr, workspace, stream);
 }
 
-int nvfp4_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+int nvfp4_gemm_launch_fp4(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                           const void* sfb, const float* alpha, void* d_packed, void* d_scales,
                           void* workspace, void* stream) {
   if (plan == nullptr || plan->kind != kDense || plan->out_kind != NVFP4_OUT_FP4) {
@@ -896,7 +965,7 @@ int static_scratch_address(int device, void** out) {
 
 }  // namespace
 
-int nvfp4_gemm_launch_static(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+int nvfp4_gemm_launch_static(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                              const void* sfb, const float* alpha, void* d, void* stream) {
   if (plan == nullptr || plan->kind != kDense) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "not a dense GEMM plan");
@@ -921,56 +990,80 @@ int nvfp4_gemm_launch_static(nvfp4_plan* plan, const void* a, const void* b, con
 
 size_t nvfp4_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
+int nvfp4_static_status(int device, void* stream, int* status) {
+  if (status == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null argument");
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(device, &scratch)) return rc;
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int value = 0;
+  CUDA_TRY(cudaMemcpyAsync(&value, scratch, sizeof(int), cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  *status = value;
+  if (value != 0) {
+    // The next nvfp4_gemm_launch_static clears the word and its counters before it launches.
+    return fail(NVFP4_E_DEVICE_TIMEOUT, "kernel abandoned a bounded wait (code %d)", value);
+  }
+  return 0;
+}
+
 }  // extern "C"
 
 namespace {
 
 // The launch behind nvfp4_dual_gemm_launch and nvfp4_dual_gemm_launch_fp4 (`sfd` null for
 // the former).
-int launch_dual(nvfp4_plan* plan, const void* a, const void* b1, const void* b2, const void* sfa,
-                const void* sfb1, const void* sfb2, const float* alpha, void* d, void* sfd,
-                void* workspace, void* stream) {
+int launch_dual(const nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+                const void* sfa, const void* sfb1, const void* sfb2, const float* alpha, void* d,
+                void* sfd, void* workspace, void* stream) {
   if (a == nullptr || b1 == nullptr || b2 == nullptr || sfa == nullptr || sfb1 == nullptr ||
       sfb2 == nullptr || alpha == nullptr || d == nullptr || workspace == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
   }
+  // FP16 rows are stored in 16-byte pieces whenever n is a multiple of 8; only rows of
+  // n % 8 == 4 elements (8-byte aligned at best) are stored in 8-byte pieces.
+  const uintptr_t d_alignment = (sfd == nullptr && plan->problems[0].n % 8 == 4) ? 8 : 16;
   if (!aligned(a, 16) || !aligned(b1, 16) || !aligned(b2, 16) || !aligned(sfa, 16) ||
-      !aligned(sfb1, 16) || !aligned(sfb2, 16) || !aligned(d, sfd != nullptr ? 16 : 8) ||
+      !aligned(sfb1, 16) || !aligned(sfb2, 16) || !aligned(d, d_alignment) ||
       !aligned(sfd, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
-  const void* now[9] = {a, b1, b2, sfa, sfb1, sfb2, alpha, d, sfd};
-  if (!plan->params_valid || plan->bound_ws != workspace ||
-      std::memcmp(now, plan->bound, sizeof(now)) != 0) {
-    ProblemDesc& pd = plan->problems[0];
-    KernelParams& kp = plan->params;
-    if (int rc = encode_operand_map(&kp.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
-    if (int rc = encode_operand_map(&kp.map_b, b1, pd.n, pd.k, pd.batches, plan->out_tile_n)) {
-      return rc;
-    }
-    if (int rc = encode_operand_map(&kp.map_b2, b2, pd.n, pd.k, pd.batches, plan->out_tile_n)) {
-      return rc;
-    }
-    pd.sfa = static_cast<const uint8_t*>(sfa);
-    pd.sfb = static_cast<const uint8_t*>(sfb1);
-    pd.sfb2 = static_cast<const uint8_t*>(sfb2);
-    pd.d = d;
-    pd.sfd = static_cast<uint8_t*>(sfd);
-    kp.dense = pd;
-    kp.alpha = alpha;
-    fill_common_params(plan, kp, workspace);
-    std::memcpy(plan->bound, now, sizeof(now));
-    plan->bound_ws = workspace;
-    plan->params_valid = true;
-  }
-  return launch_plan(plan, plan->params, stream);
+  const void* key[10] = {a, b1, b2, sfa, sfb1, sfb2, alpha, d, sfd, workspace};
+  KernelParams kp;
+  const int rc = bound_params(
+      plan, key,
+      [&](KernelParams& fresh) {
+        ProblemDesc pd = plan->problems[0];
+        if (int rc = encode_operand_map(&fresh.map_a, a, pd.m, pd.k, pd.batches, 128)) return rc;
+        if (int rc = encode_operand_map(&fresh.map_b, b1, pd.n, pd.k, pd.batches,
+                                        plan->out_tile_n)) {
+          return rc;
+        }
+        if (int rc = encode_operand_map(&fresh.map_b2, b2, pd.n, pd.k, pd.batches,
+                                        plan->out_tile_n)) {
+          return rc;
+        }
+        pd.sfa = static_cast<const uint8_t*>(sfa);
+        pd.sfb = static_cast<const uint8_t*>(sfb1);
+        pd.sfb2 = static_cast<const uint8_t*>(sfb2);
+        pd.d = d;
+        pd.sfd = static_cast<uint8_t*>(sfd);
+        fresh.dense = pd;
+        fresh.alpha = alpha;
+        fill_common_params(plan, fresh, workspace);
+        return 0;
+      },
+      &kp);
+  if (rc != 0) return rc;
+  return launch_plan(plan, kp, stream);
 }
 
 }  // namespace
 
 extern "C" {
 
-int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+int nvfp4_dual_gemm_launch(const nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
                            const void* sfa, const void* sfb1, const void* sfb2,
                            const float* alpha, void* d, void* workspace, void* stream) {
   if (plan == nullptr || plan->kind != kDual || plan->out_kind == NVFP4_OUT_FP4) {
@@ -979,7 +1072,7 @@ int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, cons
   return launch_dual(plan, a, b1, b2, sfa, sfb1, sfb2, alpha, d, nullptr, workspace, stream);
 }
 
-int nvfp4_dual_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+int nvfp4_dual_gemm_launch_fp4(const nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
                                const void* sfa, const void* sfb1, const void* sfb2,
                                const float* alpha, void* d_packed, void* d_scales,
                                void* workspace, void* stream) {
@@ -991,7 +1084,7 @@ int nvfp4_dual_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b1, 
                      stream);
 }
 
-int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* const* b,
+int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const void* const* b,
                           const void* const* sfa, const void* const* sfb, void* const* d,
                           void* workspace, void* stream) {
   if (plan == nullptr || plan->kind != kGrouped) {
@@ -1013,13 +1106,15 @@ int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* co
       return fail(NVFP4_E_MISALIGNED, "group %zu: operands must be 16-byte aligned", g);
     }
   }
+  // The group table and the tensor maps are built in a buffer of this call and copied into
+  // the workspace: the plan itself is not modified.
   const size_t table_bytes = plan->off_partials - plan->off_table;
-  plan->staging.assign(table_bytes, 0);
-  ProblemDesc* table = reinterpret_cast<ProblemDesc*>(plan->staging.data());
+  std::vector<uint8_t> staging(table_bytes, 0);
+  ProblemDesc* table = reinterpret_cast<ProblemDesc*>(staging.data());
   CUtensorMap* maps =
-      reinterpret_cast<CUtensorMap*>(plan->staging.data() + (plan->off_maps - plan->off_table));
+      reinterpret_cast<CUtensorMap*>(staging.data() + (plan->off_maps - plan->off_table));
   for (size_t g = 0; g < groups; ++g) {
-    ProblemDesc& pd = plan->problems[g];
+    ProblemDesc pd = plan->problems[g];
     pd.sfa = static_cast<const uint8_t*>(sfa[g]);
     pd.sfb = static_cast<const uint8_t*>(sfb[g]);
     pd.sfb2 = nullptr;
@@ -1033,22 +1128,30 @@ int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* co
   }
   DeviceGuard guard;
   CUDA_TRY(guard.enter(plan->device));
-  CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + plan->off_table,
-                           plan->staging.data(), table_bytes, cudaMemcpyHostToDevice,
+  // The source is pageable host memory: the runtime stages it before the call returns, so
+  // `staging` may go out of scope.
+  CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + plan->off_table, staging.data(),
+                           table_bytes, cudaMemcpyHostToDevice,
                            static_cast<cudaStream_t>(stream)));
-  plan->params_valid = true;
+  {
+    std::lock_guard<std::mutex> lock(plan->mutex);
+    plan->group_bound = true;
+  }
   return 0;
 }
 
-int nvfp4_group_gemm_launch(nvfp4_plan* plan, void* workspace, void* stream) {
+int nvfp4_group_gemm_launch(const nvfp4_plan* plan, void* workspace, void* stream) {
   if (plan == nullptr || plan->kind != kGrouped) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped GEMM plan");
   }
   if (workspace == nullptr || !aligned(workspace, 256)) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "workspace is null or not 256-byte aligned");
   }
-  if (!plan->params_valid) {
-    return fail(NVFP4_E_NOT_BOUND, "call nvfp4_group_gemm_bind on a workspace first");
+  {
+    std::lock_guard<std::mutex> lock(plan->mutex);
+    if (!plan->group_bound) {
+      return fail(NVFP4_E_NOT_BOUND, "call nvfp4_group_gemm_bind on a workspace first");
+    }
   }
   // The group table and tensor maps live in the workspace, so one plan can serve
   // several bound workspaces (different operand sets of the same shapes).
@@ -1070,7 +1173,10 @@ int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int
   CUDA_TRY(cudaStreamSynchronize(s));
   *status = value;
   if (value != 0) {
-    CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int), s));
+    // A launch that gave up may have left tile arrival counters of the stream-K schedule
+    // non-zero: clear them with the status word, as nvfp4_plan_init_workspace does, so that
+    // the workspace can be used again.
+    CUDA_TRY(cudaMemsetAsync(workspace, 0, plan->off_table, s));
     return fail(NVFP4_E_DEVICE_TIMEOUT, "kernel abandoned a bounded wait (code %d)", value);
   }
   return 0;
@@ -1087,7 +1193,8 @@ int nvfp4_pack_scales(const void* scales, void* packed, int rows, int cols, int 
   const long long lines =
       static_cast<long long>(batches) * ceil_div(rows, 128) * ceil_div(cols, 4) * 32;
   const int threads = 256;
-  const long long blocks = std::min<long long>((lines + threads - 1) / threads, 148 * 16);
+  const long long blocks =
+      std::min<long long>((lines + threads - 1) / threads, 16ll * current_sm_count());
   pack_scales_kernel<<<static_cast<unsigned int>(blocks), threads, 0,
                        static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(scales), static_cast<uint8_t*>(packed), rows, cols, batches);
@@ -1113,7 +1220,8 @@ int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int ro
   const long long total = static_cast<long long>(batches) * ceil_div(rows, 128) * 128 *
                           ceil_div(k / 16, 4) * 4;
   const int threads = 256;
-  const long long blocks = std::min<long long>((total + threads - 1) / threads, 148 * 32);
+  const long long blocks =
+      std::min<long long>((total + threads - 1) / threads, 32ll * current_sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned int grid = static_cast<unsigned int>(blocks);
   uint8_t* p8 = static_cast<uint8_t*>(packed);
@@ -1199,7 +1307,8 @@ int nvfp4_silu_product(const float* h1, const float* h2, void* out, int64_t size
   const int vector_ok = aligned(h1, 16) && aligned(h2, 16) && aligned(out, 16) ? 1 : 0;
   const int threads = 256;
   const long long work = vector_ok ? (size + 7) / 8 : size;
-  const long long blocks = std::min<long long>((work + threads - 1) / threads, 148 * 16);
+  const long long blocks =
+      std::min<long long>((work + threads - 1) / threads, 16ll * current_sm_count());
   silu_product_kernel<<<static_cast<unsigned int>(blocks), threads, 0,
                         static_cast<cudaStream_t>(stream)>>>(
       h1, h2, static_cast<__half*>(out), static_cast<long long>(size), vector_ok);

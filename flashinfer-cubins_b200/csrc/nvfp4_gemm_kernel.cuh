@@ -90,7 +90,7 @@ struct alignas(64) KernelParams {
   int num_problems;
   int mode;
   int b_streams;  // B is read once: mark its loads evict-first in L2
-  int probe;      // timing experiments only; ignored unless built with NVFP4_PROBE
+  int pad1;
   int split;      // > 1: CTAs of a cluster of this size split each tile's K (stream-K mode
                   // with grid = tiles * split) and reduce through peer shared memory
   int ring_stages;   // pipeline stages in use (fewer than the kernel's when the top of the
@@ -99,13 +99,6 @@ struct alignas(64) KernelParams {
                      // write only after this CTA has told them its pipeline memory is free
   int pad2;
 };
-
-// Timing experiments (results become wrong): compiled out of the product build.
-#ifdef NVFP4_PROBE
-#define NVFP4_PROBE_FLAG(p, bit) (((p).probe >> (bit)) & 1)
-#else
-#define NVFP4_PROBE_FLAG(p, bit) 0
-#endif
 
 struct Segment {
   int prob;
@@ -459,12 +452,11 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
   const int width = Cfg::OUT_BN / split;  // output columns per owner, a multiple of 32
   const int chunks = width / 32;
   const int lane = row & 31;
-  const bool no_exchange = NVFP4_PROBE_FLAG(p, 18);  // timing experiment
   // Bytes one CTA sends to one peer: the peer's columns of both accumulator halves, as
   // float4 [chunk][half][column / 4][row].
   const uint32_t portion = static_cast<uint32_t>(chunks * HALVES) * 16384u;
   uint32_t inbox = staging;  // where peers' columns arrive
-  if (p.inbox_offset >= 0 && !no_exchange) {
+  if (p.inbox_offset >= 0) {
     // Inbox path: the top of the pipeline memory was never used by this launch's pipeline, so
     // peers need no permission to write there. Every CTA puts the columns of each peer
     // into its own (now idle) pipeline memory with plain stores and sends them with one
@@ -510,7 +502,7 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
       report_failure(p, abort_ptr, kStatusClusterTimeout);
       return;
     }
-  } else if (!no_exchange) {
+  } else {
   // 1. My pipeline memory is free: tell every peer it may write into it.
   if (epi_tid == 0) {
     for (int peer = 0; peer < split; ++peer) {
@@ -671,7 +663,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   tc_fence_before_sync();
   __syncthreads();
   // Peers arrive on this CTA's barriers, so they must be initialised cluster-wide.
-  if (p.split > 1 && !NVFP4_PROBE_FLAG(p, 19)) cluster_sync_all();
+  if (p.split > 1) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
@@ -682,9 +674,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   grid_dependency_wait();
   grid_launch_dependents();
 
-  if (NVFP4_PROBE_FLAG(p, 12)) {
-    // timing experiment: prologue and teardown only
-  } else if (warp == 0) {
+  if (warp == 0) {
     // ------------------------------------------------------------------ producer
     // The whole warp runs the loop (waits included); one elected lane issues the copies.
     {
@@ -727,8 +717,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           sfb_src[i] = nb < pd.sf_nb ? base + (atom_row_b * pd.sf_kb + 4ll * s.k0) * 512 : nullptr;
           if (nb < pd.sf_nb) ++sfb_valid;
         }
-        const bool probe_no_ab = NVFP4_PROBE_FLAG(p, 2);
-        const uint32_t ab_bytes = probe_no_ab ? 0u : Cfg::A_BYTES + Cfg::B_BYTES;
+        constexpr uint32_t ab_bytes = Cfg::A_BYTES + Cfg::B_BYTES;
         int atoms_left = pd.sf_kb - 4 * s.k0;
         int kbyte = s.k0 * 128;
         for (int kt = s.k0; kt < s.k1; ++kt) {
@@ -748,27 +737,19 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           // scale movers can put them into tensor memory while A and B are still in
           // flight.
           if (elect_one()) {
-            if (!NVFP4_PROBE_FLAG(p, 5)) {
-              mbar_expect_tx(sf_bar, sf_bytes * (1u + sfb_valid));
-              bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol_a);
+            mbar_expect_tx(sf_bar, sf_bytes * (1u + sfb_valid));
+            bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol_a);
 #pragma unroll
-              for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
-                if (sfb_src[i] != nullptr) {
-                  bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, sf_bar, pol_b);
-                }
+            for (int i = 0; i < Cfg::SFB_BLOCKS; ++i) {
+              if (sfb_src[i] != nullptr) {
+                bulk_load(sfb_dst + i * 2048, sfb_src[i], sf_bytes, sf_bar, pol_b);
               }
-            } else {
-              mbar_arrive(sf_bar);
             }
-            if (!probe_no_ab) {
-              mbar_expect_tx(bar, ab_bytes);
-              tma_load_3d(a_dst, map_a, bar, kbyte, m0, s.batch, pol_a);
-              tma_load_3d(b_dst, map_b, bar, kbyte, n0, s.batch, pol_b);
-              if constexpr (Cfg::DUAL) {
-                tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kbyte, n0, s.batch, pol_b);
-              }
-            } else {
-              mbar_arrive(bar);
+            mbar_expect_tx(bar, ab_bytes);
+            tma_load_3d(a_dst, map_a, bar, kbyte, m0, s.batch, pol_a);
+            tma_load_3d(b_dst, map_b, bar, kbyte, n0, s.batch, pol_b);
+            if constexpr (Cfg::DUAL) {
+              tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kbyte, n0, s.batch, pol_b);
             }
           }
           __syncwarp();
@@ -840,7 +821,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           const uint32_t lo_b = lo_b0 + stage16;
           const uint32_t t_sfb = t_sf + 16 + sfb_half;
           if (elect_one()) {
-            if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 1)) {
+            if (atoms_left >= 4) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
@@ -848,8 +829,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                             t_sfb + j * Cfg::SFB_COLS, j > 0 ? 1u : accumulate);
               }
             } else {
-              // K tail: fewer than four 64-wide blocks left (or a timing experiment).
-              const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
+              // K tail: fewer than four 64-wide blocks left.
+              const int mmas = min(4, atoms_left);
               for (int j = 0; j < mmas; ++j) {
                 tc_mma_nvf4(d_tmem, pack_desc(lo_a + 2 * j, kHiOperand),
                             pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
@@ -905,7 +886,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           ok = false;
           break;
         }
-        const int atoms = NVFP4_PROBE_FLAG(p, 13) ? 0 : min(4, atoms_left);
+        const int atoms = min(4, atoms_left);
         if (atoms == 4) {
           uint4 va[4];
           uint4 vb[4][Cfg::SFB_BLOCKS];
@@ -967,8 +948,6 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           t_sf = tmem_base + lane_base + Cfg::SF_COL;
         }
       }
-    }
-    if (warp == 6 && lane == 0) {
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------------ epilogue
@@ -1083,9 +1062,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             tmem_load_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              v[i] = NVFP4_PROBE_FLAG(p, 10)
-                         ? __uint_as_float(r1[i]) + __uint_as_float(r2[i])
-                         : silu_f32(__uint_as_float(r1[i]) * alpha) * (__uint_as_float(r2[i]) * alpha);
+              v[i] = silu_f32(__uint_as_float(r1[i]) * alpha) * (__uint_as_float(r2[i]) * alpha);
             }
           } else {
             tmem_load_wait();
@@ -1096,10 +1073,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bar_acc_empty[acc]));
           }
-          if (!NVFP4_PROBE_FLAG(p, 11)) {
-            store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
-                                   rows_valid, lane, v);
-          }
+          store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
+                                 rows_valid, lane, v);
         }
       } else if (!Cfg::GROUPED && p.split > 1) {  // grouped plans never split in clusters
         cluster_reduce<Cfg>(p, pd, s, taddr, smem_base, smem_u32(&bar_peer_ready),
@@ -1120,13 +1095,12 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           tmem_load_wait();
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            if (NVFP4_PROBE_FLAG(p, 7)) break;
             ws[(c * 8 + q) * 128 + row] =
                 make_float4(__uint_as_float(r1[4 * q]), __uint_as_float(r1[4 * q + 1]),
                             __uint_as_float(r1[4 * q + 2]), __uint_as_float(r1[4 * q + 3]));
           }
         }
-        if (!NVFP4_PROBE_FLAG(p, 9)) __threadfence();
+        __threadfence();
         named_barrier_sync(1, 128);
         const long long unit_last = s.tile_unit0 + pd.k_tiles - 1;
         const long long first_cta = ((s.tile_unit0 + 1) * grid - 1) / p.total_units;
@@ -1153,9 +1127,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             // Partials are added in segment order, so the sum does not depend on which
             // CTA arrives last: the segments before this CTA's from the workspace, its
             // own straight from tensor memory (it is still there), then the rest.
-            const long long stop_before = NVFP4_PROBE_FLAG(p, 8) ? first_cta - 1 : cta - 1;
-            const long long stop_after = NVFP4_PROBE_FLAG(p, 8) ? cta : last_cta;
-            add_partials<Cfg>(p, s1, s2, first_cta, stop_before, s.tile_unit0, grid, c, row);
+            add_partials<Cfg>(p, s1, s2, first_cta, cta - 1, s.tile_unit0, grid, c, row);
             {
               uint32_t own[32];
               tmem_load_32(taddr + c * 32, own);
@@ -1169,7 +1141,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                 for (int i = 0; i < 32; ++i) s2[i] += __uint_as_float(own[i]);
               }
             }
-            add_partials<Cfg>(p, s1, s2, cta + 1, stop_after, s.tile_unit0, grid, c, row);
+            add_partials<Cfg>(p, s1, s2, cta + 1, last_cta, s.tile_unit0, grid, c, row);
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -1196,7 +1168,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   tc_fence_before_sync();
   __syncthreads();
   // No CTA of a cluster leaves while a peer could still write into its shared memory.
-  if (p.split > 1 && !NVFP4_PROBE_FLAG(p, 19)) cluster_sync_all();
+  if (p.split > 1) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
     __syncwarp();

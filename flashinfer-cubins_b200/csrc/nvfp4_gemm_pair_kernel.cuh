@@ -224,15 +224,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
             bulk_load(sfb_dst, sfb_src0, sf_bytes, sf_bar, pol);
             if (sfb1_valid) bulk_load(sfb_dst + 2048, sfb_src1, sf_bytes, sf_bar, pol);
             // The leader arms its full barrier for the A and B bytes of both CTAs.
-            if (NVFP4_PROBE_FLAG(p, 2)) {
-              if (leader) mbar_arrive(smem_u32(&bar_full[stage]));
-            } else {
-              if (leader) {
-                mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
-              }
-              tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
-              tma_load_3d_pair(b_dst, map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
+            if (leader) {
+              mbar_expect_tx(smem_u32(&bar_full[stage]), 2u * (Cfg::A_BYTES + Cfg::B_BYTES));
             }
+            tma_load_3d_pair(a_dst, &p.map_a, leader_full0 + 8 * stage, kbyte, m0, batch, pol);
+            tma_load_3d_pair(b_dst, map_b, leader_full0 + 8 * stage, kbyte, n0, batch, pol);
           }
           __syncwarp();
           sfa_src += 2048;
@@ -286,7 +282,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           const uint32_t lo_a = lo_a0 + stage16;
           const uint32_t lo_b = lo_b0 + stage16;
           if (elect_one()) {
-            if (atoms_left >= 4 && !NVFP4_PROBE_FLAG(p, 1)) {
+            if (atoms_left >= 4) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 tc_mma_nvf4_pair(tmem_base, pack_desc(lo_a + 2 * j, kHiOperand),
@@ -294,7 +290,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
                                  t_sf + 16 + 8 * j, j > 0 ? 1u : accumulate);
               }
             } else {
-              const int mmas = NVFP4_PROBE_FLAG(p, 1) ? 0 : min(4, atoms_left);
+              const int mmas = min(4, atoms_left);
               for (int j = 0; j < mmas; ++j) {
                 tc_mma_nvf4_pair(tmem_base, pack_desc(lo_a + 2 * j, kHiOperand),
                                  pack_desc(lo_b + 2 * j, kHiOperand), idesc, t_sf + 4 * j,
@@ -340,11 +336,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           ok = false;
           break;
         }
-        const int atoms = NVFP4_PROBE_FLAG(p, 13) ? 0 : min(4, atoms_left);
-        if (NVFP4_PROBE_FLAG(p, 14)) {  // timing experiment: signal before the work
-          __syncwarp();
-          if (lane == 0) mbar_arrive_peer(leader_full0 + 8 * stage);
-        }
+        const int atoms = min(4, atoms_left);
         if (atoms == 4) {
           // All twelve loads first, then the twelve stores: the loads overlap.
           uint4 va[4], vb0[4], vb1[4];
@@ -370,7 +362,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         tmem_store_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0 && !NVFP4_PROBE_FLAG(p, 14)) mbar_arrive_peer(leader_full0 + 8 * stage);
+        if (lane == 0) mbar_arrive_peer(leader_full0 + 8 * stage);
         atoms_left -= 4;
         sf_smem += Cfg::STAGE_BYTES;
         t_sf += Cfg::SF_STAGE_COLS;

@@ -100,6 +100,7 @@ _PROTOTYPES = {
     "nvfp4_gemm_launch_fp4": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_gemm_launch_static": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_static_scratch_bytes": (ctypes.c_size_t, []),
+    "nvfp4_static_status": (ctypes.c_int, [ctypes.c_int, _P, ctypes.POINTER(ctypes.c_int)]),
     "nvfp4_dual_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_group_gemm_bind": (
         ctypes.c_int,
@@ -287,6 +288,15 @@ class Plan:
             self.destroy()
         except Exception:
             pass
+
+
+def static_status(device: int, stream: int) -> int:
+    """Synchronise ``stream`` and return the status word shared by the launches on the
+    built-in scratch array of ``device`` (0 = ok); raises ``NativeError`` if one of them
+    abandoned a bounded wait."""
+    value = ctypes.c_int(0)
+    check(load().nvfp4_static_status(device, stream, ctypes.byref(value)))
+    return value.value
 
 
 def pack_scales(scales: int, packed: int, rows: int, cols: int, batches: int, stream: int) -> None:

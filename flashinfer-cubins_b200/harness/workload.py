@@ -252,26 +252,31 @@ class Workload(ABC):
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def plan_for(self, key: Any, create: Callable[[], native.Plan]):
-        """(plan, workspace tensor) cached under ``key``. The workspace is a torch
-        allocation owned by the workload, zeroed once when the plan is made."""
+        """(plan, workspace tensor) cached under ``key`` and the current stream. The
+        workspace is a torch allocation owned by the workload, zeroed on that stream
+        when the entry is made: launches on another stream get a plan and a workspace
+        of their own, so a workspace is never shared by launches that could overlap and
+        never used before its initialisation has run. A launch callable returned by
+        ``prepare`` belongs to the stream that was current when it was prepared."""
         with self._lock:
-            entry = self._plans.get(key)
+            stream = self.stream_handle()
+            entry = self._plans.get((key, stream))
             if entry is None:
                 plan = create()
                 size = max(plan.workspace_bytes(), 256)
                 with torch.cuda.device(self.device):
                     workspace = torch.empty(size, dtype=torch.uint8, device=self.device)
-                    plan.init_workspace(workspace.data_ptr(), self.stream_handle())
+                    plan.init_workspace(workspace.data_ptr(), stream)
                 entry = (plan, workspace)
-                self._plans[key] = entry
+                self._plans[(key, stream)] = entry
             return entry
 
     def check_status(self) -> None:
         """Synchronise and raise ``native.NativeError`` if a kernel of any cached plan
         abandoned a bounded wait."""
         with self._lock:
-            for plan, workspace in self._plans.values():
-                plan.status(workspace.data_ptr(), self.stream_handle())
+            for (_, stream), (plan, workspace) in self._plans.items():
+                plan.status(workspace.data_ptr(), stream)
 
     def _drop_plans(self) -> None:
         if self._plans:

@@ -18,6 +18,13 @@
  *     launch. The workspace must be initialised once with nvfp4_plan_init_workspace
  *     (it zeroes the status word and the per-tile arrival counters) and must not be
  *     shared by launches that can overlap on the GPU.
+ *   - A plan is immutable once created. Launches of one plan may be issued from several
+ *     host threads and on several streams at the same time, each with its own workspace;
+ *     the only state a launch shares is a mutex-guarded cache of encoded tensor maps
+ *     keyed by the operand addresses. nvfp4_plan_destroy must not race with a launch.
+ *   - Tensor maps of operands smaller than 128 KiB declare a batch extent that covers
+ *     addresses past the end of the operand; those batches are never addressed, so
+ *     nothing beyond the operand is read.
  *   - Operand layout (harness/workloads/quantization.py:1-37): packed E2M1 bytes,
  *     low nibble = even K index, K contiguous, storage [batch][rows][k/2]; UE4M3
  *     scales, one per 16 K elements, in the blocked layout
@@ -120,9 +127,10 @@ int nvfp4_plan_info_get(const nvfp4_plan* plan, nvfp4_plan_info* info);
 
 /* One dense GEMM launch. Replaces CutlassFp4Gemm.launch_config + _launch
  * (harness/workloads/nvfp4_gemm.py:395-435). `alpha` is a device FP32 scalar read by
- * the kernel (nvfp4_gemm.py:35-39); `d` is FP16 or FP32 per the plan. Tensor maps are
- * re-encoded only when a pointer differs from the previous launch of this plan. */
-int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+ * the kernel (nvfp4_gemm.py:35-39); `d` is FP16, BF16 or FP32 per the plan. Tensor maps
+ * are encoded once per set of operand addresses (the plan remembers the sixteen most
+ * recently used sets). */
+int nvfp4_gemm_launch(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                       const void* sfb, const float* alpha, void* d, void* workspace,
                       void* stream);
 
@@ -134,7 +142,7 @@ int nvfp4_gemm_launch(nvfp4_plan* plan, const void* a, const void* b, const void
  * the bytes follow. `d_packed` is [l][m][n/2] bytes, `d_scales` the blocked layout
  * [l][ceil(m/128)][n/64][32][4][4]; rows beyond m in the last atom row are not written.
  * The result equals nvfp4_quantize applied to the FP32 product alpha * A * B^T. */
-int nvfp4_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+int nvfp4_gemm_launch_fp4(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                           const void* sfb, const float* alpha, void* d_packed, void* d_scales,
                           void* workspace, void* stream);
 
@@ -146,7 +154,7 @@ int nvfp4_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b, const 
  * reference. */
 int nvfp4_dual_gemm_plan_create_fp4(nvfp4_plan** plan, int device, int m, int n, int k, int l,
                                     const nvfp4_config* config);
-int nvfp4_dual_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+int nvfp4_dual_gemm_launch_fp4(const nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
                                const void* sfa, const void* sfb1, const void* sfb2,
                                const float* alpha, void* d_packed, void* d_scales,
                                void* workspace, void* stream);
@@ -163,15 +171,23 @@ int nvfp4_dual_gemm_launch_fp4(nvfp4_plan* plan, const void* a, const void* b1, 
  * launches. The first call on a device also looks the array's address up; make that
  * first call before any stream capture begins. All calls on a device share the one
  * array, so two such launches that can overlap on the GPU (different streams, no
- * ordering between them) race; nvfp4_plan_status is not meaningful for this array. */
-int nvfp4_gemm_launch_static(nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
+ * ordering between them) race. The status word of these launches is read with
+ * nvfp4_static_status, not nvfp4_plan_status. */
+int nvfp4_gemm_launch_static(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                              const void* sfb, const float* alpha, void* d, void* stream);
 
 /* Size in bytes of the built-in scratch array used by nvfp4_gemm_launch_static. */
 size_t nvfp4_static_scratch_bytes(void);
 
-/* One fused dual-GEMM launch (see nvfp4_dual_gemm_plan_create). */
-int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
+/* Synchronises `stream` and reads the status word that nvfp4_gemm_launch_static launches
+ * on `device` share into *status; returns NVFP4_E_DEVICE_TIMEOUT if a launch abandoned a
+ * bounded wait since the word was last cleared (every nvfp4_gemm_launch_static clears it
+ * before it launches). Allocates nothing. No counterpart in the reference. */
+int nvfp4_static_status(int device, void* stream, int* status);
+
+/* One fused dual-GEMM launch (see nvfp4_dual_gemm_plan_create). `d` must be 16-byte
+ * aligned, except that rows of n % 8 == 4 FP16 elements need only 8 bytes. */
+int nvfp4_dual_gemm_launch(const nvfp4_plan* plan, const void* a, const void* b1, const void* b2,
                            const void* sfa, const void* sfb1, const void* sfb2,
                            const float* alpha, void* d, void* workspace, void* stream);
 
@@ -179,7 +195,7 @@ int nvfp4_dual_gemm_launch(nvfp4_plan* plan, const void* a, const void* b1, cons
  * encodes the per-group tensor maps and copies the group table into the workspace
  * (one stream-ordered host-to-device copy). Replaces NVFP4GroupGEMM.launch_config
  * (harness/workloads/nvfp4_group_gemm.py:514-591). */
-int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* const* b,
+int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const void* const* b,
                           const void* const* sfa, const void* const* sfb, void* const* d,
                           void* workspace, void* stream);
 
@@ -187,10 +203,13 @@ int nvfp4_group_gemm_bind(nvfp4_plan* plan, const void* const* a, const void* co
  * nvfp4_group_gemm_bind wrote into `workspace` (one plan may be bound to several
  * workspaces, one per operand set). Replaces NVFP4GroupGEMM._launch
  * (harness/workloads/nvfp4_group_gemm.py:593-600). */
-int nvfp4_group_gemm_launch(nvfp4_plan* plan, void* workspace, void* stream);
+int nvfp4_group_gemm_launch(const nvfp4_plan* plan, void* workspace, void* stream);
 
-/* Synchronises `stream`, reads the workspace's status word into *status and clears
- * it. Returns NVFP4_E_DEVICE_TIMEOUT if it was non-zero. */
+/* Synchronises `stream` and reads the workspace's status word into *status. If it was
+ * non-zero (a kernel abandoned a bounded wait), returns NVFP4_E_DEVICE_TIMEOUT and
+ * re-initialises the workspace's status word and tile arrival counters (stream-ordered),
+ * so that the workspace can be launched on again; the output of the abandoned launch is
+ * undefined. */
 int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int* status);
 
 /* Logical E4M3 scales [batches][rows][cols] -> blocked layout, zero padded, flat

@@ -330,6 +330,89 @@ def test_grouped_stream_k_and_rebinding():
     plan.destroy()
 
 
+def test_one_plan_launched_from_two_threads_on_two_streams():
+    """A plan is immutable after creation: two host threads launch the same stream-K plan
+    at the same time, each on its own stream with its own workspace and operands, and
+    alternate between two operand sets (so the plan's tensor-map cache is looked up and
+    filled concurrently). Every result must be bit-identical to the oracle."""
+    import threading
+
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    m, n, k = 256, 384, 4096
+    plan = native.Plan.dense(0, native.OUT_F16, m, n, k, 1, schedule=2, tile_n=128)
+    assert plan.info()["schedule"] == "stream_k"
+    jobs, errors = [], []
+    for t in range(2):
+        stream = torch.cuda.Stream(device=dev)
+        sets = []
+        for seed in (40 + 2 * t, 41 + 2 * t):
+            inputs = workload.get_inputs(CaseSpec("threads", {"m": m, "n": n, "k": k, "l": 1}, seed))
+            want = oracle_dense(inputs)
+            d = torch.full((1, m, n), float("nan"), dtype=torch.float16, device=dev)
+            sets.append((inputs, d, want))
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        jobs.append((stream, sets, ws))
+    torch.cuda.synchronize()
+    start = threading.Barrier(2)
+
+    def worker(stream, sets, ws):
+        try:
+            start.wait()
+            for i in range(200):
+                inputs, d, _ = sets[i % 2]
+                plan.launch_dense(*(t.data_ptr() for t in inputs), d.data_ptr(), ws.data_ptr(),
+                                  stream.cuda_stream)
+            stream.synchronize()
+        except Exception as error:  # surfaced in the main thread below
+            errors.append(error)
+
+    threads = [threading.Thread(target=worker, args=job) for job in jobs]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    assert not errors, errors
+    for stream, sets, ws in jobs:
+        assert plan.status(ws.data_ptr(), stream.cuda_stream) == 0
+        for inputs, d, want in sets:
+            assert np.array_equal(d.cpu().numpy(), want)
+    plan.destroy()
+
+
+def test_status_word_and_counters_are_reset_after_a_reported_timeout():
+    """nvfp4_plan_status on a workspace whose status word is set (written here by the host,
+    standing in for a kernel that abandoned a wait) reports the timeout once and
+    re-initialises the status word *and* the stream-K tile counters, so that the next
+    launch on that workspace is correct again."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    m, n, k = 128, 256, 4096
+    plan = native.Plan.dense(0, native.OUT_F16, m, n, k, 1, schedule=2, tile_n=128)
+    inputs = workload.get_inputs(CaseSpec("reset", {"m": m, "n": n, "k": k, "l": 1}, 9))
+    want = oracle_dense(inputs)
+    ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+    plan.init_workspace(ws.data_ptr(), stream)
+    # What an abandoned stream-K launch leaves behind: a status code and arrival counters
+    # that never reached their reset.
+    words = ws[:512].view(torch.int32)
+    words[0] = 2
+    words[64:66] = 1
+    with pytest.raises(native.NativeError):
+        plan.status(ws.data_ptr(), stream)
+    torch.cuda.synchronize()
+    assert int(words[0]) == 0 and int(words[64]) == 0 and int(words[65]) == 0
+    d = torch.full((1, m, n), float("nan"), dtype=torch.float16, device=dev)
+    plan.launch_dense(*(t.data_ptr() for t in inputs), d.data_ptr(), ws.data_ptr(), stream)
+    assert plan.status(ws.data_ptr(), stream) == 0
+    assert np.array_equal(d.cpu().numpy(), want)
+    plan.destroy()
+
+
 def test_native_rejects_misaligned_and_wrong_plans():
     stream = torch.cuda.current_stream().cuda_stream
     plan = native.Plan.dense(0, native.OUT_F16, 128, 128, 128, 1)
@@ -343,6 +426,23 @@ def test_native_rejects_misaligned_and_wrong_plans():
         native.Plan.dense(0, native.OUT_F16, 128, 128, 128, 1, tile_n=96)
     assert native.device_supported(0)
     plan.destroy()
+    # Fused dual GEMM: D at 8 modulo 16 is accepted only when rows are n % 8 == 4 elements
+    # long (8-byte stores); with n % 8 == 0 the kernel stores 16 bytes at a time. The
+    # checks come before any launch, so the buffer's contents do not matter.
+    for n, accepted in ((128, False), (132, True)):
+        dual = native.Plan.dual(0, 128, n, 128, 1)
+        ws = torch.zeros(max(dual.workspace_bytes(), 256), dtype=torch.uint8, device="cuda")
+        dual.init_workspace(ws.data_ptr(), stream)
+        args = (base, base + 65536, base + 131072, base + 196608, base + 262144, base + 327680,
+                base + 393216)
+        if accepted:
+            dual.launch_dual(*args, base + 458752 + 8, ws.data_ptr(), stream)
+            torch.cuda.synchronize()
+            assert dual.status(ws.data_ptr(), stream) == 0
+        else:
+            with pytest.raises(ValueError):
+                dual.launch_dual(*args, base + 458752 + 8, ws.data_ptr(), stream)
+        dual.destroy()
 
 
 @pytest.mark.parametrize("rows,k,batches", [(128, 256, 1), (200, 96, 2), (1, 32, 1), (1000, 4096, 1)])

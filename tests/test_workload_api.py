@@ -236,3 +236,22 @@ def test_reference_only_workload_has_no_image():
     with pytest.raises(ValueError):
         NVFP4GEMM(b"\x7fELF not ours", device="cpu")
     assert isinstance(workload, Workload) and Path(native.LIBRARY_PATH).name.endswith(".so")
+
+
+def test_fused_dual_gemm_output_alignment_follows_the_store_width():
+    """Rows of D are stored in 16-byte pieces unless n % 8 == 4, so only then may D be
+    merely 8-byte aligned: a slice of a larger tensor must not reach the kernel otherwise."""
+    fused = get_workload("nvfp4_dual_gemm")(None, device="cpu")
+    for n, offsets_ok in ((136, {0: True, 4: False}), (132, {0: True, 4: True, 2: False})):
+        case = CaseSpec("alignment", {"m": 128, "n": n, "k": 64, "l": 1}, 3)
+        inputs = fused.get_inputs(case)
+        for offset, ok in offsets_ok.items():
+            backing = torch.empty(128 * n + 64, dtype=torch.float16)
+            base = (-backing.data_ptr() % 16) // 2  # first 16-byte aligned element
+            flat = backing[base + offset: base + offset + 128 * n]
+            out = flat.view(1, 128, n).permute(1, 2, 0)
+            if ok:
+                assert fused.operands(inputs, out) == (128, n, 64, 1)
+            else:
+                with pytest.raises(ValueError):
+                    fused.operands(inputs, out)
