@@ -54,14 +54,15 @@ int fail_cuda(cudaError_t err, const char* what) {
 struct DeviceGuard {
   int saved = -1;
   bool active = false;
+  // Always sets the device, even when it is the current one: in a host thread that has made
+  // no CUDA call yet this is what binds the device's primary context to the thread, which
+  // driver entry points such as cuTensorMapEncodeTiled need.
   cudaError_t enter(int device) {
     cudaError_t e = cudaGetDevice(&saved);
     if (e != cudaSuccess) return e;
-    if (saved != device) {
-      e = cudaSetDevice(device);
-      if (e != cudaSuccess) return e;
-      active = true;
-    }
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess) return e;
+    active = saved != device;
     return cudaSuccess;
   }
   ~DeviceGuard() {
@@ -124,6 +125,28 @@ int encode_operand_map(CUtensorMap* map, const void* ptr, int rows, int k, int b
     return fail(static_cast<int>(res),
                 "cuTensorMapEncodeTiled failed (%d) for rows=%d k=%d batches=%d box_rows=%d",
                 static_cast<int>(res), rows, k, batches, box_rows);
+  }
+  return 0;
+}
+
+// 16-bit output D [batches][m][n] as a rank-3 tensor of 16-bit elements with a box of 64
+// columns (128 bytes) x 128 rows and 128-byte swizzle: what the 2-CTA kernel's epilogue
+// stores from its staging boxes. Needs rows of D 16-byte aligned (n a multiple of 8).
+int encode_output_map(CUtensorMap* map, void* ptr, int m, int n, int batches) {
+  EncodeTiledFn encode = nullptr;
+  if (int rc = get_encoder(&encode)) return rc;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(n) * 2;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m),
+                              static_cast<cuuint64_t>(batches)};
+  const cuuint64_t strides[2] = {row_bytes, row_bytes * static_cast<cuuint64_t>(m)};
+  const cuuint32_t box[3] = {64u, 128u, 1u};
+  const cuuint32_t elem_strides[3] = {1u, 1u, 1u};
+  CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, ptr, dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    return fail(static_cast<int>(res), "cuTensorMapEncodeTiled failed (%d) for D m=%d n=%d batches=%d",
+                static_cast<int>(res), m, n, batches);
   }
   return 0;
 }
@@ -703,6 +726,15 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     int want_pair = config != nullptr ? config->pair : 0;
     if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
     if (out_kind == NVFP4_OUT_FP4) want_pair = -1;  // whole tiles in one CTA, single-CTA kernel
+    // The 2-CTA kernel stores 16-bit output through a tensor map: rows 16-byte aligned.
+    if (out_kind != NVFP4_OUT_F32 && n % 8 != 0) {
+      if (want_pair > 0) {
+        delete plan;
+        return fail(NVFP4_E_UNSUPPORTED_SHAPE,
+                    "the 2-CTA kernel needs n to be a multiple of 8 for 16-bit output");
+      }
+      want_pair = -1;
+    }
     const bool explicit_choice =
         (config != nullptr && (config->tile_n > 0 || config->schedule > 0 || config->ctas > 0)) ||
         env_int("NVFP4_TILE_N", 0) > 0 || env_int("NVFP4_SCHEDULE", 0) > 0 ||
@@ -871,6 +903,8 @@ int launch_dense(const nvfp4_plan* plan, const void* a, const void* b, const voi
       !aligned(d, 16) || !aligned(sfd, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
   const void* key[10] = {a, b, nullptr, sfa, sfb, sfd, alpha, d, nullptr, workspace};
   KernelParams kp;
   const int rc = bound_params(
@@ -883,6 +917,10 @@ int launch_dense(const nvfp4_plan* plan, const void* a, const void* b, const voi
           return rc;
         }
         fresh.map_b2 = fresh.map_b;
+        fresh.map_d = fresh.map_a;  // a valid descriptor; used by the 2-CTA kernel only
+        if (plan->pair && (plan->out_kind == NVFP4_OUT_F16 || plan->out_kind == NVFP4_OUT_BF16)) {
+          if (int rc = encode_output_map(&fresh.map_d, d, pd.m, pd.n, pd.batches)) return rc;
+        }
         pd.sfa = static_cast<const uint8_t*>(sfa);
         pd.sfb = static_cast<const uint8_t*>(sfb);
         pd.sfb2 = nullptr;
@@ -1029,6 +1067,8 @@ int launch_dual(const nvfp4_plan* plan, const void* a, const void* b1, const voi
       !aligned(sfd, 16) || !aligned(alpha, 4) || !aligned(workspace, 256)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
   const void* key[10] = {a, b1, b2, sfa, sfb1, sfb2, alpha, d, sfd, workspace};
   KernelParams kp;
   const int rc = bound_params(
@@ -1043,6 +1083,10 @@ int launch_dual(const nvfp4_plan* plan, const void* a, const void* b1, const voi
         if (int rc = encode_operand_map(&fresh.map_b2, b2, pd.n, pd.k, pd.batches,
                                         plan->out_tile_n)) {
           return rc;
+        }
+        fresh.map_d = fresh.map_a;
+        if (plan->pair) {
+          if (int rc = encode_output_map(&fresh.map_d, d, pd.m, pd.n, pd.batches)) return rc;
         }
         pd.sfa = static_cast<const uint8_t*>(sfa);
         pd.sfb = static_cast<const uint8_t*>(sfb1);
@@ -1106,6 +1150,8 @@ int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const vo
       return fail(NVFP4_E_MISALIGNED, "group %zu: operands must be 16-byte aligned", g);
     }
   }
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
   // The group table and the tensor maps are built in a buffer of this call and copied into
   // the workspace: the plan itself is not modified.
   const size_t table_bytes = plan->off_partials - plan->off_table;
@@ -1126,8 +1172,6 @@ int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const vo
     if (int rc = encode_operand_map(&tmp, b[g], pd.n, pd.k, 1, plan->tile_n)) return rc;
     std::memcpy(&maps[2 * g + 1], &tmp, sizeof(tmp));
   }
-  DeviceGuard guard;
-  CUDA_TRY(guard.enter(plan->device));
   // The source is pageable host memory: the runtime stages it before the call returns, so
   // `staging` may go out of scope.
   CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + plan->off_table, staging.data(),

@@ -78,6 +78,7 @@ enum : int {
 
 struct alignas(64) KernelParams {
   CUtensorMap map_a, map_b, map_b2;  // dense / dual: by value
+  CUtensorMap map_d;  // 2-CTA kernel, 16-bit output: D as [l][m][n], box 64 columns x 128 rows
   ProblemDesc dense;
   const ProblemDesc* problems;  // grouped: one per group, device memory
   const CUtensorMap* maps;      // grouped: maps[2g] = A_g, maps[2g + 1] = B_g
@@ -696,10 +697,23 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
       const uint32_t empty0 = smem_u32(&bar_empty[0]);
       bool ok = true;
+      int acquired_prob = -1;
       while (ok && it.next(s)) {
         const ProblemDesc& pd = it.pd;
         const CUtensorMap* map_a = Cfg::GROUPED ? &p.maps[2 * s.prob] : &p.map_a;
         const CUtensorMap* map_b = Cfg::GROUPED ? &p.maps[2 * s.prob + 1] : &p.map_b;
+        if constexpr (Cfg::GROUPED) {
+          // A group's tensor maps were copied into the workspace by the host; an earlier
+          // plan's maps may have lived at the same addresses.
+          if (s.prob != acquired_prob) {
+            if (elect_one()) {
+              tensormap_acquire(map_a);
+              tensormap_acquire(map_b);
+            }
+            __syncwarp();
+            acquired_prob = s.prob;
+          }
+        }
         const int m0 = s.m_tile * Cfg::BM;
         const int n0 = s.n_tile * Cfg::OUT_BN;
         // Scale atoms of this tile's rows: one 512-byte atom per 64 K elements, four per

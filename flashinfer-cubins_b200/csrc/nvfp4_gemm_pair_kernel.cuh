@@ -8,21 +8,30 @@
 // CTAs' shared memory): 38 KB per k-tile for the same 512 clocks. No cluster multicast is
 // involved: every byte a CTA needs is loaded by that CTA.
 //
-// Per CTA (320 threads, same roles as the single-CTA kernel):
+// Per CTA (448 threads):
 //   warp 0      TMA producer: own A rows, own half of B, own SFA atoms, all SFB atoms.
 //               The A/B copies of both CTAs complete on the *leader's* full barrier
 //               (cp.async.bulk.tensor ... .cta_group::2), which the leader arms for the
 //               bytes of both.
-//   warps 6-9   scale movers: this CTA's scale atoms -> this CTA's tensor memory; the
-//               movers of both CTAs arrive on the leader's full barrier (shared::cluster),
-//               so a stage is full after nine arrivals: the leader's producer + 8 movers.
+//   warps 6-9   scale movers: this CTA's scale atoms -> this CTA's tensor memory (shared ->
+//               registers -> tcgen05.st, one warp per 32-lane quarter); the movers of both
+//               CTAs arrive on the leader's full barrier (shared::cluster), so a stage is
+//               full after nine arrivals: the leader's producer + 8 movers.
 //   warp 1      leader CTA only: issues the MMAs (M = 256, N = 256, K = 64 each); its
 //               tcgen05.commit is multicast to both CTAs' barriers.
-//   warps 2-5   epilogue: each CTA stores its own 128 rows of the tile, coalesced through
-//               shared memory as in the single-CTA kernel.
+//   warps 2-5,  epilogue, two groups of four warps (one warp per 32-lane quarter of tensor
+//   10-13       memory in each). 16-bit output: a group owns half of the CTA's output
+//               columns. It reads them out of tensor memory into registers (rounded and
+//               packed), hands the accumulator back to the MMA issuer - the next tile's MMAs
+//               start here - and only then writes them, 64 columns at a time, into a 16 KB
+//               staging box in the 128-byte-swizzled layout and stores the box with one
+//               cp.async.bulk.tensor (which clips rows and columns beyond the tensor). The
+//               accumulator is single-buffered (tensor memory holds 256 accumulator columns
+//               and five stages of scales), so what the MMA issuer waits for per tile is
+//               four tcgen05.ld and two conversions per epilogue warp. FP32 output (the
+//               dual-GEMM stage) keeps one group and per-thread stores.
 // The producer and MMA warps run their loops with all lanes and elect one to issue.
-// Tiles are dealt round-robin to the pairs (data parallel, persistent). The accumulator
-// (256 columns) is single-buffered; 5 stages of 38 KB.
+// Tiles are dealt round-robin to the pairs (data parallel, persistent); 5 stages of 38 KB.
 #pragma once
 
 #include "nvfp4_gemm_kernel.cuh"
@@ -97,7 +106,10 @@ struct PairConfig {
   static constexpr int SF_STAGE_COLS = 16 + 4 * 8;
   static constexpr int SF_COL = TILE_N;  // after the accumulator's 256 columns
   static constexpr int TMEM_COLS = 512;
-  static constexpr int THREADS = 320;
+  static constexpr int THREADS = 448;
+  // 16-bit outputs leave through staged tensor stores; FP32 through per-thread stores.
+  static constexpr bool TMA_STORE = sizeof(OutT_) == 2;
+  static constexpr int STAGING_BYTES = TMA_STORE ? 2 * 16384 : 4 * 2048;
   static_assert(SF_COL + STAGES * SF_STAGE_COLS <= TMEM_COLS, "tensor memory exceeded");
 };
 
@@ -113,7 +125,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
   __shared__ alignas(8) uint64_t bar_sf_full[STAGES];  // each CTA: own scale atoms landed
   __shared__ alignas(8) uint64_t bar_acc_full;         // each CTA: tile accumulated
   __shared__ alignas(8) uint64_t bar_acc_empty;        // leader: both epilogues have drained
-  __shared__ alignas(16) uint8_t epi_stage[4][2048];   // per epilogue warp: 32 rows x 64 bytes
+  // TMA_STORE: per epilogue group one box of 128 rows x 128 bytes (64 columns), swizzled;
+  // otherwise per epilogue warp 32 rows x 64 bytes.
+  __shared__ alignas(1024) uint8_t epi_stage[Cfg::STAGING_BYTES];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -131,7 +145,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
       mbar_init(smem_u32(&bar_sf_full[s]), 1);
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
-    mbar_init(smem_u32(&bar_acc_empty), 256);
+    // One arrival per epilogue warp of both CTAs (16-bit output: eight warps per CTA).
+    mbar_init(smem_u32(&bar_acc_empty), Cfg::TMA_STORE ? 16 : 8);
     abort_flag = 0;
     mbar_fence_init();
   }
@@ -173,6 +188,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         prefetch_tensormap(&p.map_a);
         prefetch_tensormap(&p.map_b);
         if constexpr (Cfg::DUAL) prefetch_tensormap(&p.map_b2);
+        if constexpr (Cfg::TMA_STORE) prefetch_tensormap(&p.map_d);
       }
       const uint32_t leader_full0 = cluster_map_shared(smem_u32(&bar_full[0]), 0);
       const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
@@ -317,7 +333,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         acc_phase ^= 1u;
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 6 && warp < 10) {
     // ------------------------------------------------------------------ scale movers
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t sf_full0 = smem_u32(&bar_sf_full[0]);
@@ -374,8 +390,96 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         }
       }
     }
-  } else if (warp >= 2) {
-    // ------------------------------------------------------------------ epilogue
+  } else if (Cfg::TMA_STORE) {
+    // ------------------------------------------------------------------ epilogue, 16-bit D
+    if constexpr (Cfg::TMA_STORE) {
+      const int group = warp >= 10 ? 1 : 0;
+      const int quarter = warp & 3;
+      const int row = quarter * 32 + lane;
+      const bool issuer = (warp == 2 || warp == 10) && lane == 0;  // one thread per group
+      const uint32_t barrier_id = 1u + static_cast<uint32_t>(group);
+      const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
+      const uint32_t leader_acc_empty = cluster_map_shared(smem_u32(&bar_acc_empty), 0);
+      // The group's accumulator columns: half of the 256 (dual: the group's 64 columns of h1
+      // at 64 g and of h2 at 128 + 64 g).
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(group) * (Cfg::DUAL ? 64u : 128u);
+      const uint32_t box = smem_u32(epi_stage) + static_cast<uint32_t>(group) * 16384u;
+      // Row `row` of the box: eight 16-byte pieces, piece j at position j ^ (row % 8).
+      const uint32_t box_row = box + static_cast<uint32_t>(row) * 128u;
+      const uint32_t swizzle = static_cast<uint32_t>(row) & 7u;
+      constexpr int BOXES = Cfg::DUAL ? 1 : 2;  // 64-column boxes per group and tile
+      uint32_t acc_phase = 0;
+      for (long long t = first_tile; t < tiles; t += pairs) {
+        int batch, m_tile, n_tile;
+        decode(t, batch, m_tile, n_tile);
+        if (!mbar_wait(smem_u32(&bar_acc_full), acc_phase, abort_ptr)) {
+          report_failure(p, abort_ptr, kStatusEpilogueTimeout);
+          break;
+        }
+        tc_fence_after_sync();
+        uint32_t packed[BOXES][32];
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b) {
+          uint32_t r1[32], r2[32];
+          if constexpr (Cfg::DUAL) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              tmem_load_32(taddr + 32 * half, r1);
+              tmem_load_32(taddr + 128 + 32 * half, r2);
+              tmem_load_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                packed[b][16 * half + i] = pack_pair<OutT>(
+                    silu_f32(__uint_as_float(r1[2 * i]) * alpha) *
+                        (__uint_as_float(r2[2 * i]) * alpha),
+                    silu_f32(__uint_as_float(r1[2 * i + 1]) * alpha) *
+                        (__uint_as_float(r2[2 * i + 1]) * alpha));
+              }
+            }
+          } else {
+            tmem_load_32(taddr + 64 * b, r1);
+            tmem_load_32(taddr + 64 * b + 32, r2);
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              packed[b][i] = pack_pair<OutT>(__uint_as_float(r1[2 * i]) * alpha,
+                                             __uint_as_float(r1[2 * i + 1]) * alpha);
+              packed[b][16 + i] = pack_pair<OutT>(__uint_as_float(r2[2 * i]) * alpha,
+                                                  __uint_as_float(r2[2 * i + 1]) * alpha);
+            }
+          }
+        }
+        // Everything this warp needs has left tensor memory: hand the accumulator back.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_peer(leader_acc_empty);
+        const int row0 = m_tile * 256 + static_cast<int>(rank) * 128;
+        const int col0 = n_tile * Cfg::OUT_N + group * (Cfg::DUAL ? 64 : 128);
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b) {
+          // The box is free once the previous store has read it.
+          if (issuer) bulk_wait_group_read_all();
+          named_barrier_sync(barrier_id, 128);
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) {
+            st_shared_v4(box_row + ((j ^ swizzle) << 4), packed[b][4 * j], packed[b][4 * j + 1],
+                         packed[b][4 * j + 2], packed[b][4 * j + 3]);
+          }
+          fence_proxy_async_shared();
+          named_barrier_sync(barrier_id, 128);
+          if (issuer && row0 < pd.m && col0 + 64 * b < pd.n) {
+            tma_store_3d(&p.map_d, box, col0 + 64 * b, row0, batch);
+            bulk_commit_group();
+          }
+        }
+        acc_phase ^= 1u;
+      }
+      // The staging box must outlive the reads of the last stores.
+      if (issuer) bulk_wait_group_read_all();
+    }
+  } else if (warp >= 2 && warp < 6) {
+    // ------------------------------------------------------------------ epilogue, FP32 D
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
@@ -396,86 +500,22 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
                       (static_cast<long long>(batch) * pd.m + grow) * pd.n;
       OutT* out_block = out_row - static_cast<long long>(lane) * pd.n;
       const int rows_valid = pd.m - (grow - lane);
-      const uint32_t stage_smem = smem_u32(&epi_stage[quarter][0]);
-      if constexpr (Cfg::DUAL) {
-        // h1 in columns [0, 128), h2 in [128, 256): gate, pack, hand the accumulator back,
-        // then store.
-        uint32_t packed[4][16];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r1[32], r2[32];
-          tmem_load_32(taddr + c * 32, r1);
-          tmem_load_32(taddr + 128 + c * 32, r2);
-          tmem_load_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            packed[c][i] = pack_pair<OutT>(
-                silu_f32(__uint_as_float(r1[2 * i]) * alpha) * (__uint_as_float(r2[2 * i]) * alpha),
-                silu_f32(__uint_as_float(r1[2 * i + 1]) * alpha) *
-                    (__uint_as_float(r2[2 * i + 1]) * alpha));
-          }
-        }
-        tc_fence_before_sync();
-        mbar_arrive_peer(leader_acc_empty);
-        if ((pd.n & 7) == 0) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            store_block_coalesced<OutT>(stage_smem, packed[c], out_block, n0 + c * 32, pd.n,
-                                        rows_valid, lane);
-          }
-        } else if (grow < pd.m) {
-          // Rows of D only 8-byte aligned (n % 8 == 4): 8-byte pieces.
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              const int col = n0 + c * 32 + 4 * g;
-              if (col < pd.n) {
-                *reinterpret_cast<uint2*>(out_row + col) =
-                    make_uint2(packed[c][2 * g], packed[c][2 * g + 1]);
-              }
-            }
-          }
-        }
-      } else if constexpr (sizeof(OutT) == 2) {
-        // Read the whole row out of tensor memory first (packed to FP16: 128 registers),
-        // hand the accumulator back to the MMA issuer, then store: the next tile's MMAs
-        // start while this tile is still being written.
-        uint32_t packed[8][16];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t r1[32];
-          tmem_load_32(taddr + c * 32, r1);
-          tmem_load_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            packed[c][i] = pack_pair<OutT>(__uint_as_float(r1[2 * i]) * alpha,
-                                           __uint_as_float(r1[2 * i + 1]) * alpha);
-          }
-        }
-        tc_fence_before_sync();
-        mbar_arrive_peer(leader_acc_empty);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          store_block_coalesced<OutT>(stage_smem, packed[c], out_block, n0 + c * 32, pd.n,
-                                      rows_valid, lane);
-        }
-      } else {
+      const uint32_t stage_smem = smem_u32(epi_stage) + static_cast<uint32_t>(quarter) * 2048u;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          uint32_t r1[32];
-          float v[32];
-          tmem_load_32(taddr + c * 32, r1);
-          tmem_load_wait();
+      for (int c = 0; c < 8; ++c) {
+        uint32_t r1[32];
+        float v[32];
+        tmem_load_32(taddr + c * 32, r1);
+        tmem_load_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * alpha;
-          if (c == 7) {
-            tc_fence_before_sync();
-            mbar_arrive_peer(leader_acc_empty);
-          }
-          store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
-                                 rows_valid, lane, v);
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * alpha;
+        if (c == 7) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_peer(leader_acc_empty);
         }
+        store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
+                               rows_valid, lane, v);
       }
       acc_phase ^= 1u;
     }

@@ -114,6 +114,16 @@ __device__ __forceinline__ void prefetch_tensormap(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
+// Before the first use of a tensor map that lives in global memory and was written there by
+// a copy or by other code (not passed as a kernel parameter): the tensor-map proxy may hold
+// an older descriptor that was stored at the same address, and this acquire makes it read
+// the current 128 bytes. Executed by the thread that issues the copies.
+__device__ __forceinline__ void tensormap_acquire(const void* map) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(
+                   reinterpret_cast<uint64_t>(map))
+               : "memory");
+}
+
 // Rank-3 tiled tensor copy. The innermost coordinate times the element size must
 // be a multiple of 16 bytes (callers pass multiples of 128 bytes of uint8).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar,
@@ -146,6 +156,29 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t peer_dst, uint32_t sr
           "r"(peer_dst),
       "r"(src), "r"(bytes), "r"(peer_bar)
       : "memory");
+}
+
+// Rank-3 tiled tensor store, shared -> global, as part of the thread's current bulk group.
+// The innermost coordinate times the element size must be a multiple of 16 bytes and no
+// coordinate may be negative; the part of the box outside the tensor is not written. The
+// source must have been written before a fence.proxy.async by the writing threads.
+__device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int c0, int c1,
+                                             int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(map)),
+      "r"(src), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// Blocks until every bulk group this thread committed has finished *reading* its
+// shared-memory source (the global writes may still be in flight).
+__device__ __forceinline__ void bulk_wait_group_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 // Makes this thread's earlier generic-proxy writes to shared memory visible to the async

@@ -551,12 +551,15 @@ def test_nvfp4_output_plan_rejects_what_it_cannot_do():
         plan.launch_dense_fp4(256, 256, 256, 256, 256, 256, 256, 256, 0)
 
 
-@pytest.mark.parametrize("m,n,k,l", [(300, 264, 2080, 1), (512, 1024, 1024, 1), (130, 260, 512, 2)])
+@pytest.mark.parametrize("m,n,k,l", [(300, 264, 2080, 1), (512, 1024, 1024, 1), (130, 328, 512, 2)])
 def test_dual_gemm_on_cta_pairs(m, n, k, l):  # noqa: E741
     """The fused dual GEMM on the 2-CTA kernel: the leader loads B1's tile, its peer B2's, one
-    256-column MMA per pair; partial tiles in M and N, a K tail, batches, and rows of D that
-    are only 8-byte aligned (n = 260)."""
+    256-column MMA per pair; partial tiles in M and N (also a last 64-column box that is
+    partly and one that is wholly outside D), a K tail, batches. The kernel stores D through
+    a tensor map, so rows of D that are only 8-byte aligned (n = 260) are refused for it."""
     from harness import CaseSpec
+    with pytest.raises(ValueError):
+        native.Plan.dual(0, 130, 260, 512, 2, pair=1)
     workload = get_workload("nvfp4_dual_gemm")(None, device="cuda")
     dev = torch.device("cuda:0")
     stream = torch.cuda.current_stream().cuda_stream
