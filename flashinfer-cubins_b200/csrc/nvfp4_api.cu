@@ -103,16 +103,11 @@ int encode_operand_map(CUtensorMap* map, const void* ptr, int rows, int k, int b
   EncodeTiledFn encode = nullptr;
   if (int rc = get_encoder(&encode)) return rc;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(k) / 2;
-  // Loads through the descriptor of a tensor smaller than 128 KiB are markedly slower on
-  // current drivers. The batch extent is only a bound for coordinates, and the kernels never
-  // pass a batch index beyond the real count (Segment::batch < ProblemDesc::batches; grouped
-  // problems pass 0), so a small tensor is described with enough never-addressed batches to
-  // reach 128 KiB.
-  cuuint64_t declared_batches = static_cast<cuuint64_t>(batches);
-  const cuuint64_t batch_bytes = row_bytes * static_cast<cuuint64_t>(rows);
-  if (batch_bytes * declared_batches < 131072) {
-    declared_batches = (131072 + batch_bytes - 1) / batch_bytes;
-  }
+  // The map describes exactly the caller's tensor. (Loads through the map of a tensor below
+  // 128 KiB are slower on current drivers, and declaring never-addressed extra batches up to
+  // that size makes them fast again - but the copy engine then touches memory inside the
+  // declared extent beyond the real tensor, which faults when that memory is not mapped.)
+  const cuuint64_t declared_batches = static_cast<cuuint64_t>(batches);
   const cuuint64_t dims[3] = {row_bytes, static_cast<cuuint64_t>(rows), declared_batches};
   const cuuint64_t strides[2] = {row_bytes, row_bytes * static_cast<cuuint64_t>(rows)};
   const cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), 1u};
@@ -1172,11 +1167,18 @@ int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const vo
     if (int rc = encode_operand_map(&tmp, b[g], pd.n, pd.k, 1, plan->tile_n)) return rc;
     std::memcpy(&maps[2 * g + 1], &tmp, sizeof(tmp));
   }
-  // The source is pageable host memory: the runtime stages it before the call returns, so
-  // `staging` may go out of scope.
-  CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + plan->off_table, staging.data(),
-                           table_bytes, cudaMemcpyHostToDevice,
-                           static_cast<cudaStream_t>(stream)));
+  // Into the workspace as kernel parameters, 3.5 KB per launch: parameters are copied when a
+  // launch is enqueued, so `staging` may go out of scope when this function returns. (An
+  // asynchronous copy from pageable memory may still be reading its source then.)
+  uint8_t* dst = static_cast<uint8_t*>(workspace) + plan->off_table;
+  for (size_t done = 0; done < table_bytes; done += ParamBlob::kBytes) {
+    ParamBlob blob;
+    const size_t bytes = std::min<size_t>(ParamBlob::kBytes, table_bytes - done);
+    std::memcpy(blob.data, staging.data() + done, bytes);
+    write_blob_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(dst + done, blob,
+                                                                        static_cast<int>(bytes));
+    CUDA_TRY(cudaGetLastError());
+  }
   {
     std::lock_guard<std::mutex> lock(plan->mutex);
     plan->group_bound = true;

@@ -14,6 +14,23 @@
 
 namespace nvfp4 {
 
+// A few KB of host data delivered to device memory *as a kernel parameter*: the runtime
+// copies parameters when the launch is enqueued, so the host buffer they came from may be
+// freed or reused as soon as the launch call returns, on every system (an asynchronous copy
+// from pageable host memory has no such guarantee where the GPU can read pageable memory
+// directly), and the launch can be captured in a graph. `bytes` is a multiple of 16.
+struct alignas(16) ParamBlob {
+  static constexpr int kBytes = 3584;
+  uint8_t data[kBytes];
+};
+
+__global__ void write_blob_kernel(uint8_t* __restrict__ dst, const __grid_constant__ ParamBlob blob,
+                                  int bytes) {
+  const uint4* src = reinterpret_cast<const uint4*>(blob.data);
+  uint4* out = reinterpret_cast<uint4*>(dst);
+  for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) out[i] = src[i];
+}
+
 // scales: [batches][rows][cols] bytes. packed: [batches][rb][cb][32][4][4] bytes with
 // rb = ceil(rows/128), cb = ceil(cols/4); scale (r, c) goes to
 // [r/128][c/4][r%32][(r/32)%4][c%4]; padding is zero. One thread writes one 16-byte

@@ -22,9 +22,6 @@
  *     host threads and on several streams at the same time, each with its own workspace;
  *     the only state a launch shares is a mutex-guarded cache of encoded tensor maps
  *     keyed by the operand addresses. nvfp4_plan_destroy must not race with a launch.
- *   - Tensor maps of operands smaller than 128 KiB declare a batch extent that covers
- *     addresses past the end of the operand; those batches are never addressed, so
- *     nothing beyond the operand is read.
  *   - Operand layout (harness/workloads/quantization.py:1-37): packed E2M1 bytes,
  *     low nibble = even K index, K contiguous, storage [batch][rows][k/2]; UE4M3
  *     scales, one per 16 K elements, in the blocked layout
@@ -192,8 +189,10 @@ int nvfp4_dual_gemm_launch(const nvfp4_plan* plan, const void* a, const void* b1
                            const float* alpha, void* d, void* workspace, void* stream);
 
 /* Records the groups' device pointers (host arrays of `groups` pointers each),
- * encodes the per-group tensor maps and copies the group table into the workspace
- * (one stream-ordered host-to-device copy). Replaces NVFP4GroupGEMM.launch_config
+ * encodes the per-group tensor maps and writes the group table into the workspace,
+ * stream-ordered, by small kernel launches that carry the table as parameters (so the
+ * call neither synchronises nor depends on host memory after it returns, and can be
+ * captured in a graph). Replaces NVFP4GroupGEMM.launch_config
  * (harness/workloads/nvfp4_group_gemm.py:514-591). */
 int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const void* const* b,
                           const void* const* sfa, const void* const* sfb, void* const* d,

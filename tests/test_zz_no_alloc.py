@@ -65,6 +65,7 @@ def test_static_scratch_launch_matches_workspace_launch_twice():
             torch.testing.assert_close(got, expected, rtol=1e-3, atol=1e-3)
             assert torch.equal(got, expected), f"call {call}: differs from the workspace launch"
             # The array's status word: no wait was abandoned, and reading it allocates nothing.
+            blocks = torch.cuda.memory_stats()["allocation.all.allocated"]
             assert native.static_status(0, stream) == 0
             assert torch.cuda.memory_stats()["allocation.all.allocated"] == blocks
     plan.destroy()
