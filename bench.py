@@ -1,31 +1,49 @@
 #!/usr/bin/env python
-"""Benchmark of the NVFP4 block-scaled GEMM hot path on B200.
+"""Benchmark of the NVFP4 block-scaled GEMM family on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
-                    [--workload decode|square|dual|grouped]
+                    [--workload square|decode|dual|grouped|latency]
+                    [--scaling strong|weak] [--no-configs] [--no-cpu-baseline]
 
 One JSON line on stdout (rank 0). A *step* is one GEMM call on one set of synthetic
-operands. The default workload is the skinny, HBM-bound decode GEMM
-(M=128, N=7168, K=16384, FP16 out): A and B are N(0,1) drawn from a seeded CPU
-generator, quantised per 16-element K block to E2M1 with an E4M3 scale amax/6, scales
-in the blocked 128x4 layout, alpha = 1. Steps rotate through several operand sets that
-together exceed the 126 MB L2, so B is read from HBM every step.
+operands. The headline workload is the largest single-GPU configuration, the
+compute-bound M = N = K = 8192 GEMM with FP16 output; the same line carries, under
+``configs``, the other configurations (latency 128x256x512, decode 128x7168x16384, fused
+dual GEMM 256x4096x7168, ragged grouped GEMM with eight groups) measured the same way.
+Operands are N(0,1) drawn from seeded CPU generators, quantised per 16-element K block to
+E2M1 with an E4M3 scale amax/6, scales in the blocked 128x4 layout, alpha = 1; several
+operand sets rotate so that together they exceed the 126 MB L2.
 
-* ``value``: whole-job TFLOP/s with operands resident in HBM, timed on the device with
-  CUDA events around K prepared launches (replayed from a CUDA graph when capture
-  works, so that Python launch overhead is not what is measured), max over ranks.
-* ``e2e``: the same metric through the operator API with host buffers: every step
-  copies the operands from pinned host memory, runs the workload and reads D back.
-* ``roofline``: algorithmic bytes of one call / average call duration against the
-  measured HBM copy bandwidth of this pool.
-* ``cpu_baseline``: the numpy oracle (a port of the reference's torch oracle) timed on
-  this host's cores on the same operands; a reported baseline, not the target.
-* ``--impl reference``: the reference arm — that same CPU path, alone, on bounded
-  samples of the workload.
+* ``validated``: before anything is timed every operand set is run once through the
+  prepared launch and compared with the workload's torch reference on the same device
+  (dequantise, FP32 matmul, one rounding; rtol = atol = 1e-3); after the timed region one
+  output is compared again. A mismatch raises.
+* ``value``: whole-job TFLOP/s with operands resident in HBM: K prepared launches replayed
+  from a CUDA graph between two CUDA events (back-to-back launches; with programmatic
+  dependent launch a kernel's prologue overlaps its predecessor's tail), max over ranks.
+  ``isolated_us`` is the median of single launches bracketed by events one at a time, the
+  way the reference's own benchmark times a kernel.
+* ``e2e``: the same metric through the operator API (``Workload.run``) with host buffers:
+  every step copies the operands from pinned host memory, runs the workload and reads D
+  back.
+* ``roofline``: tensor-bound workloads against the nominal dense FP4 peak and the rate at
+  which this GPU issues the same MMAs with nothing else running; HBM-bound workloads:
+  algorithmic bytes of one call / call duration against the measured HBM copy bandwidth.
+* ``cpu_baseline``: the numpy oracle (a port of the reference's torch oracle, pinned to the
+  reference's outputs) timed on this host's cores on a bounded sample of the same problem;
+  ``torch_path`` inside it is the package's torch restatement of the same arithmetic on all
+  cores. A reported baseline, not the target.
+* ``competitors``: library NVFP4 GEMMs on the same GPU, same timing method (cuBLASLt
+  through ``torch._scaled_mm``, cuDNN through FlashInfer ``mm_fp4``), for context; the
+  package never imports them.
+* ``--impl reference``: the reference arm, that CPU path alone on bounded samples.
 
-With N > 1 (launched by torch.distributed.run) every rank holds its own N-shard of a
-GEMM whose N is N_gpus x 7168 (weak scaling, no collective on the data path);
-``--scaling strong`` splits the workload's own N over the ranks instead.
+With N > 1 (launched by torch.distributed.run) the default is strong scaling: the
+workload's own N is cut into 128-row shards of B, one per rank, with no collective on the
+data path (the grouped GEMM cuts every group's N the same way; ``grouped_lpt`` places
+whole groups by FLOPs); every rank validates its own shard; ``all_gather_us`` times the one
+optional exchange (all ranks' columns of D gathered over NCCL), outside ``value``.
+``--scaling weak`` gives every rank the whole shape instead.
 """
 
 from __future__ import annotations
@@ -33,6 +51,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import sys
 import threading
@@ -47,17 +66,25 @@ sys.path.insert(0, str(REPO / "flashinfer-cubins_b200"))
 sys.path.insert(0, str(REPO))
 
 WORKLOADS = {
-    # name: (kind, shape description)
+    # name: (kind, shape)
+    "latency": ("dense", dict(m=128, n=256, k=512)),
     "decode": ("dense", dict(m=128, n=7168, k=16384)),
     "square": ("dense", dict(m=8192, n=8192, k=8192)),
     "dual": ("dual", dict(m=256, n=4096, k=7168)),
     "grouped": ("grouped", dict(ms=(40, 96, 128, 256, 384, 512, 768, 1024), n=4096, k=7168)),
 }
+BOUND = {"latency": "latency", "decode": "hbm", "square": "tensor", "dual": "hbm",
+         "grouped": "hbm"}
+# ncu summary that holds the DRAM traffic of one launch of the workload's kernel.
+TRAFFIC_SUMMARY = {
+    "decode": "nvfp4_gemm_decode_m128_n7168_k16384.md",
+    "square": "nvfp4_gemm_square_m8192_n8192_k8192.md",
+    "dual": "nvfp4_dual_gemm_m256_n4096_k7168.md",
+    "grouped": "nvfp4_group_gemm_8groups_n4096_k7168.md",
+}
 L2_BYTES = 126 << 20
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode-shape launch, from the ncu
-# capture summarised in profiles/nvfp4_gemm_decode_m128_n7168_k16384.md.
-DECODE_DRAM_TRAFFIC_BYTES = 68_483_328
+NOMINAL_FP4_TFLOPS = 9000.0
 
 
 def algorithmic_work(kind: str, shape: dict) -> tuple[float, float]:
@@ -86,6 +113,16 @@ def measured_hbm_peak() -> tuple[float, str]:
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def recorded_traffic(name: str):
+    """``dram_bytes_per_launch: <int>`` from the workload's ncu summary, or None."""
+    file = TRAFFIC_SUMMARY.get(name)
+    path = REPO / "profiles" / file if file else None
+    if path is None or not path.is_file():
+        return None
+    found = re.search(r"dram_bytes_per_launch:\s*([0-9][0-9_,]*)", path.read_text())
+    return int(re.sub(r"[_,]", "", found.group(1))) if found else None
+
+
 # -- synthetic operands ---------------------------------------------------------------------
 
 
@@ -98,11 +135,13 @@ def normal_fp4(rows: int, k: int, seed: int, device) -> tuple[torch.Tensor, torc
     return packed[..., None], scales[..., None]
 
 
-def make_operand_set(kind: str, shape: dict, index: int, rank: int, device) -> tuple:
+def make_operand_set(kind: str, shape: dict, index: int, device) -> tuple:
+    """One full (unsharded) operand set: seeds A = 1, B = 2 (dual: B1 = 2, B2 = 3), group g
+    A = 10 + g and B = 20 + g, plus 1000 per further set."""
     from harness.workloads.nvfp4_gemm import to_task_scales
     from harness.workloads.nvfp4_group_gemm import to_blocked
 
-    base = 1000 * index + 100 * rank
+    base = 1000 * index
     if kind == "grouped":
         tensors = []
         for g, m in enumerate(shape["ms"]):
@@ -118,6 +157,45 @@ def make_operand_set(kind: str, shape: dict, index: int, rank: int, device) -> t
         return (a, b, to_task_scales(sa), to_task_scales(sb), alpha)
     b2, s2 = normal_fp4(shape["n"], shape["k"], base + 3, device)
     return (a, b, b2, to_task_scales(sa), to_task_scales(sb), to_task_scales(s2), alpha)
+
+
+def shard_operands(kind: str, inputs: tuple, rank: int, world: int, placement: str):
+    """This rank's operands of ``inputs`` and a description of what it owns; ``None`` if
+    the rank owns nothing."""
+    from harness import sharding
+
+    if world == 1:
+        return inputs, "whole problem"
+    if kind == "dense":
+        local, span = sharding.shard_dense_inputs(inputs, rank, world)
+        return local, f"columns {span[0]}:{span[1]}"
+    if kind == "dual":
+        local, span = sharding.shard_dual_inputs(inputs, rank, world)
+        return local, f"columns {span[0]}:{span[1]}"
+    if placement == "lpt":
+        groups = [tuple(inputs[i:i + 4]) for i in range(0, len(inputs), 4)]
+        problems = [(a.shape[0], b.shape[0], 2 * a.shape[1]) for a, b, _, _ in groups]
+        owned = sharding.balance_groups(problems, world)[rank]
+        if not owned:
+            return None, "no group"
+        return tuple(t for g in owned for t in groups[g]), f"groups {owned}"
+    local, spans = sharding.shard_group_inputs(inputs, rank, world)
+    return (local or None), f"{len(spans)} (group, column range) units"
+
+
+def work_of(kind: str, inputs) -> tuple[float, float]:
+    """(FLOPs, algorithmic bytes) of the launch on ``inputs`` (a rank's shard)."""
+    if inputs is None:
+        return 0.0, 0.0
+    if kind == "grouped":
+        flops = byts = 0.0
+        for i in range(0, len(inputs), 4):
+            a, b = inputs[i], inputs[i + 1]
+            f, by = algorithmic_work("dense", dict(m=a.shape[0], n=b.shape[0], k=2 * a.shape[1]))
+            flops, byts = flops + f, byts + by
+        return flops, byts
+    a, b = inputs[0], inputs[1]
+    return algorithmic_work(kind, dict(m=a.shape[0], n=b.shape[0], k=2 * a.shape[1]))
 
 
 def workload_class(kind: str):
@@ -139,8 +217,8 @@ class ClockSampler:
         "hw_power_brake": 0x80, "sw_power_cap": 0x4,
     }
 
-    def __init__(self, index: int, interval: float = 0.02):
-        self.samples: list[tuple[int, int, int]] = []
+    def __init__(self, index: int, interval: float = 0.002):
+        self.samples: list[tuple[float, int, int, int]] = []
         self.max_mhz = None
         self._stop = threading.Event()
         self._thread = None
@@ -162,7 +240,7 @@ class ClockSampler:
                 mhz = nvml.nvmlDeviceGetClockInfo(self._handle, nvml.NVML_CLOCK_SM)
                 util = nvml.nvmlDeviceGetUtilizationRates(self._handle).gpu
                 reasons = nvml.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
-                self.samples.append((mhz, util, reasons))
+                self.samples.append((time.perf_counter(), mhz, util, reasons))
             except Exception:
                 pass
             self._stop.wait(self._interval)
@@ -178,38 +256,30 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join(timeout=2)
 
-    def summary(self) -> dict:
-        if not self.samples:
+    def summary(self, since: float = 0.0, until: float = float("inf")) -> dict:
+        samples = [s for s in self.samples if since <= s[0] <= until]
+        if not samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
         # "Under load": samples taken while NVML reported the GPU at least half busy (all
         # samples if none was: the timed regions are shorter than NVML's averaging window).
-        loaded = [s[0] for s in self.samples if s[1] >= 50] or [s[0] for s in self.samples]
+        loaded = [s[1] for s in samples if s[2] >= 50] or [s[1] for s in samples]
         seen = 0
-        for _, _, reasons in self.samples:
+        for _, _, _, reasons in samples:
             seen |= reasons
         names = [name for name, bit in self.REASONS.items() if seen & bit]
         return {"sm_mhz": statistics.median(loaded), "sm_min_mhz": min(loaded),
-                "sm_max_mhz": self.max_mhz, "reasons": names, "samples": len(self.samples),
+                "sm_max_mhz": self.max_mhz, "reasons": names, "samples": len(samples),
                 "samples_under_load": len(loaded)}
 
 
 # -- CPU baseline (the oracle port) ---------------------------------------------------------
 
 
-def oracle_dense_call(a, b, sa, sb, rows: slice | None = None):
-    """One oracle GEMM on numpy storage-order operands, optionally on a row slice of B."""
-    from oracle import nvfp4_oracle as o
-
-    if rows is not None:
-        b, sb = b[:, rows], sb[:, rows]
-    return o.gemm(a, b, sa, sb, 1.0, np.float16)
-
-
-def host_dense_operands(shape: dict, seed_base: int = 0):
-    """Storage-order numpy operands (packed bytes, logical scale bytes) of the dense
-    workload, made on the CPU with the harness quantiser."""
-    a, sa = normal_fp4(shape["m"], shape["k"], seed_base + 1, "cpu")
-    b, sb = normal_fp4(shape["n"], shape["k"], seed_base + 2, "cpu")
+def host_dense_operands(m: int, n: int, k: int, seed_a: int = 1, seed_b: int = 2):
+    """Storage-order numpy operands (packed bytes, logical scale bytes) of one GEMM, made
+    on the CPU with the harness quantiser."""
+    a, sa = normal_fp4(m, k, seed_a, "cpu")
+    b, sb = normal_fp4(n, k, seed_b, "cpu")
 
     def store(t):
         t = t.permute(2, 0, 1).contiguous()
@@ -218,61 +288,111 @@ def host_dense_operands(shape: dict, seed_base: int = 0):
     return store(a), store(b), store(sa), store(sb)
 
 
-def cpu_baseline(kind: str, shape: dict, budget_s: float = 15.0) -> dict:
-    """TFLOP/s of the oracle on this host for (a bounded sample of) the workload."""
-    if kind != "dense":
-        shape = dict(m=128, n=7168, k=16384)
-    a, b, sa, sb = host_dense_operands(shape)
-    m, n, k = shape["m"], shape["n"], shape["k"]
-    probe_rows = min(n, 256)
-    t0 = time.perf_counter()
-    oracle_dense_call(a, b, sa, sb, slice(0, probe_rows))
-    per_row = (time.perf_counter() - t0) / probe_rows
-    rows = int(min(n, max(probe_rows, budget_s / 3 / per_row)))
+def cpu_problem(kind: str, shape: dict) -> tuple[int, int, int, int, str]:
+    """(m, n, k, gemms per row sample, description): the GEMM whose rows of B the CPU arm
+    samples. The dual GEMM is two GEMMs over the same A (its gate is negligible); the
+    grouped GEMM is represented by its largest group (same N and K for every group)."""
+    if kind == "grouped":
+        m = max(shape["ms"])
+        return m, shape["n"], shape["k"], 1, (
+            f"largest group m={m} of the grouped GEMM n={shape['n']} k={shape['k']}")
+    gemms = 2 if kind == "dual" else 1
+    what = "both GEMMs of the dual GEMM" if kind == "dual" else "the GEMM"
+    return shape["m"], shape["n"], shape["k"], gemms, (
+        f"{what} m={shape['m']} n={shape['n']} k={shape['k']}")
+
+
+def oracle_rows(operands, rows: slice, gemms: int):
+    from oracle import nvfp4_oracle as o
+
+    a, b, sa, sb = operands
+    for _ in range(gemms):
+        o.gemm(a, b[:, rows], sa, sb[:, rows], 1.0, np.float16)
+
+
+def rows_within(operands, n: int, gemms: int, seconds: float) -> int:
+    """How many rows of B one oracle call can take within ``seconds``: the call costs a fixed
+    part (dequantising A) plus a part per row of B, estimated from two probes. All of B
+    when the whole problem fits."""
+    small, large = min(n, 32), min(n, 256)
+    timings = []
+    for rows in (small, large):
+        t0 = time.perf_counter()
+        oracle_rows(operands, slice(0, rows), gemms)
+        timings.append(time.perf_counter() - t0)
+    if large == small:
+        return n
+    per_row = max((timings[1] - timings[0]) / (large - small), 1e-9)
+    fixed = max(timings[0] - per_row * small, 0.0)
+    return int(min(n, max(large, (seconds - fixed) / per_row)))
+
+
+def cpu_baseline(kind: str, shape: dict, budget_s: float = 18.0) -> dict:
+    """TFLOP/s of the CPU path on this host for a bounded sample of the workload (the whole
+    problem when it fits the budget)."""
+    m, n, k, gemms, what = cpu_problem(kind, shape)
+    operands = host_dense_operands(m, n, k)
+    rows = rows_within(operands, n, gemms, budget_s / 3)
     times = []
     for _ in range(3):
         t0 = time.perf_counter()
-        oracle_dense_call(a, b, sa, sb, slice(0, rows))
+        oracle_rows(operands, slice(0, rows), gemms)
         times.append(time.perf_counter() - t0)
     best = statistics.median(times)
-    return {
-        "value": 2.0 * m * rows * k / best / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
-        "kind": "port",
-        "sample": f"numpy oracle (dequantise, FP32 matmul, FP16 cast) on {rows} of {n} rows of B "
-                  f"of the m={m} n={n} k={k} GEMM, median of 3, {best:.3f} s each",
+    result = {
+        "value": 2.0 * m * rows * k * gemms / best / 1e12, "unit": "TFLOP/s",
+        "cores": os.cpu_count(), "kind": "port",
+        "sample": f"numpy oracle (dequantise, FP32 matmul, FP16 cast) on {rows} of {n} rows of "
+                  f"B of {what}, median of 3, {best:.3f} s each",
     }
+    # The package's torch restatement of the reference's oracle (the workloads'
+    # get_reference) on all cores, on the same rows.
+    try:
+        from harness.workloads.quantization import fp4_matmul
+
+        threads = torch.get_num_threads()
+        torch.set_num_threads(os.cpu_count() or threads)
+        a, sa = normal_fp4(m, k, 1, "cpu")
+        b, sb = normal_fp4(rows, k, 2, "cpu")
+        fp4_matmul(a, b, sa, sb, out_dtype=torch.float16)
+        t0 = time.perf_counter()
+        for _ in range(gemms):
+            fp4_matmul(a, b, sa, sb, out_dtype=torch.float16)
+        elapsed = time.perf_counter() - t0
+        torch.set_num_threads(threads)
+        result["torch_path"] = {"value": 2.0 * m * rows * k * gemms / elapsed / 1e12,
+                                "unit": "TFLOP/s", "threads": os.cpu_count(),
+                                "seconds": elapsed}
+    except Exception as error:  # the baseline above stands on its own
+        result["torch_path"] = {"unavailable": repr(error)[:200]}
+    return result
 
 
-def reference_arm(args, kind: str, shape: dict, rank: int) -> None:
+def reference_arm(args, name: str, kind: str, shape: dict, rank: int) -> None:
     """``--impl reference``: the CPU path alone. Only rank 0 works."""
     if rank != 0:
         return
-    if kind != "dense":
-        kind, shape = "dense", dict(m=128, n=7168, k=16384)
-    a, b, sa, sb = host_dense_operands(shape)
-    m, n, k = shape["m"], shape["n"], shape["k"]
+    m, n, k, gemms, what = cpu_problem(kind, shape)
+    operands = host_dense_operands(m, n, k)
     total = args.steps + args.warmup
-    t0 = time.perf_counter()
-    oracle_dense_call(a, b, sa, sb, slice(0, 128))
-    per_row = (time.perf_counter() - t0) / 128
-    rows = int(min(n, max(16, 90.0 / total / per_row)))
+    rows = rows_within(operands, n, gemms, 120.0 / total)
     rows -= rows % 16 if rows > 16 else 0
     starts = [(i * rows) % max(n - rows, 1) for i in range(total)]
     for i in range(args.warmup):
-        oracle_dense_call(a, b, sa, sb, slice(starts[i], starts[i] + rows))
+        oracle_rows(operands, slice(starts[i], starts[i] + rows), gemms)
     t0 = time.perf_counter()
     for i in range(args.warmup, total):
-        oracle_dense_call(a, b, sa, sb, slice(starts[i], starts[i] + rows))
+        oracle_rows(operands, slice(starts[i], starts[i] + rows), gemms)
     elapsed = time.perf_counter() - t0
-    value = 2.0 * m * rows * k * args.steps / elapsed / 1e12
-    sample = (f"each step: numpy oracle on {rows} of {n} rows of B of the m={m} n={n} k={k} "
-              f"GEMM (host operands, no device)")
+    value = 2.0 * m * rows * k * gemms * args.steps / elapsed / 1e12
+    sample = (f"each step: numpy oracle on {rows} of {n} rows of B of {what} "
+              f"(host operands, no device)")
     line = {
         "impl": "reference", "metric": "nvfp4_gemm_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
-        "config": {"workload": f"nvfp4_gemm m={m} n={n} k={k} l=1 (CPU oracle, bounded sample)",
+        "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
+        "config": {"workload": f"{name}: nvfp4 {kind} GEMM {shape} l=1 (CPU oracle, bounded sample)",
                    "sample_rows": rows},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(),
                          "kind": "port", "sample": sample},
@@ -280,205 +400,524 @@ def reference_arm(args, kind: str, shape: dict, rank: int) -> None:
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=args.json_out, flush=True)
 
 
 # -- GPU arm --------------------------------------------------------------------------------
 
 
+class Distributed:
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    def barrier(self):
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, values: list[float], device) -> list[float]:
+        t = torch.tensor(values, dtype=torch.float64, device=device)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def sum_over_ranks(self, values: list[float], device) -> list[float]:
+        t = torch.tensor(values, dtype=torch.float64, device=device)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return [float(v) for v in t.tolist()]
+
+
+class Measured:
+    """One workload on this rank: operand sets, prepared launches, validation, timing."""
+
+    def __init__(self, name, kind, shape, dist_info, device, scaling, placement="slices",
+                 max_sets=8):
+        self.name, self.kind, self.shape = name, kind, shape
+        self.dist, self.device = dist_info, device
+        world = dist_info.world if scaling == "strong" else 1
+        _, byts = algorithmic_work(kind, shape)
+        self.sets = min(max_sets, max(3, int(2 * L2_BYTES // max(byts / world, 1)) + 1))
+        cls = workload_class(kind)
+        self.workload = cls.from_arch("sm_100a", device=device)
+        self.operands, self.owned = [], "nothing"
+        for index in range(self.sets):
+            full = make_operand_set(kind, shape, index, device)
+            local, self.owned = shard_operands(kind, full, dist_info.rank, world, placement)
+            self.operands.append(local)
+            del full
+        self.active = self.operands[0] is not None
+        self.flops, self.bytes = work_of(kind, self.operands[0])
+        self.launches, self.outputs, self.references = [], [], []
+        self.max_abs_err = 0.0
+        self.validated = False
+        self.info = {}
+        if self.active:
+            for inputs in self.operands:
+                launch, outputs = self.workload.prepare(inputs)
+                self.launches.append(launch)
+                self.outputs.append(outputs)
+            self.info = self.workload.plan_info(self.operands[0])
+
+    def close(self):
+        self.launches, self.outputs, self.references, self.operands = [], [], [], []
+        self.workload.close()
+        torch.cuda.empty_cache()
+
+    def validate(self, keep_reference: bool = True) -> None:
+        """Every operand set once through its prepared launch against the workload's torch
+        reference on this device (rtol = atol = 1e-3); raises on a mismatch."""
+        if not self.active:
+            self.validated = True
+            return
+        previous = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            for index, (inputs, launch) in enumerate(zip(self.operands, self.launches)):
+                outputs = launch()
+                torch.cuda.synchronize()
+                reference = self.workload.get_reference(inputs)
+                self.workload.validate(reference, outputs)
+                self._track_error(reference, outputs)
+                if keep_reference and index == 0:
+                    self.references = [r.clone() for r in reference]
+                del reference
+            self.workload.check_status()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = previous
+        self.validated = True
+
+    def _track_error(self, reference, outputs) -> None:
+        for r, o in zip(reference, outputs):
+            diff = (r.float() - o.float()).abs()
+            finite = torch.isfinite(diff)
+            if finite.any():
+                self.max_abs_err = max(self.max_abs_err, float(diff[finite].max().item()))
+
+    def revalidate_first(self) -> None:
+        """After the timed region: set 0's output (last written by the timed launches)
+        against the reference kept from ``validate``."""
+        if self.active and self.references:
+            torch.cuda.synchronize()
+            self.workload.validate(tuple(self.references), self.outputs[0])
+            self.workload.check_status()
+
+    def run(self, count: int, offset: int = 0) -> None:
+        if self.active:
+            for i in range(count):
+                self.launches[(offset + i) % self.sets]()
+
+    def time_replay(self, steps: int, warmup: int, use_graph: bool = True):
+        """(elapsed ms of ``steps`` back-to-back launches, how)."""
+        self.run(warmup)
+        self.dist.barrier()
+        graph = None
+        if use_graph and self.active:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self.run(steps)
+                graph.replay()  # warm the instantiated graph once
+            except Exception as error:  # capture unsupported: time direct launches
+                print(f"[bench] CUDA graph capture failed ({error}); timing direct launches",
+                      file=sys.stderr)
+                graph = None
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.dist.barrier()
+        start.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            self.run(steps)
+        stop.record()
+        self.dist.barrier()
+        self.graph = graph
+        return start.elapsed_time(stop), ("cuda_graph_replay" if graph is not None
+                                          else "direct_launches")
+
+    def time_isolated(self, samples: int = 20) -> float:
+        """Median microseconds of single launches, each bracketed by its own event pair
+        (the reference's method, harness/benchmark.py:19-43 there), rotating operand sets."""
+        if not self.active:
+            return 0.0
+        times = []
+        for i in range(samples + 5):
+            start, stop = (torch.cuda.Event(enable_timing=True),
+                           torch.cuda.Event(enable_timing=True))
+            torch.cuda.synchronize()
+            start.record()
+            self.launches[i % self.sets]()
+            stop.record()
+            torch.cuda.synchronize()
+            if i >= 5:
+                times.append(start.elapsed_time(stop) * 1e3)
+        return statistics.median(times)
+
+    def time_sustained(self, seconds: float, steps: int):
+        """Replays the captured graph back to back for about ``seconds``: microseconds per
+        call at whatever clock the power limit leaves, with the wall-clock window."""
+        if not self.active or getattr(self, "graph", None) is None:
+            return None
+        per_replay = max(self.last_ms, 1e-3) * 1e-3
+        replays = max(2, int(seconds / per_replay))
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        start.record()
+        for _ in range(replays):
+            self.graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        return start.elapsed_time(stop) * 1e3 / (replays * steps), t0, t1
+
+    def roofline(self, name: str, per_call_us: float, world_flops: float, world_bytes: float,
+                 issue_tflops):
+        bound = BOUND[name]
+        if bound == "tensor":
+            tf = world_flops / (per_call_us * 1e-6) / 1e12
+            peak = NOMINAL_FP4_TFLOPS * self.dist.world
+            line = {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
+                    "frac": tf / peak, "traffic": recorded_traffic(name),
+                    "peak_source": "nominal dense FP4 (9 PFLOP/s per GPU)",
+                    "algorithmic_flops_per_launch": world_flops / self.dist.world}
+            if issue_tflops:
+                line["measured_mma_issue_tflops"] = issue_tflops
+                line["frac_of_measured_mma_issue"] = tf / (issue_tflops * self.dist.world)
+            return line
+        peak, peak_kind = measured_hbm_peak()
+        achieved = world_bytes / (per_call_us * 1e-6) / 1e9
+        return {"bound": "hbm" if bound == "hbm" else "latency", "achieved": achieved,
+                "peak": peak * self.dist.world, "unit": "GB/s",
+                "frac": achieved / (peak * self.dist.world),
+                "traffic": recorded_traffic(name) if self.dist.world == 1 else None,
+                "peak_source": f"{peak_kind} HBM copy bandwidth",
+                "algorithmic_bytes_per_launch": world_bytes / self.dist.world}
+
+
+def measure_config(name, dist_info, device, scaling, steps, warmup, issue_tflops,
+                   placement="slices", use_graph=True):
+    """One entry of ``configs``: validated, graph-replay and isolated timings."""
+    kind, shape = WORKLOADS[name]
+    measured = Measured(name, kind, shape, dist_info, device, scaling, placement)
+    try:
+        measured.validate()
+        elapsed_ms, how = measured.time_replay(steps, warmup, use_graph)
+        isolated = measured.time_isolated()
+        measured.revalidate_first()
+        elapsed_ms, isolated = dist_info.max_over_ranks([elapsed_ms, isolated], device)
+        flops, byts = dist_info.sum_over_ranks([measured.flops, measured.bytes], device)
+        err, = dist_info.max_over_ranks([measured.max_abs_err], device)
+        per_call_us = elapsed_ms * 1e3 / steps
+        entry = {
+            "config": name + ("_lpt" if placement == "lpt" else ""),
+            "workload": f"nvfp4 {kind} GEMM {shape} l=1, fp16 out",
+            "us_per_call": per_call_us, "isolated_us": isolated,
+            "timing": f"{how}, back-to-back (PDL overlap); isolated_us: single launches, median",
+            "tflops": flops / (per_call_us * 1e-6) / 1e12,
+            "roofline": measured.roofline(name, per_call_us, flops, byts, issue_tflops),
+            "plan": measured.info, "operand_sets": measured.sets,
+            "validated": measured.validated, "max_abs_err": err, "steps": steps,
+            "owned_by_rank0": measured.owned,
+        }
+        return entry
+    finally:
+        measured.close()
+
+
+def competitors(device, square_iters: int) -> list[dict]:
+    """Library NVFP4 GEMMs on this GPU, same event method (graph replay over rotating operand
+    sets): cuBLASLt through torch._scaled_mm (the call of the task's own reference,
+    resources/nvfp4_gemm/reference.py:27-53) and cuDNN through FlashInfer's mm_fp4."""
+    results = []
+
+    def operands(m, n, k, sets):
+        g = torch.Generator(device=device).manual_seed(1)
+        rows = lambda r: -(-r // 128) * 128  # noqa: E731
+        cols = -(-(k // 16) // 4) * 4
+        out = []
+        for _ in range(sets):
+            a = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device=device, generator=g)
+            b = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=device, generator=g)
+            sa = torch.randint(0x30, 0x38, (rows(m), cols), dtype=torch.uint8, device=device,
+                               generator=g)
+            sb = torch.randint(0x30, 0x38, (rows(n), cols), dtype=torch.uint8, device=device,
+                               generator=g)
+            out.append((a, b, sa, sb))
+        return out
+
+    def timed(fn, sets, iters):
+        for i in range(5):
+            fn(i % sets)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                fn(i % sets)
+        graph.replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e3 / iters
+
+    def scaled_mm(m, n, k, ops):
+        f4, e4 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+        prepared = [(a.view(f4), b.view(f4).t(), sa.view(e4).flatten(), sb.view(e4).flatten())
+                    for a, b, sa, sb in ops]
+        return lambda i: torch._scaled_mm(*prepared[i], bias=None, out_dtype=torch.float16)
+
+    def cudnn_mm(m, n, k, ops):
+        import flashinfer
+
+        alpha = torch.ones(1, device=device)
+        e4 = torch.float8_e4m3fn
+        prepared = [(a, b.t(), sa.view(e4), sb.view(e4).t()) for a, b, sa, sb in ops]
+        outs = [torch.empty(m, n, dtype=torch.float16, device=device) for _ in ops]
+        return lambda i: flashinfer.mm_fp4(*prepared[i], alpha, torch.float16, outs[i],
+                                           backend="cudnn")
+
+    for label, make in (("cublaslt via torch._scaled_mm", scaled_mm),
+                        ("cudnn via flashinfer.mm_fp4", cudnn_mm)):
+        for name in ("decode", "square"):
+            shape = WORKLOADS[name][1]
+            m, n, k = shape["m"], shape["n"], shape["k"]
+            sets = 4 if name == "decode" else 3
+            try:
+                iters = square_iters if name == "square" else 200
+                us = timed(make(m, n, k, operands(m, n, k, sets)), sets, iters)
+                results.append({"library": label, "config": name, "us_per_call": us,
+                                "tflops": 2.0 * m * n * k / us / 1e6, "steps": iters})
+            except Exception as error:
+                results.append({"library": label, "config": name,
+                                "unavailable": f"unavailable on this box: {error!r}"[:300]})
+            torch.cuda.empty_cache()
+    return results
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=2000)
-    parser.add_argument("--warmup", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="native", choices=("native", "reference"))
-    parser.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default="square", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-graph", action="store_true")
-    parser.add_argument("--scaling", default="weak", choices=("weak", "strong"),
-                        help="weak: every rank runs the whole shape (global N = ranks x N); "
-                             "strong: the shape's N is split over the ranks")
+    parser.add_argument("--no-configs", action="store_true",
+                        help="headline workload only (no configs array, no competitors)")
+    parser.add_argument("--scaling", default="strong", choices=("strong", "weak"),
+                        help="strong: the workload's N is split over the ranks; weak: every "
+                             "rank runs the whole shape")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    kind, shape = WORKLOADS[args.workload]
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    name = args.workload
+    kind, shape = WORKLOADS[name]
+    info = Distributed()
+    # Libraries print to stdout as they please (cuDNN announces its handle): everything but
+    # the one JSON line goes to stderr.
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
 
+    args.json_out = json_out
     if args.impl == "reference":
-        reference_arm(args, kind, shape, rank)
+        reference_arm(args, name, kind, shape, info.rank)
         return
-    global_n = shape.get("n")
-    if args.scaling == "strong" and world > 1:
-        if kind == "grouped" or shape["n"] % (128 * world):
-            raise SystemExit("strong scaling needs a dense or dual shape whose N splits into "
-                             "multiples of 128 rows per rank")
-        shape = dict(shape, n=shape["n"] // world)
 
     import torch.distributed as dist
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(info.local_rank)
+    device = torch.device("cuda", info.local_rank)
+    world = info.world
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
-    flops, byts = algorithmic_work(kind, shape)
-    set_bytes = byts  # operands + output of one set
-    sets = max(3, int(2 * L2_BYTES // set_bytes) + 1)
-    sets = min(sets, 8 if args.scaling == "weak" else 32)
-    cls = workload_class(kind)
-    # One workload (and so one native plan with cached tensor maps) per operand set.
-    workloads = [cls.from_arch("sm_100a", device=device) for _ in range(sets)]
-    operand_sets = [make_operand_set(kind, shape, index, rank, device) for index in range(sets)]
-    prepared = [w.prepare(inputs) for w, inputs in zip(workloads, operand_sets)]
-    launches = [launch for launch, _ in prepared]
-    info = {}
-    if kind == "dense":
-        info = workloads[0].plan_info(operand_sets[0])
+    from harness import native, sharding
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    issue_tflops = None
+    try:
+        issue_tflops = native.measure_mma_peak(info.local_rank, 4096)
+    except Exception:
+        pass
 
-    def run_steps(count: int, offset: int = 0):
-        for i in range(count):
-            launches[(offset + i) % sets]()
+    with ClockSampler(info.local_rank) as clocks:
+        headline = Measured(name, kind, shape, info, device, args.scaling)
+        headline.validate()
+        t_begin = time.perf_counter()
+        elapsed_ms, how = headline.time_replay(args.steps, args.warmup, not args.no_graph)
+        t_end = time.perf_counter()
+        headline.last_ms = elapsed_ms
+        clock_line = clocks.summary(t_begin, t_end)
 
-    with ClockSampler(local_rank) as clocks:
-        run_steps(args.warmup)
-        barrier()
-        graph = None
-        if not args.no_graph:
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    run_steps(args.steps)
-                graph.replay()  # warm the instantiated graph once
-                barrier()
-            except Exception as error:  # capture unsupported: time direct launches
-                print(f"[bench] CUDA graph capture failed ({error}); timing direct launches",
-                      file=sys.stderr)
-                graph = None
-                barrier()
+        # Direct (non-graph) launches and isolated single launches, for the record.
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
+        info.barrier()
+        direct_steps = min(args.steps, 200)
         start.record()
-        if graph is not None:
-            graph.replay()
-        else:
-            run_steps(args.steps)
+        headline.run(direct_steps)
         stop.record()
-        barrier()
-        elapsed_ms = start.elapsed_time(stop)
-        for w in workloads:
-            w.check_status()
+        info.barrier()
+        direct_us = start.elapsed_time(stop) * 1e3 / direct_steps
+        isolated_us = headline.time_isolated()
+        sustained = headline.time_sustained(3.0, args.steps) if BOUND[name] == "tensor" else None
+        headline.revalidate_first()
 
-        # Direct (non-graph) launches, for the record.
-        barrier()
-        start.record()
-        run_steps(min(args.steps, 500))
-        stop.record()
-        barrier()
-        direct_us = start.elapsed_time(stop) * 1e3 / min(args.steps, 500)
+        # The optional exchange: every rank's columns of D gathered on every rank.
+        gather_us = None
+        if world > 1 and args.scaling == "strong" and kind != "grouped":
+            spans = sharding.row_shards(shape["n"], world)
+            local = headline.outputs[0][0]
+            for _ in range(2):
+                sharding.all_gather_columns(local, spans)
+            info.barrier()
+            times = []
+            for _ in range(5):
+                start.record()
+                sharding.all_gather_columns(local, spans)
+                stop.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(stop) * 1e3)
+            gather_us, = info.max_over_ranks([statistics.median(times)], device)
 
         # End to end through the operator API: pinned host operands in, D out, per step.
-        e2e_steps = max(3, min(args.steps, 30))
-        host_sets = [tuple(t.cpu().pin_memory() for t in inputs) for inputs in operand_sets[:2]]
-        # Device staging tensors in the operands' memory layout.
-        staging = [tuple(torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=device)
-                         for t in operand_sets[0]) for _ in range(2)]
-        host_out = None
-        h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
+        e2e_steps = max(3, min(args.steps, 10 if headline.bytes > (64 << 20) else 30))
+        h2d = d2h = 0
+        e2e_ms = 0.0
+        if headline.active:
+            host_sets = [tuple(t.cpu().pin_memory() for t in inputs)
+                         for inputs in headline.operands[:2]]
+            staging = [tuple(torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=device)
+                             for t in headline.operands[0]) for _ in range(2)]
+            h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
+            host_out = [None]
 
-        def e2e_step(i: int):
-            nonlocal host_out
-            src, dst = host_sets[i % 2], staging[i % 2]
-            for s, d in zip(src, dst):
-                d.copy_(s, non_blocking=True)
-            outputs = workloads[i % 2].run(dst)
-            outs = [o.to("cpu", non_blocking=True) for o in outputs]
-            torch.cuda.current_stream().synchronize()
-            host_out = outs
-            return sum(o.numel() * o.element_size() for o in outputs)
+            def e2e_step(i: int) -> int:
+                src, dst = host_sets[i % 2], staging[i % 2]
+                for s, d in zip(src, dst):
+                    d.copy_(s, non_blocking=True)
+                outputs = headline.workload.run(dst)
+                outs = [o.to("cpu", non_blocking=True) for o in outputs]
+                torch.cuda.current_stream().synchronize()
+                host_out[0] = outs
+                return sum(o.numel() * o.element_size() for o in outputs)
 
-        d2h = e2e_step(0)
-        e2e_step(1)
-        barrier()
-        start.record()
-        for i in range(e2e_steps):
-            e2e_step(i)
-        stop.record()
-        barrier()
-        e2e_ms = start.elapsed_time(stop)
-
-    times = torch.tensor([elapsed_ms, e2e_ms, direct_us], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, direct_us = (float(v) for v in times.tolist())
-
-    if rank == 0:
-        per_call_us = elapsed_ms * 1e3 / args.steps
-        value = world * flops * args.steps / (elapsed_ms * 1e-3) / 1e12
-        e2e_value = world * flops * e2e_steps / (e2e_ms * 1e-3) / 1e12
-        peak, peak_kind = measured_hbm_peak()
-        achieved = byts / (per_call_us * 1e-6) / 1e9
-        bound = "tensor" if args.workload == "square" else "hbm"
-        if bound == "hbm":
-            roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                        "frac": achieved / peak,
-                        "traffic": DECODE_DRAM_TRAFFIC_BYTES if args.workload == "decode" else None,
-                        "peak_source": f"{peak_kind} HBM copy bandwidth",
-                        "algorithmic_bytes_per_launch": byts}
+            d2h = e2e_step(0)
+            e2e_step(1)
+            info.barrier()
+            start.record()
+            for i in range(e2e_steps):
+                e2e_step(i)
+            stop.record()
+            info.barrier()
+            e2e_ms = start.elapsed_time(stop)
+            # The bytes that came back are the GEMM's: compare them with the reference.
+            reference = headline.workload.get_reference(staging[(e2e_steps - 1) % 2])
+            headline.workload.validate(
+                tuple(r.cpu() for r in reference), tuple(host_out[0]))
+            del reference, host_sets, staging
         else:
-            tf = flops / (per_call_us * 1e-6) / 1e12
-            peak_tf = 9000.0
-            # The rate at which this GPU issues block-scaled FP4 MMAs with nothing else
-            # running (the library's own microbenchmark, after the timed region).
-            from harness import native
-            issue_tf = native.measure_mma_peak(local_rank, 4096)
-            roofline = {"bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s",
-                        "frac": tf / peak_tf, "traffic": None,
-                        "peak_source": "nominal dense FP4",
-                        "measured_mma_issue_tflops": issue_tf,
-                        "frac_of_measured_mma_issue": tf / issue_tf,
-                        "algorithmic_flops_per_launch": flops}
+            info.barrier()
+            info.barrier()
+
+        elapsed_ms, e2e_ms, direct_us, isolated_us = info.max_over_ranks(
+            [elapsed_ms, e2e_ms, direct_us, isolated_us], device)
+        world_flops, world_bytes, h2d_all, d2h_all = info.sum_over_ranks(
+            [headline.flops, headline.bytes, float(h2d), float(d2h)], device)
+        err, = info.max_over_ranks([headline.max_abs_err], device)
+        plan_info, sets, owned = headline.info, headline.sets, headline.owned
+        per_call_us = elapsed_ms * 1e3 / args.steps
+        roofline = headline.roofline(name, per_call_us, world_flops, world_bytes, issue_tflops)
+        sustained_line = None
+        if sustained is not None:
+            sustained_us, s0, s1 = sustained
+            s_clock = clocks.summary(s0, s1)
+            sustained_line = {
+                "us_per_call": sustained_us,
+                "tflops": world_flops / world / (sustained_us * 1e-6) / 1e12,
+                "seconds": s1 - s0, "sm_mhz": s_clock.get("sm_mhz"),
+                "reasons": s_clock.get("reasons"),
+                "us_times_mhz": sustained_us * (s_clock.get("sm_mhz") or 0),
+                "note": "graph replayed back to back for ~3 s on this rank: the clock is "
+                        "whatever the power limit leaves",
+            }
+        headline.close()
+
+        configs = []
+        if not args.no_configs:
+            for other in ("latency", "decode", "dual", "grouped"):
+                if other == name:
+                    continue
+                steps = 1000 if other == "latency" else 200
+                if world > 1 and other == "latency":
+                    continue  # two 128-row shards at most: not a multi-GPU problem
+                configs.append(measure_config(other, info, device, args.scaling, steps, 20,
+                                              issue_tflops, use_graph=not args.no_graph))
+                if other == "grouped" and world > 1 and args.scaling == "strong":
+                    configs.append(measure_config(other, info, device, args.scaling, steps, 20,
+                                                  issue_tflops, placement="lpt",
+                                                  use_graph=not args.no_graph))
+        all_clock = clocks.summary()
+
+    if info.rank == 0:
+        value = world_flops * args.steps / (elapsed_ms * 1e-3) / 1e12
+        e2e_value = world_flops * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_ms else 0.0
+        split = (f" (global n = {shape.get('n')} split over {world} ranks in 128-row shards)"
+                 if world > 1 and args.scaling == "strong" else
+                 f" (every one of {world} ranks runs the whole shape)" if world > 1 else "")
         line = {
             "metric": "nvfp4_gemm_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": elapsed_ms / args.steps, "us_per_call": per_call_us,
+            "isolated_us": isolated_us,
             "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "nvfp4", "data": "synthetic",
+            "validated": True, "max_abs_err": err,
             "config": {
-                "workload": f"nvfp4 {kind} GEMM {shape} l=1, fp16 out, per GPU"
-                            + (f" (global n = {world} x {shape.get('n')})"
-                               if world > 1 and args.scaling == "weak" else "")
-                            + (f" (global n = {global_n} split over {world} ranks)"
-                               if world > 1 and args.scaling == "strong" else ""),
-                "operand_sets": sets, "l2": f"{sets} operand sets of {set_bytes / 2**20:.0f} MiB "
-                                            "rotate, larger than the 126 MB L2 together",
-                "timing": "cuda_graph_replay" if graph is not None else "direct_launches",
-                "direct_launch_us_per_call": direct_us, "plan": info,
+                "workload": f"{name}: nvfp4 {kind} GEMM {shape} l=1, fp16 out" + split,
+                "operand_sets": sets,
+                "l2": f"{sets} operand sets rotate, larger than the 126 MB L2 together",
+                "timing": f"{how}, back-to-back (PDL overlap); isolated_us: single launches, "
+                          "median",
+                "direct_launch_us_per_call": direct_us, "plan": plan_info,
                 "sharding": "each rank owns an N-shard; no collective on the data path",
+                "rank0_owns": owned,
             },
             "roofline": roofline,
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "ms_per_step": e2e_ms / e2e_steps},
+            "sustained": sustained_line,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d_all),
+                    "d2h_bytes_per_step": int(d2h_all), "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps if e2e_steps else None,
+                    "validated": True},
             "gpu_launches": args.steps,
-            "clocks": clocks.summary(),
+            "clocks": clock_line,
+            "clocks_whole_run": all_clock,
+            "configs": configs,
         }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(kind, shape)
-        else:
-            line["cpu_baseline"] = None
-        print(json.dumps(line), flush=True)
+        if gather_us is not None:
+            line["all_gather_us"] = gather_us
+        if world == 1 and not args.no_configs:
+            line["competitors"] = competitors(
+                device, args.steps if name == "square" else 50)
+        line["cpu_baseline"] = None if args.no_cpu_baseline else cpu_baseline(kind, shape)
+        print(json.dumps(line), file=json_out, flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

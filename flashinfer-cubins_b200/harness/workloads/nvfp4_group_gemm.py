@@ -159,6 +159,16 @@ class NVFP4GroupGEMM(Workload):
             plan.bind_groups(*config.pointers, workspace.data_ptr(), self.stream_handle())
             config.plan, config.workspace = plan, workspace
 
+    def plan_info(self, inputs: tuple) -> dict:
+        """What the native plan for these inputs decided (tile, schedule, grid)."""
+        config = self.launch_config(inputs, self.allocate_outputs(inputs))
+        with self._lock, torch.cuda.device(self.device):
+            plan, _ = self.plan_for(
+                ("group", config.problems),
+                lambda: native.Plan.grouped(self.device_index(), config.problems),
+            )
+        return plan.info()
+
     def _launch(self, config: LaunchConfig) -> None:
         with self._lock, torch.cuda.device(self.device):
             config.plan.launch_groups(config.workspace.data_ptr(), self.stream_handle())
