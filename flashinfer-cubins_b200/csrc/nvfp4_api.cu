@@ -504,6 +504,9 @@ int prepare_kernel(nvfp4_plan* plan) {
       plan->inbox_offset = plan->ring_stages * plan->kernel.stage_bytes;
     }
   }
+  // Experiments: fewer pipeline stages than the kernel has room for (single-CTA kernel).
+  const int fewer = env_int("NVFP4_STAGES", 0);
+  if (!plan->pair && fewer >= 2 && fewer < plan->ring_stages) plan->ring_stages = fewer;
   return 0;
 }
 

@@ -4,10 +4,33 @@ lists use from the reference's ``harness/throughput.py`` (lines 31-44, 87-113)."
 
 from __future__ import annotations
 
+import json
 import random
+from functools import lru_cache
 
 from .models import MODELS
-from .workload import CaseSpec
+from .workload import ROOT, CaseSpec
+
+# The reference's downloaded trace inventories (none of them belongs to an NVFP4 GEMM
+# workload; they are read only where ``REFERENCE_ROOT`` names a checkout that has them).
+DATA = ROOT / "resources/benchmark_workloads"
+
+
+@lru_cache(None)
+def inventory(name):
+    """(rows, manifest entry) of trace inventory ``name`` (``harness/throughput.py:47-55``
+    in the reference)."""
+    rows = [json.loads(line)["workload"]
+            for line in (DATA / f"{name}.jsonl").read_text().splitlines()]
+    return rows, json.loads((DATA / "manifest.json").read_text())[name]
+
+
+def throughput_cases(package):
+    """The throughput cases the kernels of ``harness.workloads.<package>`` must serve
+    together (that module's ``throughput_cases()``)."""
+    from importlib import import_module
+
+    return import_module(f"{__package__}.workloads.{package}").throughput_cases()
 
 
 def skewed_lengths(total, batch, seed=0, sigma=1.0, minimum=1):

@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import contextlib
 import functools
+import os
 import re
 import threading
 from abc import ABC, abstractmethod
@@ -39,7 +40,13 @@ import torch
 
 from . import native
 
-ROOT = Path(__file__).resolve().parents[1]
+# Where data files of the reference project are looked up (its ``resources/`` tree: the
+# NVIDIA task definitions and the trace inventories, which are not part of this package).
+# ``REFERENCE_ROOT`` names a checkout of the reference; without it the paths simply do not
+# exist and everything that needs only this package's own case tables still works.
+ROOT = Path(os.environ.get("REFERENCE_ROOT") or Path(__file__).resolve().parents[1])
+IMPLS = ROOT / "impls"
+MANIFEST = "kernels.json"
 IMAGE_PREFIX = b"nvfp4-b200-cabi:"
 
 
@@ -165,6 +172,15 @@ class Workload(ABC):
             self._accept_image(cubin)
 
     # -- construction -------------------------------------------------------------------
+
+    @classmethod
+    def manifest_path(cls) -> Path:
+        """Where the reference keeps the cubin manifest of this workload's package
+        (``impls/<package>/kernels.json``, ``harness/workload.py:312-314`` there). Nothing
+        is read from it here; its parent's name is how callers group workloads by
+        package."""
+        package = cls.package or cls.__module__.rsplit(".", 1)[-1]
+        return IMPLS / package / MANIFEST
 
     @classmethod
     def default_arch(cls, device: str | torch.device | None = None) -> str | None:

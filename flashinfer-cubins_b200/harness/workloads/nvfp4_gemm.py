@@ -56,6 +56,44 @@ TASK_SEED = 1111
 BLOCKED_ORDER = (5, 2, 4, 0, 1, 3)  # permutation that makes a task-view scale tensor contiguous
 
 
+class TaskLines:
+    """The test and benchmark lines of one NVIDIA task as this package records them. The
+    reference keeps a path to the task's ``task.yml`` under this name (``TASK``) and parses
+    it on every use (``nvfp4_gemm.py:72,481-491`` there); here the lines are tables in the
+    workload modules and ``task_shapes`` turns them into the same list of dicts."""
+
+    def __init__(self, name: str, tests, benchmarks, seed: int = TASK_SEED):
+        self.name, self.tests, self.benchmarks, self.seed = name, tuple(tests), tuple(benchmarks), seed
+
+
+TASK = TaskLines("nvfp4_gemm", TASK_TESTS, TASK_BENCHMARKS)
+
+
+def task_shapes(task: TaskLines, section: str) -> list[dict[str, Any]]:
+    """The ``tests`` or ``benchmarks`` entries of a task: dicts with ``m, n, k, l`` (lists
+    per group for the grouped task) and the task's ``seed``."""
+    if section not in ("tests", "benchmarks"):
+        raise ValueError(f"unknown section {section!r}")
+    entries = []
+    for line in getattr(task, section):
+        if line and isinstance(line[0], (tuple, list)):  # grouped: (ms, ns, ks)
+            ms, ns, ks = line
+            entry = {"m": list(ms), "n": list(ns), "k": list(ks), "g": len(ms)}
+        else:
+            entry = dict(zip(("m", "n", "k", "l"), line))
+        entry["seed"] = task.seed
+        entries.append(entry)
+    return entries
+
+
+def fake_encode(*args, **kwargs):
+    """The reference's deterministic stand-in for ``cuTensorMapEncodeTiled``, which its
+    tests use to compare CUTLASS ``Params`` bytes (``nvfp4_gemm.py:78-102`` there). This
+    package builds no ``Params`` struct, so there is nothing for it to encode."""
+    raise NotImplementedError("no CUTLASS Params are built here; tensor maps are encoded "
+                              "inside the native library")
+
+
 def blocked_scale_shape(rows: int, k: int, batches: int) -> tuple[int, ...]:
     """Shape of the task's permuted view of the blocked scales of a rows x k operand."""
     return (32, 4, ceil_div(rows, SF_ROWS), SF_COLS, ceil_div(ceil_div(k, SF_VEC), SF_COLS), batches)
@@ -89,8 +127,11 @@ def fp4_case(m, n, k, l=1, *, seed, suite="smoke", **extra) -> CaseSpec:  # noqa
     return CaseSpec("_".join(f"{key}{value}" for key, value in params.items()), params, seed, suite)
 
 
-def task_cases(shapes: Sequence[tuple[int, int, int, int]], name: str, **extra) -> list[CaseSpec]:
-    """One smoke case per distinct task test shape, with the task's seed."""
+def task_cases(shapes, name: str, **extra) -> list[CaseSpec]:
+    """One smoke case per distinct task test shape, with the task's seed. ``shapes`` is a
+    sequence of ``(m, n, k, l)`` or a ``TaskLines`` (its test lines)."""
+    if isinstance(shapes, TaskLines):
+        shapes = shapes.tests
     cases: dict[str, CaseSpec] = {}
     for index, (m, n, k, l) in enumerate(shapes):  # noqa: E741
         label = f"task_m{m}_n{n}_k{k}_l{l}"

@@ -27,7 +27,7 @@ from .. import native
 from ..registry import register
 from ..throughput import model_case, skewed_lengths, upstream_case
 from ..workload import CaseSpec, Workload
-from .nvfp4_gemm import official_source
+from .nvfp4_gemm import TaskLines, fake_encode, official_source
 from .quantization import ceil_div, fp4_matmul, from_blocked_scales, make_fp4, to_blocked_scales
 
 SF_VEC = 16  # K elements per scale factor
@@ -55,6 +55,31 @@ TASK_BENCHMARKS = (
     ((192, 320), (3072, 3072), (4096, 4096)),
     ((128, 384), (4096, 4096), (1536, 1536)),
 )
+
+
+TASK = TaskLines("nvfp4_group_gemm", TASK_TESTS, TASK_BENCHMARKS, TASK_SEED)
+# The reference names here the per-group device arrays of a CUTLASS grouped launch
+# (``nvfp4_group_gemm.py:250-315`` there). The native library keeps one table of problems
+# and two tensor maps per group in its workspace instead, so there are none to list.
+ARRAYS: tuple[str, ...] = ()
+
+
+def fast_divmod_u64(divisor: int) -> tuple[int, int, int, int]:
+    """``(divisor, multiplier, shift, round_up)`` with which an unsigned 64-bit division is
+    a multiply-high and a shift: ``x // divisor == (((x + round_up) * multiplier) >> 64)
+    >> shift`` when ``multiplier`` is non-zero, ``x >> shift`` when it is zero (powers of
+    two). The reference packs such constants into its grouped kernel's scheduler parameters
+    (``nvfp4_group_gemm.py:113-137`` there); the persistent scheduler of this package
+    divides on the device and does not use them, the function is kept for callers that do.
+    With ``shift = floor(log2(divisor))`` the multiplier ``ceil(2**(64 + shift) / divisor)``
+    lies in ``[2**63, 2**64)`` and the quotient is exact for every ``x < 2**63``."""
+    if divisor < 1:
+        raise ValueError("divisor must be positive")
+    shift = divisor.bit_length() - 1
+    if divisor == 1 << shift:
+        return divisor, 0, shift, 0
+    multiplier = -(-(1 << (64 + shift)) // divisor)
+    return divisor, multiplier, shift, 0
 
 
 def blocked_shape(rows: int, k: int) -> tuple[int, int, int, int, int]:

@@ -44,7 +44,7 @@ def test_dense_full_size_exact_with_integer_scales(m, n, k):
         assert torch.equal(out, again), "two launches must agree bit for bit"
 
 
-def test_dense_decode_shape_with_normal_operands_and_shards():
+def test_C2_decode_config_with_normal_operands_and_shards():
     m, n, k = 128, 7168, 16384
     dev = torch.device("cuda")
     with get_workload("nvfp4_gemm").from_arch("sm_100a", device="cuda") as workload:
@@ -73,7 +73,7 @@ def test_dense_decode_shape_with_normal_operands_and_shards():
         workload.check_status()
 
 
-def test_dual_config_matches_reference_with_normal_operands():
+def test_C4_dual_config_matches_reference_with_normal_operands():
     m, n, k = 256, 4096, 7168
     dev = torch.device("cuda")
     with get_workload("nvfp4_dual_gemm").from_arch("sm_100a", device="cuda") as workload:
@@ -93,7 +93,7 @@ def test_dual_config_matches_reference_with_normal_operands():
         torch.testing.assert_close(out[finite], ref[finite], rtol=1e-2, atol=1e-2)
 
 
-def test_grouped_config_exact_with_task_distribution():
+def test_C5_grouped_config_exact_with_task_distribution():
     ms = (40, 96, 128, 256, 384, 512, 768, 1024)
     with get_workload("nvfp4_group_gemm").from_arch("sm_100a", device="cuda") as workload:
         case = CaseSpec("config5", {"groups": [(m, 4096, 7168) for m in ms]}, 1111)
@@ -104,3 +104,57 @@ def test_grouped_config_exact_with_task_distribution():
         workload.check_status()
         for got, want in zip(out, ref):
             assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (8192, 8192, 8192)],
+                         ids=["C1_latency_128x256x512", "C3_square_8192x8192x8192"])
+def test_dense_config_with_normal_operands(m, n, k):
+    """The benchmark's own operands (N(0,1) -> NVFP4, seeds A = 1 and B = 2, unit-range
+    scales, where the order of the FP32 sums matters) at the reference's tolerance
+    rtol = atol = 1e-3 (harness/workloads/nvfp4_gemm.py:600 there), and run-to-run
+    determinism."""
+    dev = torch.device("cuda")
+    with get_workload("nvfp4_gemm").from_arch("sm_100a", device="cuda") as workload:
+        a, sa = normal_operand(m, k, 1, dev)
+        b, sb = normal_operand(n, k, 2, dev)
+        inputs = (a, b, to_task_scales(sa), to_task_scales(sb), torch.ones(1, device=dev))
+        (ref,) = workload.get_reference(inputs)
+        (out,) = workload.run(inputs)
+        (again,) = workload.run(inputs)
+        torch.cuda.synchronize()
+        workload.check_status()
+        workload.validate((ref,), (out,))
+        assert torch.equal(out, again)
+
+
+def test_C5_grouped_config_with_normal_operands_and_column_slices():
+    """Grouped configuration with the benchmark's operands (group g: seeds A = 10 + g,
+    B = 20 + g) at rtol = atol = 1e-3, and the multi-GPU decomposition on one GPU: every
+    rank's (group, column range) units of a four-way split, run as that rank's own grouped
+    launch, equal the matching columns of the full result within the tolerance."""
+    from harness.workloads.nvfp4_group_gemm import to_blocked
+
+    ms = (40, 96, 128, 256, 384, 512, 768, 1024)
+    n, k = 4096, 7168
+    dev = torch.device("cuda")
+    tensors = []
+    for g, m in enumerate(ms):
+        a, sa = normal_operand(m, k, 10 + g, dev)
+        b, sb = normal_operand(n, k, 20 + g, dev)
+        tensors += [a[..., 0].contiguous(), b[..., 0].contiguous(),
+                    to_blocked(sa[..., 0]), to_blocked(sb[..., 0])]
+    inputs = tuple(tensors)
+    with get_workload("nvfp4_group_gemm").from_arch("sm_100a", device="cuda") as workload:
+        ref = workload.get_reference(inputs)
+        out = workload.run(inputs)
+        torch.cuda.synchronize()
+        workload.check_status()
+        workload.validate(ref, out)
+        for rank in range(4):
+            part, spans = sharding.shard_group_inputs(inputs, rank, 4)
+            assert [g for g, _, _ in spans] == list(range(len(ms)))
+            pieces = workload.run(part)
+            torch.cuda.synchronize()
+            workload.check_status()
+            expected = tuple(ref[g][:, start:stop].contiguous() for g, start, stop in spans)
+            workload.validate(expected, tuple(p.contiguous() for p in pieces))
