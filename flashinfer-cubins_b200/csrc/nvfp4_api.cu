@@ -565,10 +565,12 @@ int bound_params(const nvfp4_plan* plan, const void* const (&key)[10], Encode en
   return 0;
 }
 
-int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream) {
+int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream,
+                KernelFn kernel_override = nullptr) {
   DeviceGuard guard;
   CUDA_TRY(guard.enter(plan->device));
   void* args[1] = {&kp};
+  const KernelFn kernel = kernel_override != nullptr ? kernel_override : plan->kernel.fn;
   // Programmatic stream serialization (as the reference's dense launches use,
   // harness/workloads/nvfp4_gemm.py:143-147): this kernel's prologue may overlap the
   // tail of the kernel before it; it waits on the device before touching global memory.
@@ -594,7 +596,7 @@ int launch_plan(const nvfp4_plan* plan, KernelParams& kp, void* stream) {
   config.stream = static_cast<cudaStream_t>(stream);
   config.attrs = attribute;
   config.numAttrs = attributes;
-  CUDA_TRY(cudaLaunchKernelExC(&config, reinterpret_cast<const void*>(plan->kernel.fn), args));
+  CUDA_TRY(cudaLaunchKernelExC(&config, reinterpret_cast<const void*>(kernel), args));
   return 0;
 }
 
@@ -892,7 +894,7 @@ namespace {
 // the former).
 int launch_dense(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                  const void* sfb, const float* alpha, void* d, void* sfd, void* workspace,
-                 void* stream) {
+                 void* stream, KernelFn kernel_override = nullptr) {
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || alpha == nullptr ||
       d == nullptr || workspace == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
@@ -931,12 +933,33 @@ int launch_dense(const nvfp4_plan* plan, const void* a, const void* b, const voi
       },
       &kp);
   if (rc != 0) return rc;
-  return launch_plan(plan, kp, stream);
+  return launch_plan(plan, kp, stream, kernel_override);
 }
 
 }  // namespace
 
 extern "C" {
+
+int nvfp4_selftest_abandoned_wait(const nvfp4_plan* plan, const void* a, const void* b,
+                                  const void* sfa, const void* sfb, const float* alpha, void* d,
+                                  void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kDense || plan->out_kind != NVFP4_OUT_F16 || plan->pair ||
+      plan->tile_n != 128 || plan->schedule == 3) {
+    return fail(NVFP4_E_INVALID_ARGUMENT,
+                "the self-test runs dense FP16 plans with 128-column tiles (config.tile_n = 128, "
+                "schedule 1 or 2) only");
+  }
+  using Stalled = GemmConfig<128, false, __half, false>;
+  const KernelFn kernel = &nvfp4_gemm_kernel<Stalled, true>;
+  {
+    DeviceGuard guard;
+    CUDA_TRY(guard.enter(plan->device));
+    CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  Stalled::SMEM_BYTES));
+  }
+  return launch_dense(plan, a, b, sfa, sfb, alpha, d, nullptr, workspace, stream, kernel);
+}
 
 int nvfp4_gemm_launch(const nvfp4_plan* plan, const void* a, const void* b, const void* sfa,
                       const void* sfb, const float* alpha, void* d, void* workspace,

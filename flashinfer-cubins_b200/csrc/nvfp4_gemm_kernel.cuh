@@ -610,10 +610,16 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
   }
 }
 
-template <class Cfg>
+// STALLED is the failure-detection self-test: the producer issues no copy at all, so every
+// other role waits on a barrier that nothing completes, and the wait limit is a few
+// milliseconds instead of about a second. The kernel must then report the abandoned wait in
+// the status word, stop all roles through the abort flag, free its tensor memory and return
+// by itself. Instantiated once, for nvfp4_selftest_abandoned_wait.
+template <class Cfg, bool STALLED = false>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   constexpr int BN = Cfg::BN;
+  constexpr uint32_t kLimit = STALLED ? (1u << 17) : kWaitLimitSpins;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int ACC_BUFS = Cfg::ACC_BUFS;
   using OutT = typename Cfg::OutT;
@@ -735,7 +741,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         int atoms_left = pd.sf_kb - 4 * s.k0;
         int kbyte = s.k0 * 128;
         for (int kt = s.k0; kt < s.k1; ++kt) {
-          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_ptr)) {
+          if (!mbar_wait<kLimit>(empty0 + 8 * stage, phase ^ 1u, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusProducerTimeout);
             ok = false;
             break;
@@ -750,7 +756,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
           // Scales first, on their own barrier: they are small, land early, and the
           // scale movers can put them into tensor memory while A and B are still in
           // flight.
-          if (elect_one()) {
+          if (!STALLED && elect_one()) {
             mbar_expect_tx(sf_bar, sf_bytes * (1u + sfb_valid));
             bulk_load(sfa_dst, sfa_src, sf_bytes, sf_bar, pol_a);
 #pragma unroll
@@ -814,7 +820,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       bool ok = true;
       while (ok && it.next(s)) {
         const ProblemDesc& pd = it.pd;
-        if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) {
+        if (!mbar_wait<kLimit>(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr)) {
           report_failure(p, abort_ptr, kStatusMmaAccumTimeout);
           break;
         }
@@ -825,7 +831,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
         int atoms_left = pd.sf_kb - 4 * s.k0;
         uint32_t accumulate = 0;
         for (int kt = s.k0; kt < s.k1; ++kt) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_ptr)) {
+          if (!mbar_wait<kLimit>(full0 + 8 * stage, phase, abort_ptr)) {
             report_failure(p, abort_ptr, kStatusMmaInputTimeout);
             ok = false;
             break;
@@ -895,7 +901,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       int atoms_left = it.pd.sf_kb - 4 * s.k0;
       const bool upper_half = (s.n_tile & 1) != 0;  // narrow dual: rows 64-127 of the atoms
       for (int kt = s.k0; kt < s.k1; ++kt) {
-        if (!mbar_wait(sf_full0 + 8 * stage, phase, abort_ptr)) {
+        if (!mbar_wait<kLimit>(sf_full0 + 8 * stage, phase, abort_ptr)) {
           report_failure(p, abort_ptr, kStatusScaleTimeout);
           ok = false;
           break;
@@ -977,7 +983,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
     uint32_t acc_phase = 0;
     while (it.next(s)) {
       const ProblemDesc& pd = it.pd;
-      if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr)) {
+      if (!mbar_wait<kLimit>(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr)) {
         report_failure(p, abort_ptr, kStatusEpilogueTimeout);
         break;
       }

@@ -83,12 +83,13 @@ constexpr uint32_t kWaitLimitSpins = 1u << 27;
 // waiting soon after. Returns false when the wait was abandoned. The loop is kept
 // this small on purpose: the single-lane roles run it once per pipeline step, and
 // every extra exit or counter in it showed up as 100-200 clocks per step.
+template <uint32_t LIMIT = kWaitLimitSpins>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag) {
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3FFu) == 0u) {
-      if (*abort_flag != 0 || spins >= kWaitLimitSpins) return false;
+      if (*abort_flag != 0 || spins >= LIMIT) return false;
     }
   }
   return true;

@@ -97,6 +97,7 @@ _PROTOTYPES = {
     "nvfp4_plan_init_workspace": (ctypes.c_int, [_P, _P, _P]),
     "nvfp4_plan_info_get": (ctypes.c_int, [_P, ctypes.POINTER(PlanInfo)]),
     "nvfp4_gemm_launch": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "nvfp4_selftest_abandoned_wait": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_gemm_launch_fp4": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_gemm_launch_static": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
     "nvfp4_static_scratch_bytes": (ctypes.c_size_t, []),
@@ -240,6 +241,12 @@ class Plan:
 
     def launch_dense(self, a, b, sfa, sfb, alpha, d, workspace, stream) -> None:
         check(load().nvfp4_gemm_launch(self.handle, a, b, sfa, sfb, alpha, d, workspace, stream))
+
+    def selftest_abandoned_wait(self, a, b, sfa, sfb, alpha, d, workspace, stream) -> None:
+        """The failure-detection self-test: the same launch with a producer that issues
+        nothing and waits that give up after milliseconds (``status`` then raises)."""
+        check(load().nvfp4_selftest_abandoned_wait(
+            self.handle, a, b, sfa, sfb, alpha, d, workspace, stream))
 
     def launch_dense_fp4(self, a, b, sfa, sfb, alpha, d_packed, d_scales, workspace, stream) -> None:
         """Dense launch of a plan made with ``OUT_FP4``: D quantised to NVFP4 in the epilogue."""

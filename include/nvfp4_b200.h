@@ -211,6 +211,18 @@ int nvfp4_group_gemm_launch(const nvfp4_plan* plan, void* workspace, void* strea
  * undefined. */
 int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int* status);
 
+/* Failure-detection self-test, with no counterpart in the reference: launches the dense
+ * kernel of `plan` (FP16 output, 128-column tiles, data-parallel or stream-K schedule; same
+ * operands as nvfp4_gemm_launch) in a build whose producer issues no copy and whose waits
+ * give up after a few milliseconds. Every role then abandons a wait: the kernel records the
+ * first role's code in the workspace's status word, stops, frees its tensor memory and
+ * returns by itself; D is left unwritten. nvfp4_plan_status afterwards returns
+ * NVFP4_E_DEVICE_TIMEOUT and re-initialises the workspace, and the next nvfp4_gemm_launch
+ * on it is correct. Nothing faults and nothing waits without a bound. */
+int nvfp4_selftest_abandoned_wait(const nvfp4_plan* plan, const void* a, const void* b,
+                                  const void* sfa, const void* sfb, const float* alpha, void* d,
+                                  void* workspace, void* stream);
+
 /* Logical E4M3 scales [batches][rows][cols] -> blocked layout, zero padded, flat
  * [batches][round_up(rows,128) * round_up(cols,4)]. Replaces the pack_scales kernel
  * (impls/nvfp4_dual_gemm/kernels/pack_scales.cu:9-19,

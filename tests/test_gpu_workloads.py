@@ -413,6 +413,46 @@ def test_status_word_and_counters_are_reset_after_a_reported_timeout():
     plan.destroy()
 
 
+@pytest.mark.parametrize("schedule", (1, 2))
+def test_abandoned_wait_is_reported_and_the_context_stays_usable(schedule):
+    """The bounded waits, exercised without a fault: in the self-test build of the dense
+    kernel the producer issues no copy, so the MMA, scale-mover and epilogue roles wait on
+    barriers that nothing completes and give up after a few milliseconds. The kernel must
+    return by itself (tensor memory freed: the launch that follows allocates it again),
+    leave a code in the status word, and nvfp4_plan_status must report the timeout once and
+    re-initialise the workspace, after which the same workspace gives the exact result."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    m, n, k = 256, 384, 2048
+    plan = native.Plan.dense(0, native.OUT_F16, m, n, k, 1, schedule=schedule, tile_n=128)
+    inputs = workload.get_inputs(CaseSpec("stall", {"m": m, "n": n, "k": k, "l": 1}, 13))
+    want = oracle_dense(inputs)
+    ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+    plan.init_workspace(ws.data_ptr(), stream)
+    d = torch.full((1, m, n), float("nan"), dtype=torch.float16, device=dev)
+    pointers = [t.data_ptr() for t in inputs]
+    for _ in range(2):
+        plan.selftest_abandoned_wait(*pointers, d.data_ptr(), ws.data_ptr(), stream)
+        with pytest.raises(native.NativeError) as caught:
+            plan.status(ws.data_ptr(), stream)
+        assert caught.value.status == native.E_DEVICE_TIMEOUT
+        assert torch.isnan(d).all(), "an abandoned launch must not have written D"
+        assert plan.status(ws.data_ptr(), stream) == 0  # reported once, then clear
+        plan.launch_dense(*pointers, d.data_ptr(), ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        assert np.array_equal(d.cpu().numpy(), want)
+        d.fill_(float("nan"))
+    with pytest.raises(ValueError):
+        other = native.Plan.dense(0, native.OUT_F16, m, n, k, 1, tile_n=256, schedule=1)
+        try:
+            other.selftest_abandoned_wait(*pointers, d.data_ptr(), ws.data_ptr(), stream)
+        finally:
+            other.destroy()
+    plan.destroy()
+
+
 def test_native_rejects_misaligned_and_wrong_plans():
     stream = torch.cuda.current_stream().cuda_stream
     plan = native.Plan.dense(0, native.OUT_F16, 128, 128, 128, 1)
