@@ -669,8 +669,12 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   }
   tc_fence_before_sync();
   __syncthreads();
-  // Peers arrive on this CTA's barriers, so they must be initialised cluster-wide.
-  if (p.split > 1) cluster_sync_all();
+  // Peers arrive on this CTA's barriers, so they must be initialised cluster-wide before the
+  // first remote access, which comes only after the mainloop: every thread announces itself
+  // here and collects the others' announcements when it first needs them (the epilogue
+  // before the exchange, everyone else at the exit), instead of stalling the start.
+  if (p.split > 1) cluster_arrive();
+  bool cluster_joined = false;
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
@@ -1097,6 +1101,10 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                                  rows_valid, lane, v);
         }
       } else if (!Cfg::GROUPED && p.split > 1) {  // grouped plans never split in clusters
+        if (!cluster_joined) {
+          cluster_wait();
+          cluster_joined = true;
+        }
         cluster_reduce<Cfg>(p, pd, s, taddr, smem_base, smem_u32(&bar_peer_ready),
                             smem_u32(&bar_peer_data), abort_ptr, alpha, row, epi_tid, grow,
                             out_row, out_block, rows_valid, stage_smem);
@@ -1188,7 +1196,10 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
   tc_fence_before_sync();
   __syncthreads();
   // No CTA of a cluster leaves while a peer could still write into its shared memory.
-  if (p.split > 1) cluster_sync_all();
+  if (p.split > 1) {
+    if (!cluster_joined) cluster_wait();
+    cluster_sync_all();
+  }
   if (warp == 1) {
     tc_fence_after_sync();
     __syncwarp();

@@ -403,6 +403,17 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// The two halves of the cluster barrier, for a thread that has other work between telling
+// the cluster where it is and needing to know where the others are. Every thread of every
+// CTA executes both, in this order, once per barrier phase (whole warps together).
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Programmatic dependent launch: `grid_dependency_wait` blocks until the preceding
 // kernel in the stream has completed and its writes are visible (a no-op when the
 // kernel was not launched with programmatic stream serialization);
