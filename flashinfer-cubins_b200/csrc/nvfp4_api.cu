@@ -240,6 +240,7 @@ struct nvfp4_plan {
   int ctas = 1;
   int split = 1;      // cluster size of schedule 3
   bool pair = false;  // 2-CTA kernel: 256 x 256 tiles, one cluster of two CTAs per tile
+  int b_shuffle = 0;  // 16 / 32: B's rows are in FlashInfer's epilogue-shuffled order
   double estimate_us = 0.0;  // the time model's figure for the chosen schedule (mainloop + tail)
   int ring_stages = 0;       // pipeline stages the kernel cycles through
   int inbox_offset = -1;     // cluster split-K: byte offset of the peers' inbox, or -1
@@ -530,7 +531,7 @@ void fill_common_params(const nvfp4_plan* plan, KernelParams& kp, void* workspac
     if (pd.tiles_m > 1) streams = false;
   }
   kp.b_streams = streams ? 1 : 0;
-  kp.pad1 = 0;
+  kp.b_shuffle = plan->b_shuffle;
 }
 
 // The kernel parameters of a dense or dual launch on the operands named by `key`: taken from
@@ -640,9 +641,19 @@ int check_dense_shape(int m, int n, int k, int l, int out_bytes) {
 }
 
 int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int m, int n, int k,
-                      int l, const nvfp4_config* config) {
+                      int l, const nvfp4_config* config, int b_shuffle = 0) {
   if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
   *out = nullptr;
+  if (b_shuffle != 0) {
+    if (b_shuffle != 16 && b_shuffle != 32) {
+      return fail(NVFP4_E_INVALID_ARGUMENT, "the shuffle block is 16 or 32 rows");
+    }
+    if (kind != kDense || out_kind == NVFP4_OUT_FP4 || n % b_shuffle != 0) {
+      return fail(NVFP4_E_UNSUPPORTED_SHAPE,
+                  "shuffled weights: dense GEMM with FP16, BF16 or FP32 output and n a "
+                  "multiple of the shuffle block");
+    }
+  }
   double chosen_us = 1e30;  // the time model's figure for the best single-CTA plan
   if (out_kind != NVFP4_OUT_F16 && out_kind != NVFP4_OUT_F32 && out_kind != NVFP4_OUT_FP4 &&
       out_kind != NVFP4_OUT_BF16) {
@@ -677,6 +688,7 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
   plan->device = device;
   plan->out_kind = out_kind;
   plan->sm_count = sms;
+  plan->b_shuffle = b_shuffle;
   if (kind == kDual) {
     // The MMA is as wide as both B tiles together: 2 x 128 columns, or 2 x 64 when that
     // fills the SMs better (its accumulator is double-buffered and it needs no K split).
@@ -799,6 +811,14 @@ int nvfp4_device_supported(int device) {
 int nvfp4_gemm_plan_create(nvfp4_plan** plan, int device, int out_kind, int m, int n, int k,
                            int l, const nvfp4_config* config) {
   return create_dense_like(plan, kDense, device, out_kind, m, n, k, l, config);
+}
+
+int nvfp4_gemm_plan_create_shuffled(nvfp4_plan** plan, int device, int out_kind, int m, int n,
+                                    int k, int l, int shuffle_block, const nvfp4_config* config) {
+  if (shuffle_block != 16 && shuffle_block != 32) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "the shuffle block is 16 or 32 rows");
+  }
+  return create_dense_like(plan, kDense, device, out_kind, m, n, k, l, config, shuffle_block);
 }
 
 int nvfp4_dual_gemm_plan_create(nvfp4_plan** plan, int device, int m, int n, int k, int l,

@@ -91,7 +91,8 @@ struct alignas(64) KernelParams {
   int num_problems;
   int mode;
   int b_streams;  // B is read once: mark its loads evict-first in L2
-  int pad1;
+  int b_shuffle;  // 0, or 16 / 32: rows of B (and of its scales) are stored in FlashInfer's
+                  // epilogue-shuffled order inside blocks of that many rows
   int split;      // > 1: CTAs of a cluster of this size split each tile's K (stream-K mode
                   // with grid = tiles * split) and reduce through peer shared memory
   int ring_stages;   // pipeline stages in use (fewer than the kernel's when the top of the
@@ -349,6 +350,26 @@ __device__ __forceinline__ void store_block_coalesced(uint32_t stage, const uint
   __syncwarp();
 }
 
+// Weights prepared for FlashInfer's trtllm-gen kernels have their rows permuted inside blocks
+// of 16 or 32 rows (physical row base + map[o] holds logical row base + o, with
+// map[o] = (o % 4) * 8 + o / 4 for blocks of 32 and (o % 2) * 8 + o / 2 for blocks of 16:
+// harness/workloads/batched_gemm/formats.py:143-161 in the reference). A GEMM on such a B
+// produces the columns of D in the physical order; this puts the 32 columns a thread holds
+// (one or two whole blocks) back in logical order. A register renaming: no data moves.
+__device__ __forceinline__ void unshuffle_columns(float (&v)[32], int block) {
+  if (block == 0) return;
+  float u[32];
+  if (block == 32) {
+#pragma unroll
+    for (int o = 0; o < 32; ++o) u[o] = v[(o % 4) * 8 + o / 4];
+  } else {
+#pragma unroll
+    for (int o = 0; o < 32; ++o) u[o] = v[(o / 16) * 16 + ((o % 16) % 2) * 8 + (o % 16) / 2];
+  }
+#pragma unroll
+  for (int o = 0; o < 32; ++o) v[o] = u[o];
+}
+
 // 32 output columns of the warp's 32 rows: coalesced when the rows of D are 16-byte
 // aligned, row by row otherwise. `v` is this lane's row; `block` as above; `row_ptr`
 // this lane's own row at column 0; `row_ok` whether that row exists.
@@ -604,6 +625,7 @@ __device__ __forceinline__ void cluster_reduce(const KernelParams& p, const Prob
       // Two accumulators are live here; the staged store on top of them spills.
       if (grow < pd.m) store_row_chunk<OutT>(out_row, n0 + c * 32, pd.n, v);
     } else {
+      unshuffle_columns(v, p.b_shuffle);
       store_warp_chunk<OutT>(store_stage, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
                              rows_valid, row & 31, v);
     }
@@ -1097,6 +1119,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bar_acc_empty[acc]));
           }
+          if constexpr (!Cfg::DUAL) unshuffle_columns(v, p.b_shuffle);
           store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
                                  rows_valid, lane, v);
         }
@@ -1179,6 +1202,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
                 v[i] = s1[i] * alpha;
               }
             }
+            if constexpr (!Cfg::DUAL) unshuffle_columns(v, p.b_shuffle);
             store_warp_chunk<OutT>(stage_smem, out_block, out_row, grow < pd.m, n0 + c * 32, pd.n,
                                    rows_valid, lane, v);
           }

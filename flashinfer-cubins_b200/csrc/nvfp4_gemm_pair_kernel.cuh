@@ -441,12 +441,18 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
             tmem_load_32(taddr + 64 * b, r1);
             tmem_load_32(taddr + 64 * b + 32, r2);
             tmem_load_wait();
+            float v1[32], v2[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v1[i] = __uint_as_float(r1[i]) * alpha;
+              v2[i] = __uint_as_float(r2[i]) * alpha;
+            }
+            unshuffle_columns(v1, p.b_shuffle);
+            unshuffle_columns(v2, p.b_shuffle);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              packed[b][i] = pack_pair<OutT>(__uint_as_float(r1[2 * i]) * alpha,
-                                             __uint_as_float(r1[2 * i + 1]) * alpha);
-              packed[b][16 + i] = pack_pair<OutT>(__uint_as_float(r2[2 * i]) * alpha,
-                                                  __uint_as_float(r2[2 * i + 1]) * alpha);
+              packed[b][i] = pack_pair<OutT>(v1[2 * i], v1[2 * i + 1]);
+              packed[b][16 + i] = pack_pair<OutT>(v2[2 * i], v2[2 * i + 1]);
             }
           }
         }
@@ -509,6 +515,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
         tmem_load_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * alpha;
+        if constexpr (!Cfg::DUAL) unshuffle_columns(v, p.b_shuffle);
         if (c == 7) {
           tc_fence_before_sync();
           __syncwarp();

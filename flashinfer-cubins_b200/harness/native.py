@@ -76,6 +76,11 @@ _PROTOTYPES = {
         [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
          ctypes.c_int, ctypes.c_int, ctypes.POINTER(Config)],
     ),
+    "nvfp4_gemm_plan_create_shuffled": (
+        ctypes.c_int,
+        [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(Config)],
+    ),
     "nvfp4_dual_gemm_plan_create": (
         ctypes.c_int,
         [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
@@ -194,6 +199,16 @@ class Plan:
         handle = _P()
         check(load().nvfp4_gemm_plan_create(
             ctypes.byref(handle), device, out_kind, m, n, k, l, cls._config(**config)))
+        return cls(handle.value)
+
+    @classmethod
+    def dense_shuffled(cls, device: int, out_kind: int, m: int, n: int, k: int, l: int,  # noqa: E741
+                       shuffle_block: int, **config):
+        """Dense GEMM on a B whose rows are in FlashInfer's epilogue-shuffled order."""
+        handle = _P()
+        check(load().nvfp4_gemm_plan_create_shuffled(
+            ctypes.byref(handle), device, out_kind, m, n, k, l, shuffle_block,
+            cls._config(**config)))
         return cls(handle.value)
 
     @classmethod

@@ -38,6 +38,7 @@ from .quantization import (
     fp4_matmul,
     from_blocked_scales,
     make_fp4,
+    shuffle_rows,
     to_blocked_scales,
 )
 
@@ -339,6 +340,57 @@ class NVFP4GEMMBf16(NVFP4GEMM):
         # One BF16 rounding of the same FP32 value on both sides: equal for integer scales,
         # at most one BF16 ulp (2^-8 relative) apart otherwise.
         self.assert_close(ref, impl, rtol=8e-3, atol=1e-3)
+
+
+@register(name="nvfp4_gemm_bf16_shuffled", supported_arches=("sm_100a",))
+class NVFP4GEMMBf16Shuffled(NVFP4GEMMBf16):
+    """``nvfp4_gemm_bf16`` on weights in the layout FlashInfer's ``mm_fp4`` takes with its
+    trtllm backend: the rows of B and of B's scales permuted inside blocks of 32 rows
+    (``quantization.shuffle_rows``; the reference prepares such weights in
+    ``harness/workloads/batched_gemm/trtllm.py:257-288``), BF16 output in logical column
+    order. Inputs ``(a, b_shuffled, sfa, sfb_shuffled, alpha)`` with the shapes and layouts
+    of ``nvfp4_gemm``; n a multiple of the shuffle block. Not a workload of the reference,
+    whose kernels for this layout are the prebuilt ``cubins/gemm/Gemm_Bfloat16_E2m1E2m1_*``."""
+
+    SHUFFLE_BLOCK = 32
+
+    SMOKE = (
+        fp4_case(128, 128, 128, seed=1),
+        fp4_case(200, 160, 96, seed=5, scales="uniform"),
+        fp4_case(300, 288, 384, 3, seed=6, alpha=0.0123),
+        fp4_case(1, 128, 512, seed=12, alpha=0.0123),
+        fp4_case(16, 7168, 2048, seed=13),
+        fp4_case(1000, 256, 512, seed=11, values="restricted", scales="int1_2"),
+    )
+
+    def shuffle_index(self, n: int) -> torch.Tensor:
+        return shuffle_rows(n, self.SHUFFLE_BLOCK)
+
+    def get_inputs(self, case):
+        a, b, sfa, sfb, alpha = super().get_inputs(case)
+        n, cols = b.shape[0], 2 * b.shape[1] // SF_VEC
+        idx = self.shuffle_index(n).to(b.device)
+        logical = from_task_scales(sfb, n, cols)
+        b_physical = b[idx].permute(2, 0, 1).contiguous().permute(1, 2, 0)
+        return a, b_physical, sfa, to_task_scales(logical[idx].contiguous()), alpha
+
+    def get_reference(self, inputs):
+        a, b_physical, sfa, sfb_physical, alpha = inputs
+        n, cols = b_physical.shape[0], 2 * b_physical.shape[1] // SF_VEC
+        idx = self.shuffle_index(n).to(b_physical.device)
+        b = torch.empty_like(b_physical)
+        b[idx] = b_physical
+        physical = from_task_scales(sfb_physical, n, cols)
+        logical = torch.empty_like(physical)
+        logical[idx] = physical
+        return super().get_reference((a, b, sfa, to_task_scales(logical), alpha))
+
+    def _plan(self, problem):
+        return self.plan_for(
+            ("dense_shuffled", self.SHUFFLE_BLOCK, problem),
+            lambda: native.Plan.dense_shuffled(self.device_index(), native.OUT_BF16, *problem,
+                                               self.SHUFFLE_BLOCK),
+        )
 
 
 # FlashInfer's mm_fp4 tests that run this kernel family (cutlass backend, nvfp4, 128x4

@@ -193,6 +193,24 @@ def quantize_nvfp4(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return packed, scales
 
 
+def shuffle_rows(rows: int, block: int) -> torch.Tensor:
+    """Row order of weights prepared for FlashInfer's trtllm-gen ``mm_fp4`` kernels
+    (``nvfp4_quantize(..., do_shuffle=True)``): physical row i of the packed data and of
+    the logical scales holds logical row ``idx[i]``. Inside blocks of ``block`` rows (32,
+    or 16 for kernels whose epilogue tile is not a multiple of 128 rows) logical row
+    ``base + o`` sits at physical row ``base + (o % g) * 8 + o // g``, ``g = block / 8``
+    (the reference's ``harness/workloads/batched_gemm/formats.py:143-161``)."""
+    if block not in (16, 32) or rows % block:
+        raise ValueError(f"rows must be a multiple of the shuffle block (16 or 32), got {rows}, {block}")
+    g = block // 8
+    old = torch.arange(rows)
+    o = old % block
+    physical = old - o + (o % g) * 8 + o // g
+    idx = torch.empty(rows, dtype=torch.long)
+    idx[physical] = old
+    return idx
+
+
 def quantize_nvfp4_native(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """``quantize_nvfp4`` on the GPU by the library's kernel (``nvfp4_quantize``): FP32 or
     BF16 ``(rows, k, l)`` (a view of contiguous ``(l, rows, k)``) on a CUDA device ->

@@ -98,6 +98,18 @@ int nvfp4_device_supported(int device);
 int nvfp4_gemm_plan_create(nvfp4_plan** plan, int device, int out_kind, int m, int n, int k,
                            int l, const nvfp4_config* config);
 
+/* Dense GEMM plan whose B operand is in the layout FlashInfer prepares for its trtllm-gen
+ * `mm_fp4` kernels (`nvfp4_quantize(..., do_shuffle=True)`; the reference's
+ * harness/workloads/batched_gemm/trtllm.py:257-288 with formats.py:143-161): the rows of B,
+ * and the rows of its scales before they are put into the blocked layout, are permuted inside
+ * blocks of `shuffle_block` rows (32 when the producing kernel's epilogue tile is a multiple
+ * of 128 rows, else 16), physical row base + map[o] holding logical row base + o. D comes out
+ * in logical column order: the epilogue undoes the permutation in registers. Launched with
+ * nvfp4_gemm_launch; n must be a multiple of `shuffle_block`; NVFP4_OUT_BF16 is the output
+ * type of that path, FP16 and FP32 work as well. */
+int nvfp4_gemm_plan_create_shuffled(nvfp4_plan** plan, int device, int out_kind, int m, int n,
+                                    int k, int l, int shuffle_block, const nvfp4_config* config);
+
 /* Fused dual GEMM plan: D = half(silu(alpha*A*B1^T) * (alpha*A*B2^T)). The reference
  * runs this as two GEMM launches plus silu_product
  * (harness/workloads/nvfp4_dual_gemm.py:1-30, resources/nvfp4_dual_gemm/task.yml:12-26);

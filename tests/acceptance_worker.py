@@ -51,8 +51,19 @@ def oracle_check(workload, case, inputs, out):
     exact = integer_scaled(case, default)
     if workload.name == "nvfp4_gemm":
         assert_matches_oracle(out[0], oracle_dense(inputs), name, exact and case.params.get("alpha", 1.0) == 1.0)
-    elif workload.name == "nvfp4_gemm_bf16":
-        want = o.round_to_bf16_bits(oracle_dense(inputs, np.float32))
+    elif workload.name in ("nvfp4_gemm_bf16", "nvfp4_gemm_bf16_shuffled"):
+        if workload.name == "nvfp4_gemm_bf16_shuffled":
+            # The oracle puts the rows of B and of its scales back in logical order.
+            a, b, sfa, sfb, alpha = inputs
+            m, half_k, _ = a.shape
+            n, k = b.shape[0], 2 * half_k
+            product = o.shuffled_gemm(
+                storage(a), storage(b), o.from_blocked(blocked_storage(sfa), m, k // 16),
+                o.from_blocked(blocked_storage(sfb), n, k // 16), workload.SHUFFLE_BLOCK,
+                float(alpha.item()), np.float32)
+        else:
+            product = oracle_dense(inputs, np.float32)
+        want = o.round_to_bf16_bits(product)
         got = out[0].permute(2, 0, 1).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
         if integer_scaled(case, "int0_3") and case.params.get("alpha", 1.0) == 1.0:
             assert np.array_equal(got, want), f"{name}: not bit-identical to the oracle"

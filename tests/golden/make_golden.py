@@ -158,6 +158,16 @@ def quantiser():
     )
 
 
+def shuffled_weights():
+    """The epilogue row shuffle of weights prepared for FlashInfer's trtllm-gen kernels
+    (batched_gemm/formats.py:143-161, applied by trtllm.py:257-288: physical row i of the
+    data and of the scales holds logical row idx[i])."""
+    data = {}
+    for rows, tile_m in ((32, 128), (96, 128), (256, 256), (16, 64), (48, 64), (144, 32)):
+        data[f"idx_rows{rows}_tile{tile_m}"] = fmt.shuffle_rows(rows, tile_m).numpy()
+    np.savez_compressed(OUT / "shuffled_weights.npz", **data)
+
+
 def case_inventory():
     """Names, seeds and suites of every case of the five reference workloads, so that
     the mirror's case lists can be compared without the reference."""
@@ -177,6 +187,7 @@ if __name__ == "__main__":
     dual_cases()
     group_cases()
     quantiser()
+    shuffled_weights()
     case_inventory()
     for path in sorted(OUT.glob("*.npz")) + sorted(OUT.glob("*.tsv")):
         print(path.name, path.stat().st_size)

@@ -21,7 +21,8 @@ from oracle import nvfp4_oracle as o
 
 pytestmark = pytest.mark.gpu
 
-WORKLOADS = ("nvfp4_gemm", "nvfp4_gemm_bf16", "nvfp4_dual_gemm_gemm", "nvfp4_dual_gemm",
+WORKLOADS = ("nvfp4_gemm", "nvfp4_gemm_bf16", "nvfp4_gemm_bf16_shuffled", "nvfp4_dual_gemm_gemm",
+             "nvfp4_dual_gemm",
              "nvfp4_group_gemm", "nvfp4_dual_gemm_pack_scales", "nvfp4_dual_gemm_silu_product")
 
 
@@ -396,6 +397,55 @@ def test_abandoned_wait_is_reported_and_the_context_stays_usable(schedule):
         finally:
             other.destroy()
     plan.destroy()
+
+
+@pytest.mark.parametrize("block,out_kind,config", [
+    (32, native.OUT_BF16, {}), (16, native.OUT_F16, {}), (32, native.OUT_F16, {"pair": 1}),
+    (32, native.OUT_F32, {"schedule": 2, "tile_n": 128}), (16, native.OUT_BF16, {"schedule": 3}),
+    (32, native.OUT_F16, {"tile_n": 64, "schedule": 1}),
+])
+def test_shuffled_weights_give_the_logical_result_bit_for_bit(block, out_kind, config):
+    """B and its scales in FlashInfer's epilogue-shuffled row order (blocks of 32 and of 16
+    rows) through every epilogue that undoes the permutation: whole tiles, the stream-K
+    fix-up, the cluster reduction, the 2-CTA kernel. The same plan kind on the logical
+    operands must give the same bits (the products and their order are the same; only
+    the column a value is stored in differs), and the oracle agrees exactly."""
+    from harness import CaseSpec
+    from harness.workloads.nvfp4_gemm import from_task_scales, to_task_scales
+    from harness.workloads.quantization import shuffle_rows
+    workload = get_workload("nvfp4_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    m, n, k = (512, 768, 2048) if config.get("pair") else (200, 416, 4096)
+    dtype = {native.OUT_F16: torch.float16, native.OUT_BF16: torch.bfloat16,
+             native.OUT_F32: torch.float32}[out_kind]
+    a, b, sfa, sfb, alpha = workload.get_inputs(
+        CaseSpec("shuffled", {"m": m, "n": n, "k": k, "l": 1, "alpha": 0.5}, 61))
+    idx = shuffle_rows(n, block).to(dev)
+    b_physical = b[idx].permute(2, 0, 1).contiguous().permute(1, 2, 0)
+    sfb_physical = to_task_scales(from_task_scales(sfb, n, k // 16)[idx].contiguous())
+    results = []
+    for shuffled in (False, True):
+        plan = (native.Plan.dense_shuffled(0, out_kind, m, n, k, 1, block, **config) if shuffled
+                else native.Plan.dense(0, out_kind, m, n, k, 1, **config))
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        d = torch.full((1, m, n), float("nan"), dtype=dtype, device=dev)
+        operands = (a, b_physical, sfa, sfb_physical, alpha) if shuffled else (a, b, sfa, sfb, alpha)
+        plan.launch_dense(*(t.data_ptr() for t in operands), d.data_ptr(), ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        results.append(d)
+        plan.destroy()
+    assert torch.equal(results[0], results[1])
+    if out_kind == native.OUT_F16:
+        want = o.shuffled_gemm(storage(a), storage(b_physical), storage(from_task_scales(sfa, m, k // 16)),
+                               storage(from_task_scales(sfb_physical, n, k // 16)), block, 0.5,
+                               np.float16)
+        assert np.array_equal(results[1].cpu().numpy(), want)
+    with pytest.raises(ValueError):
+        native.Plan.dense_shuffled(0, out_kind, m, n + 8, k, 1, block)
+    with pytest.raises(ValueError):
+        native.Plan.dense_shuffled(0, native.OUT_FP4, m, n, k, 1, block)
 
 
 def test_native_rejects_misaligned_and_wrong_plans():
