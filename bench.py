@@ -34,8 +34,8 @@ operand sets rotate so that together they exceed the 126 MB L2.
   ``torch_path`` inside it is the package's torch restatement of the same arithmetic on all
   cores. A reported baseline, not the target.
 * ``competitors``: library NVFP4 GEMMs on the same GPU, same timing method (cuBLASLt
-  through ``torch._scaled_mm``, cuDNN through FlashInfer ``mm_fp4``), for context; the
-  package never imports them.
+  through ``torch._scaled_mm``, cuDNN and the prebuilt trtllm-gen kernels through FlashInfer
+  ``mm_fp4``), for context; the package never imports them.
 * ``--impl reference``: the reference arm, that CPU path alone on bounded samples.
 
 With N > 1 (launched by torch.distributed.run) the default is strong scaling: the
@@ -688,8 +688,22 @@ def competitors(device, square_iters: int) -> list[dict]:
         return lambda i: flashinfer.mm_fp4(*prepared[i], alpha, torch.float16, outs[i],
                                            backend="cudnn")
 
+    def trtllm_mm(m, n, k, ops):
+        # The prebuilt trtllm-gen kernels (the Gemm_Bfloat16_E2m1E2m1 family the reference
+        # ships as cubins): BF16 output, weights in the shuffled layout. Random bytes time
+        # the same as prepared weights.
+        import flashinfer
+
+        alpha = torch.ones(1, device=device)
+        e4 = torch.float8_e4m3fn
+        prepared = [(a, b.t(), sa.view(e4), sb.view(e4).t()) for a, b, sa, sb in ops]
+        outs = [torch.empty(m, n, dtype=torch.bfloat16, device=device) for _ in ops]
+        return lambda i: flashinfer.mm_fp4(*prepared[i], alpha, torch.bfloat16, outs[i],
+                                           backend="trtllm")
+
     for label, make in (("cublaslt via torch._scaled_mm", scaled_mm),
-                        ("cudnn via flashinfer.mm_fp4", cudnn_mm)):
+                        ("cudnn via flashinfer.mm_fp4", cudnn_mm),
+                        ("trtllm-gen cubins via flashinfer.mm_fp4", trtllm_mm)):
         for name in ("decode", "square"):
             shape = WORKLOADS[name][1]
             m, n, k = shape["m"], shape["n"], shape["k"]
