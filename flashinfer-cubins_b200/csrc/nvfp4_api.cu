@@ -193,6 +193,13 @@ KernelChoice select_kernel(int kind, int out_kind, int tile_n) {
     }
     return KernelChoice{nullptr, 0, 0, 0, 0};
   }
+  if (kind == kGrouped && out_kind == NVFP4_OUT_FP4) {  // grouped dual GEMM, NVFP4 output
+    switch (tile_n) {
+      case 128: return make_choice<GemmConfig<128, true, Fp4Out, true>>();
+      case 256: return make_choice<GemmConfig<256, true, Fp4Out, true>>();
+    }
+    return KernelChoice{nullptr, 0, 0, 0, 0};
+  }
   if (kind == kGrouped) {
     switch (tile_n) {
       case 64: return make_choice<GemmConfig<64, false, __half, true>>();
@@ -241,6 +248,7 @@ struct nvfp4_plan {
   int split = 1;      // cluster size of schedule 3
   bool pair = false;  // 2-CTA kernel: 256 x 256 tiles, one cluster of two CTAs per tile
   int b_shuffle = 0;  // 16 / 32: B's rows are in FlashInfer's epilogue-shuffled order
+  int maps_per_group = 2;  // grouped: tensor maps per group in the workspace (dual: 3)
   double estimate_us = 0.0;  // the time model's figure for the chosen schedule (mainloop + tail)
   int ring_stages = 0;       // pipeline stages the kernel cycles through
   int inbox_offset = -1;     // cluster split-K: byte offset of the peers' inbox, or -1
@@ -418,7 +426,7 @@ void finish_schedule(nvfp4_plan* plan, const nvfp4_config* config) {
   if (plan->kind == kGrouped) {
     off += round_up(plan->problems.size() * sizeof(ProblemDesc), 256);
     plan->off_maps = off;
-    off += round_up(plan->problems.size() * 2 * sizeof(CUtensorMap), 256);
+    off += round_up(plan->problems.size() * plan->maps_per_group * sizeof(CUtensorMap), 256);
   } else {
     plan->off_maps = off;
   }
@@ -532,6 +540,7 @@ void fill_common_params(const nvfp4_plan* plan, KernelParams& kp, void* workspac
   }
   kp.b_streams = streams ? 1 : 0;
   kp.b_shuffle = plan->b_shuffle;
+  kp.maps_per_group = plan->maps_per_group;
 }
 
 // The kernel parameters of a dense or dual launch on the operands named by `key`: taken from
@@ -873,6 +882,62 @@ int nvfp4_group_gemm_plan_create(nvfp4_plan** out, int device, int groups, const
   return 0;
 }
 
+int nvfp4_group_dual_gemm_plan_create_fp4(nvfp4_plan** out, int device, int groups,
+                                          const int* mnk, const nvfp4_config* config) {
+  if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
+  *out = nullptr;
+  if (groups < 1 || mnk == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "expected at least one group");
+  }
+  for (int g = 0; g < groups; ++g) {
+    const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
+    if (m < 1 || n < 1 || k < 1 || k % 32 != 0 || n % 64 != 0) {
+      return fail(NVFP4_E_UNSUPPORTED_SHAPE,
+                  "group %d: unsupported problem m=%d n=%d k=%d (NVFP4 output needs n to be a "
+                  "multiple of 64)", g, m, n, k);
+    }
+  }
+  if (config != nullptr && (config->schedule > 1 || config->pair > 0)) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "NVFP4 output supports the data-parallel schedule only");
+  }
+  int sms = 0;
+  if (int rc = check_device(device, &sms)) return rc;
+  nvfp4_plan* plan = new (std::nothrow) nvfp4_plan();
+  if (plan == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "out of host memory");
+  plan->kind = kGrouped;
+  plan->device = device;
+  plan->out_kind = NVFP4_OUT_FP4;
+  plan->sm_count = sms;
+  plan->maps_per_group = 3;
+  // Two 128-row B tiles side by side (128 output columns per tile) when that still gives
+  // every SM two tiles, else two 64-row tiles.
+  long long wide_tiles = 0;
+  for (int g = 0; g < groups; ++g) {
+    wide_tiles += static_cast<long long>(ceil_div(mnk[3 * g], 128)) * ceil_div(mnk[3 * g + 1], 128);
+  }
+  plan->tile_n = default_tile_n(config, wide_tiles >= 2ll * sms ? 256 : 128);
+  if (plan->tile_n != 128 && plan->tile_n != 256) {
+    delete plan;
+    return fail(NVFP4_E_INVALID_ARGUMENT, "the grouped dual GEMM has tile_n 128 or 256");
+  }
+  plan->out_tile_n = plan->tile_n / 2;
+  plan->problems.resize(groups);
+  for (int g = 0; g < groups; ++g) {
+    fill_problem(&plan->problems[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2], 1,
+                 plan->out_tile_n);
+  }
+  nvfp4_config whole_tiles = {};
+  if (config != nullptr) whole_tiles = *config;
+  whole_tiles.schedule = 1;
+  finish_schedule(plan, &whole_tiles);
+  if (int rc = prepare_kernel(plan)) {
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return 0;
+}
+
 void nvfp4_plan_destroy(nvfp4_plan* plan) { delete plan; }
 
 size_t nvfp4_plan_workspace_bytes(const nvfp4_plan* plan) {
@@ -1169,25 +1234,32 @@ int nvfp4_dual_gemm_launch_fp4(const nvfp4_plan* plan, const void* a, const void
                      stream);
 }
 
-int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const void* const* b,
-                          const void* const* sfa, const void* const* sfb, void* const* d,
-                          void* workspace, void* stream) {
-  if (plan == nullptr || plan->kind != kGrouped) {
-    return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped GEMM plan");
-  }
+}  // extern "C"
+
+namespace {
+
+// Behind nvfp4_group_gemm_bind and nvfp4_group_dual_gemm_bind_fp4 (`b2`, `sfb2`, `sfd` null
+// for the former): checks the pointers, encodes the groups' tensor maps and writes the
+// group table into the workspace.
+int bind_groups(const nvfp4_plan* plan, const void* const* a, const void* const* b,
+                const void* const* b2, const void* const* sfa, const void* const* sfb,
+                const void* const* sfb2, void* const* d, void* const* sfd, void* workspace,
+                void* stream) {
+  const bool dual = plan->maps_per_group == 3;
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || d == nullptr ||
-      workspace == nullptr) {
+      workspace == nullptr || (dual && (b2 == nullptr || sfb2 == nullptr || sfd == nullptr))) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null pointer array");
   }
   if (!aligned(workspace, 256)) return fail(NVFP4_E_MISALIGNED, "workspace must be 256-byte aligned");
   const size_t groups = plan->problems.size();
   for (size_t g = 0; g < groups; ++g) {
     if (a[g] == nullptr || b[g] == nullptr || sfa[g] == nullptr || sfb[g] == nullptr ||
-        d[g] == nullptr) {
+        d[g] == nullptr || (dual && (b2[g] == nullptr || sfb2[g] == nullptr || sfd[g] == nullptr))) {
       return fail(NVFP4_E_INVALID_ARGUMENT, "group %zu: null operand", g);
     }
     if (!aligned(a[g], 16) || !aligned(b[g], 16) || !aligned(sfa[g], 16) ||
-        !aligned(sfb[g], 16) || !aligned(d[g], 16)) {
+        !aligned(sfb[g], 16) || !aligned(d[g], 16) ||
+        (dual && (!aligned(b2[g], 16) || !aligned(sfb2[g], 16) || !aligned(sfd[g], 16)))) {
       return fail(NVFP4_E_MISALIGNED, "group %zu: operands must be 16-byte aligned", g);
     }
   }
@@ -1198,20 +1270,28 @@ int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const vo
   const size_t table_bytes = plan->off_partials - plan->off_table;
   std::vector<uint8_t> staging(table_bytes, 0);
   ProblemDesc* table = reinterpret_cast<ProblemDesc*>(staging.data());
-  CUtensorMap* maps =
-      reinterpret_cast<CUtensorMap*>(staging.data() + (plan->off_maps - plan->off_table));
+  uint8_t* maps = staging.data() + (plan->off_maps - plan->off_table);
+  const int per_group = plan->maps_per_group;
+  // Rows of B per tensor-map box: the tile's rows, or (dual) each B's half of them.
+  const int b_box_rows = dual ? plan->out_tile_n : plan->tile_n;
   for (size_t g = 0; g < groups; ++g) {
     ProblemDesc pd = plan->problems[g];
     pd.sfa = static_cast<const uint8_t*>(sfa[g]);
     pd.sfb = static_cast<const uint8_t*>(sfb[g]);
-    pd.sfb2 = nullptr;
+    pd.sfb2 = dual ? static_cast<const uint8_t*>(sfb2[g]) : nullptr;
     pd.d = d[g];
+    pd.sfd = dual ? static_cast<uint8_t*>(sfd[g]) : nullptr;
     table[g] = pd;
     CUtensorMap tmp;
+    uint8_t* slot = maps + g * per_group * sizeof(CUtensorMap);
     if (int rc = encode_operand_map(&tmp, a[g], pd.m, pd.k, 1, 128)) return rc;
-    std::memcpy(&maps[2 * g], &tmp, sizeof(tmp));
-    if (int rc = encode_operand_map(&tmp, b[g], pd.n, pd.k, 1, plan->tile_n)) return rc;
-    std::memcpy(&maps[2 * g + 1], &tmp, sizeof(tmp));
+    std::memcpy(slot, &tmp, sizeof(tmp));
+    if (int rc = encode_operand_map(&tmp, b[g], pd.n, pd.k, 1, b_box_rows)) return rc;
+    std::memcpy(slot + sizeof(tmp), &tmp, sizeof(tmp));
+    if (dual) {
+      if (int rc = encode_operand_map(&tmp, b2[g], pd.n, pd.k, 1, b_box_rows)) return rc;
+      std::memcpy(slot + 2 * sizeof(tmp), &tmp, sizeof(tmp));
+    }
   }
   // Into the workspace as kernel parameters, 3.5 KB per launch: parameters are copied when a
   // launch is enqueued, so `staging` may go out of scope when this function returns. (An
@@ -1230,6 +1310,30 @@ int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const vo
     plan->group_bound = true;
   }
   return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const void* const* b,
+                          const void* const* sfa, const void* const* sfb, void* const* d,
+                          void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kGrouped || plan->maps_per_group != 2) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped GEMM plan");
+  }
+  return bind_groups(plan, a, b, nullptr, sfa, sfb, nullptr, d, nullptr, workspace, stream);
+}
+
+int nvfp4_group_dual_gemm_bind_fp4(const nvfp4_plan* plan, const void* const* a,
+                                   const void* const* b1, const void* const* b2,
+                                   const void* const* sfa, const void* const* sfb1,
+                                   const void* const* sfb2, void* const* d_packed,
+                                   void* const* d_scales, void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kGrouped || plan->maps_per_group != 3) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped dual GEMM plan");
+  }
+  return bind_groups(plan, a, b1, b2, sfa, sfb1, sfb2, d_packed, d_scales, workspace, stream);
 }
 
 int nvfp4_group_gemm_launch(const nvfp4_plan* plan, void* workspace, void* stream) {

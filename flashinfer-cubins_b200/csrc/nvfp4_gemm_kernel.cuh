@@ -81,7 +81,8 @@ struct alignas(64) KernelParams {
   CUtensorMap map_d;  // 2-CTA kernel, 16-bit output: D as [l][m][n], box 64 columns x 128 rows
   ProblemDesc dense;
   const ProblemDesc* problems;  // grouped: one per group, device memory
-  const CUtensorMap* maps;      // grouped: maps[2g] = A_g, maps[2g + 1] = B_g
+  const CUtensorMap* maps;      // grouped: maps[s g] = A_g, maps[s g + 1] = B_g (dual: B1_g and
+                                // maps[s g + 2] = B2_g), s = maps_per_group
   const float* alpha;           // device scalar, may be null (= 1)
   float* partials;              // stream-K: 2 * grid slots of slot_floats FP32 each
   unsigned int* counters;       // stream-K: one per tile, zero between launches
@@ -99,7 +100,7 @@ struct alignas(64) KernelParams {
                      // pipeline memory is set aside as the cluster inbox)
   int inbox_offset;  // byte offset of that inbox from the pipeline base, or -1: peers may then
                      // write only after this CTA has told them its pipeline memory is free
-  int pad2;
+  int maps_per_group;  // grouped: 2, or 3 for the grouped dual GEMM
 };
 
 struct Segment {
@@ -732,8 +733,10 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       int acquired_prob = -1;
       while (ok && it.next(s)) {
         const ProblemDesc& pd = it.pd;
-        const CUtensorMap* map_a = Cfg::GROUPED ? &p.maps[2 * s.prob] : &p.map_a;
-        const CUtensorMap* map_b = Cfg::GROUPED ? &p.maps[2 * s.prob + 1] : &p.map_b;
+        const CUtensorMap* group_maps = p.maps + p.maps_per_group * s.prob;  // grouped only
+        const CUtensorMap* map_a = Cfg::GROUPED ? group_maps : &p.map_a;
+        const CUtensorMap* map_b = Cfg::GROUPED ? group_maps + 1 : &p.map_b;
+        const CUtensorMap* map_b2 = Cfg::GROUPED ? group_maps + 2 : &p.map_b2;
         if constexpr (Cfg::GROUPED) {
           // A group's tensor maps were copied into the workspace by the host; an earlier
           // plan's maps may have lived at the same addresses.
@@ -741,6 +744,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             if (elect_one()) {
               tensormap_acquire(map_a);
               tensormap_acquire(map_b);
+              if constexpr (Cfg::DUAL) tensormap_acquire(map_b2);
             }
             __syncwarp();
             acquired_prob = s.prob;
@@ -795,7 +799,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             tma_load_3d(a_dst, map_a, bar, kbyte, m0, s.batch, pol_a);
             tma_load_3d(b_dst, map_b, bar, kbyte, n0, s.batch, pol_b);
             if constexpr (Cfg::DUAL) {
-              tma_load_3d(b_dst + Cfg::B_BYTES / 2, &p.map_b2, bar, kbyte, n0, s.batch, pol_b);
+              tma_load_3d(b_dst + Cfg::B_BYTES / 2, map_b2, bar, kbyte, n0, s.batch, pol_b);
             }
           }
           __syncwarp();

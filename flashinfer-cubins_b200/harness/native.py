@@ -113,6 +113,15 @@ _PROTOTYPES = {
         [_P, ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P), ctypes.POINTER(_P),
          ctypes.POINTER(_P), _P, _P],
     ),
+    "nvfp4_group_dual_gemm_plan_create_fp4": (
+        ctypes.c_int,
+        [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+         ctypes.POINTER(Config)],
+    ),
+    "nvfp4_group_dual_gemm_bind_fp4": (
+        ctypes.c_int,
+        [_P] + [ctypes.POINTER(_P)] * 8 + [_P, _P],
+    ),
     "nvfp4_group_gemm_launch": (ctypes.c_int, [_P, _P, _P]),
     "nvfp4_plan_status": (ctypes.c_int, [_P, _P, _P, ctypes.POINTER(ctypes.c_int)]),
     "nvfp4_pack_scales": (
@@ -235,6 +244,16 @@ class Plan:
             ctypes.byref(handle), device, len(flat) // 3, array, cls._config(**config)))
         return cls(handle.value)
 
+    @classmethod
+    def grouped_dual_fp4(cls, device: int, problems, **config):
+        """Grouped fused dual GEMM (gate/up projection) with NVFP4 output."""
+        flat = [int(v) for problem in problems for v in problem]
+        array = (ctypes.c_int * len(flat))(*flat)
+        handle = _P()
+        check(load().nvfp4_group_dual_gemm_plan_create_fp4(
+            ctypes.byref(handle), device, len(flat) // 3, array, cls._config(**config)))
+        return cls(handle.value)
+
     @property
     def handle(self) -> ctypes.c_void_p:
         if self._handle is None:
@@ -289,6 +308,15 @@ class Plan:
 
         check(load().nvfp4_group_gemm_bind(
             self.handle, array(a), array(b), array(sfa), array(sfb), array(d), workspace, stream))
+
+    def bind_dual_groups_fp4(self, a, b1, b2, sfa, sfb1, sfb2, d_packed, d_scales, workspace,
+                             stream) -> None:
+        def array(values):
+            return (_P * len(values))(*values)
+
+        check(load().nvfp4_group_dual_gemm_bind_fp4(
+            self.handle, array(a), array(b1), array(b2), array(sfa), array(sfb1), array(sfb2),
+            array(d_packed), array(d_scales), workspace, stream))
 
     def launch_groups(self, workspace, stream) -> None:
         check(load().nvfp4_group_gemm_launch(self.handle, workspace, stream))

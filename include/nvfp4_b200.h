@@ -210,6 +210,25 @@ int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const vo
                           const void* const* sfa, const void* const* sfb, void* const* d,
                           void* workspace, void* stream);
 
+/* Grouped fused dual GEMM with NVFP4 output, the gate/up projection of a mixture-of-experts
+ * layer in one launch: for every group g, D_g = quantise(silu(A_g B1_g^T) * (A_g B2_g^T)) as
+ * packed E2M1 [m_g][n_g/2] plus blocked UE4M3 scales [ceil(m_g/128)][n_g/64][32][4][4], ready
+ * to be the A operand of the grouped down projection (nvfp4_group_gemm_*). `mnk` as for
+ * nvfp4_group_gemm_plan_create (n_g = rows of each B_g, a multiple of 64); data-parallel
+ * schedule; silu evaluated as in nvfp4_dual_gemm_launch_fp4. Bound with
+ * nvfp4_group_dual_gemm_bind_fp4 (host arrays of `groups` device pointers each) and launched
+ * with nvfp4_group_gemm_launch. The reference has no grouped dual kernel: its grouped cases
+ * are sized as the expert shards of such a layer (harness/workloads/nvfp4_group_gemm.py:751-785)
+ * and its FP8 MoE workload runs the two projections as separate launches
+ * (harness/workloads/moe.py:1-33). */
+int nvfp4_group_dual_gemm_plan_create_fp4(nvfp4_plan** plan, int device, int groups,
+                                          const int* mnk, const nvfp4_config* config);
+int nvfp4_group_dual_gemm_bind_fp4(const nvfp4_plan* plan, const void* const* a,
+                                   const void* const* b1, const void* const* b2,
+                                   const void* const* sfa, const void* const* sfb1,
+                                   const void* const* sfb2, void* const* d_packed,
+                                   void* const* d_scales, void* workspace, void* stream);
+
 /* One launch covering every group, reading the group table that
  * nvfp4_group_gemm_bind wrote into `workspace` (one plan may be bound to several
  * workspaces, one per operand set). Replaces NVFP4GroupGEMM._launch

@@ -2,11 +2,14 @@
 the same computation done stage by stage with the harness's torch quantiser and GEMM
 reference."""
 
+import numpy as np
 import pytest
 import torch
 
-from harness import moe
+from gpu_util import blocked_storage, storage
+from harness import CaseSpec, get_workload, moe, native
 from harness.workloads import quantization as q
+from oracle import nvfp4_oracle as o
 
 pytestmark = pytest.mark.gpu
 
@@ -55,3 +58,59 @@ def test_route_rows_pads_every_expert_to_whole_scale_atoms():
     assert source.numel() == 384
     assert source[:3].tolist() == [0, 5, 6] and source[128].item() == 3
     assert source[256:260].tolist() == [1, 2, 4, 7] and (source[3:128] == -1).all()
+
+
+@pytest.mark.parametrize("tile_n", (128, 256))
+def test_grouped_dual_gemm_with_nvfp4_output(tile_n):
+    """The grouped gate/up kernel: every group's packed E2M1 bytes and blocked scales equal
+    what the dense fused dual GEMM with NVFP4 output gives for that group alone (same
+    arithmetic, same tile order inside a group), and agree with the oracle's quantised dual
+    GEMM up to E2M1 rounding boundaries of the approximate silu. Groups of 1 to 300 rows,
+    partial tiles in M and N, a K tail."""
+    workload = get_workload("nvfp4_dual_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    n, k = 192, 1056
+    groups = []
+    for g, m in enumerate((1, 130, 300, 64)):
+        case = CaseSpec("group", {"m": m, "n": n, "k": k, "l": 1, "alpha": 1.0}, 70 + g)
+        groups.append((m, workload.get_inputs(case)))
+    plan = native.Plan.grouped_dual_fp4(0, [(m, n, k) for m, _ in groups], tile_n=tile_n)
+    ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+    plan.init_workspace(ws.data_ptr(), stream)
+    outs = [(torch.zeros((1, m, n // 2), dtype=torch.uint8, device=dev),
+             torch.zeros((1, -(-m // 128), n // 64, 32, 4, 4), dtype=torch.uint8, device=dev))
+            for m, _ in groups]
+    columns = list(zip(*[[t.data_ptr() for t in inputs[:6]] for _, inputs in groups]))
+    a, b1, b2, sfa, sfb1, sfb2 = columns
+    plan.bind_dual_groups_fp4(a, b1, b2, sfa, sfb1, sfb2, [p.data_ptr() for p, _ in outs],
+                              [s.data_ptr() for _, s in outs], ws.data_ptr(), stream)
+    plan.launch_groups(ws.data_ptr(), stream)
+    assert plan.status(ws.data_ptr(), stream) == 0
+    for (m, inputs), (packed, blocked) in zip(groups, outs):
+        single = native.Plan.dual_fp4(0, m, n, k, 1, tile_n=tile_n)
+        sws = torch.empty(max(single.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        single.init_workspace(sws.data_ptr(), stream)
+        want_packed = torch.zeros_like(packed)
+        want_blocked = torch.zeros_like(blocked)
+        single.launch_dual_fp4(*(t.data_ptr() for t in inputs), want_packed.data_ptr(),
+                               want_blocked.data_ptr(), sws.data_ptr(), stream)
+        assert single.status(sws.data_ptr(), stream) == 0
+        single.destroy()
+        assert torch.equal(packed, want_packed), f"group of {m} rows: packed bytes differ"
+        got_scales = o.from_blocked(blocked.cpu().numpy(), m, n // 16)
+        assert np.array_equal(got_scales, o.from_blocked(want_blocked.cpu().numpy(), m, n // 16))
+        a_t, b1_t, b2_t, sfa_t, s1_t, s2_t, alpha = inputs
+        oracle_packed, oracle_scales = o.dual_gemm_quantized(
+            storage(a_t), storage(b1_t), storage(b2_t),
+            o.from_blocked(blocked_storage(sfa_t), m, k // 16),
+            o.from_blocked(blocked_storage(s1_t), n, k // 16),
+            o.from_blocked(blocked_storage(s2_t), n, k // 16), 1.0)
+        assert (packed.cpu().numpy() != oracle_packed).mean() < 5e-3
+        assert (got_scales != oracle_scales).mean() < 5e-3
+    with pytest.raises(ValueError):
+        native.Plan.grouped_dual_fp4(0, [(16, 96, 64)])      # n not a multiple of 64
+    with pytest.raises(ValueError):
+        native.Plan.grouped_dual_fp4(0, [(16, 128, 64)], schedule=2)
+    plan.destroy()
+
