@@ -1,27 +1,41 @@
-"""A mixture-of-experts feed-forward layer on the NVFP4 kernels of this package: token
-permutation -> quantise -> grouped gate/up GEMM -> silu gate -> quantise -> grouped down GEMM
--> weighted un-permutation. One GPU; every expert's rows form one group of the two grouped
-GEMM launches.
+"""A mixture-of-experts feed-forward layer on the NVFP4 kernels of this package, on one GPU
+or expert-parallel over several.
+
+    tokens -> route -> permute by expert -> quantise
+           -> grouped gate/up dual GEMM, gated and re-quantised in its epilogue   (one launch)
+           -> grouped down GEMM                                                  (one launch)
+           -> weighted un-permutation
 
 The reference sizes its grouped cases as expert-parallel shards of such a layer
 (``harness/workloads/nvfp4_group_gemm.py:751-785`` there, ``MOE_PLAN``) but has no NVFP4 MoE
 layer itself (its FP8 one is ``harness/workloads/moe.py:1-33``); this module is the step
 around the grouped GEMM that a user of that path builds next. ``moe_reference`` is the same
-computation with the harness's torch quantiser and GEMM reference, stage by stage, so the
-two agree up to the summation order inside a GEMM.
+computation with the harness's torch quantiser and GEMM reference, stage by stage.
 
 Layout choices that keep every stage a plain kernel launch on whole buffers:
 
 * Permuted rows are grouped by expert and every expert's block is padded to a multiple of
   128 rows (padding rows are zero). A block then starts on a scale-atom row, so ONE quantiser
   launch over the whole permuted buffer produces packed rows and blocked scales that each
-  group addresses by offset, with no per-expert relayout.
+  group addresses by offset, and the gate/up kernel's NVFP4 output (packed rows + blocked
+  scales) is addressed by the down projection the same way, with no relayout in between.
 * Weights arrive quantised: ``w13`` packed ``[E, 2I, H/2]`` (gate rows then up rows) with
-  blocked scales ``[E, ceil(2I/128), ceil(H/64), 32, 4, 4]``; ``w2`` packed ``[E, H, I/2]``
-  with ``[E, ceil(H/128), ceil(I/64), 32, 4, 4]``.
+  blocked scales ``[E, 2I/128, ceil(H/64), 32, 4, 4]``; ``w2`` packed ``[E, H, I/2]``
+  with ``[E, ceil(H/128), ceil(I/64), 32, 4, 4]``. With ``fused=True`` the intermediate size
+  must be a multiple of 128 (the up projection's scales then start on an atom row).
+* Plans and workspaces are cached per tuple of expert row counts (``MoELayer``): a forward
+  with a routing pattern seen before creates nothing.
+
+Expert parallelism (``moe_forward_ep``): rank r owns experts ``[r E/W, (r+1) E/W)``. Every
+rank routes its own tokens, sends each (token, choice) row to the owner of its expert with
+one all-to-all, runs the layer above on what it received with its local experts, and sends
+the results back with a second all-to-all; the weighted sum happens where the token lives.
+``torch.distributed`` does the exchange (NCCL on GPUs, gloo on CPU for the host-logic test).
 """
 
 from __future__ import annotations
+
+from collections.abc import Callable
 
 import torch
 
@@ -34,19 +48,24 @@ ROW_BLOCK = 128
 def route_rows(topk_ids: torch.Tensor, experts: int) -> tuple[torch.Tensor, list[int], list[int]]:
     """Order the (token, choice) pairs by expert. Returns ``source`` (for every padded
     permuted row the flat pair index ``token * K + choice``, or -1 for padding), the row
-    count per expert and each expert's first padded row."""
+    count per expert and each expert's first padded row. One host read (the counts: the
+    plan's shapes depend on them); everything else stays on the device."""
     flat = topk_ids.reshape(-1)
     order = torch.argsort(flat, stable=True)
-    counts = torch.bincount(flat, minlength=experts).tolist()
-    starts, total = [], 0
-    for count in counts:
-        starts.append(total)
-        total += -(-count // ROW_BLOCK) * ROW_BLOCK
+    counts_t = torch.bincount(flat, minlength=experts)
+    padded_t = (counts_t + ROW_BLOCK - 1) // ROW_BLOCK * ROW_BLOCK
+    starts_t = torch.cumsum(padded_t, 0) - padded_t
+    counts = counts_t.tolist()
+    starts = starts_t.tolist()
+    total = starts[-1] + -(-counts[-1] // ROW_BLOCK) * ROW_BLOCK if experts else 0
     source = torch.full((max(total, ROW_BLOCK),), -1, dtype=torch.int64, device=topk_ids.device)
-    done = 0
-    for expert, count in enumerate(counts):
-        source[starts[expert]:starts[expert] + count] = order[done:done + count]
-        done += count
+    if flat.numel():
+        # Pair i of the sorted order belongs to expert flat[order[i]] and is that expert's
+        # (i - first sorted position of the expert)-th row.
+        sorted_expert = flat[order]
+        first = torch.cumsum(counts_t, 0) - counts_t
+        position = torch.arange(flat.numel(), device=flat.device) - first[sorted_expert]
+        source[starts_t[sorted_expert] + position] = order
     return source, counts, starts
 
 
@@ -66,77 +85,249 @@ def _scatter(y: torch.Tensor, source: torch.Tensor, weights: torch.Tensor, token
     return out
 
 
-def _grouped_gemm(a_packed, a_scales, w_packed, w_scales, counts, starts, n, k, stream):
-    """``D[rows of e] = A[rows of e] @ W[e]^T`` for every expert with rows: one grouped
-    launch. ``a_packed`` ``[R, k/2]``, ``a_scales`` blocked ``[R/128, k/64, 32, 4, 4]``."""
-    device = a_packed.device
-    d = torch.zeros((a_packed.shape[0], n), dtype=torch.float16, device=device)
-    live = [e for e, count in enumerate(counts) if count > 0]
-    if not live:
-        return d
-    atoms_k = -(-k // 64)
-    plan = native.Plan.grouped(device.index or 0, [(counts[e], n, k) for e in live])
-    workspace = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=device)
-    plan.init_workspace(workspace.data_ptr(), stream)
-    plan.bind_groups(
-        [a_packed.data_ptr() + starts[e] * (k // 2) for e in live],
-        [w_packed[e].data_ptr() for e in live],
-        [a_scales.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_k * 512 for e in live],
-        [w_scales[e].data_ptr() for e in live],
-        [d.data_ptr() + starts[e] * n * 2 for e in live],
-        workspace.data_ptr(), stream)
-    plan.launch_groups(workspace.data_ptr(), stream)
-    if plan.status(workspace.data_ptr(), stream) != 0:
-        raise native.NativeError(native.E_DEVICE_TIMEOUT, "grouped GEMM abandoned a wait")
-    plan.destroy()
-    return d
+class MoELayer:
+    """The experts of one layer on one GPU with their cached plans.
 
+    ``w13`` ``[E, 2I, H/2]``, ``w13_scales`` blocked, ``w2`` ``[E, H, I/2]``, ``w2_scales``
+    blocked (see the module docstring). ``fused=True`` (default when I is a multiple of
+    128) runs the gate/up projection as the grouped dual GEMM with NVFP4 output;
+    ``fused=False`` runs one grouped GEMM over both halves of ``w13``, the gate in torch
+    and a second quantiser launch."""
 
-def moe_forward(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
-                w13: torch.Tensor, w13_scales: torch.Tensor, w2: torch.Tensor,
-                w2_scales: torch.Tensor) -> torch.Tensor:
-    """``out[t] = sum_j weight[t, j] * down_e(silu(gate_e(x_t)) * up_e(x_t))`` with
-    ``e = topk_ids[t, j]``; ``x`` ``[T, H]`` FP32/BF16 on a B200, result FP32 ``[T, H]``."""
-    if x.device.type != "cuda" or not native.device_supported(x.device.index or 0):
-        raise RuntimeError(f"sm_100a code cannot run on {x.device}")
-    experts, two_i, half_h = w13.shape
-    hidden, inter = 2 * half_h, two_i // 2
-    if x.shape[1] != hidden or tuple(w2.shape) != (experts, hidden, inter // 2):
-        raise ValueError("weight shapes do not match the activations")
-    if hidden % 64 or inter % 64:
-        raise ValueError("hidden and intermediate sizes must be multiples of 64")
-    tokens, choices = topk_ids.shape
-    with torch.cuda.device(x.device):
-        stream = torch.cuda.current_stream(x.device).cuda_stream
-        source, counts, starts = route_rows(topk_ids, experts)
-        rows = _gather(x, source, choices)
-        a1, s1 = q.quantize_nvfp4_native(rows.unsqueeze(0).permute(1, 2, 0))
-        h = _grouped_gemm(a1.permute(2, 0, 1)[0], s1[0], w13, w13_scales, counts, starts,
-                          two_i, hidden, stream)
-        act = torch.nn.functional.silu(h[:, :inter].float()) * h[:, inter:].float()
-        a2, s2 = q.quantize_nvfp4_native(act.unsqueeze(0).permute(1, 2, 0))
-        y = _grouped_gemm(a2.permute(2, 0, 1)[0], s2[0], w2, w2_scales, counts, starts,
-                          hidden, inter, stream)
+    def __init__(self, w13, w13_scales, w2, w2_scales, fused: bool | None = None):
+        experts, two_i, half_h = w13.shape
+        self.experts, self.hidden, self.inter = experts, 2 * half_h, two_i // 2
+        if tuple(w2.shape) != (experts, self.hidden, self.inter // 2):
+            raise ValueError("w2 does not match w13")
+        if self.hidden % 64 or self.inter % 64:
+            raise ValueError("hidden and intermediate sizes must be multiples of 64")
+        self.fused = self.inter % ROW_BLOCK == 0 if fused is None else fused
+        if self.fused and self.inter % ROW_BLOCK:
+            raise ValueError("the fused gate/up kernel needs an intermediate size that is a "
+                             "multiple of 128")
+        self.w13, self.w13_scales, self.w2, self.w2_scales = w13, w13_scales, w2, w2_scales
+        self.device = w13.device
+        if self.device.type != "cuda" or not native.device_supported(self.device.index or 0):
+            raise RuntimeError(f"sm_100a code cannot run on {self.device}")
+        self._plans: dict[tuple, tuple] = {}
+
+    def close(self) -> None:
+        if self._plans:
+            torch.cuda.synchronize(self.device)
+        for up_plan, _, down_plan, _ in self._plans.values():
+            up_plan.destroy()
+            down_plan.destroy()
+        self._plans.clear()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _entry(self, counts: tuple[int, ...], stream: int):
+        """(gate/up plan, its workspace, down plan, its workspace) for this routing pattern."""
+        entry = self._plans.get((counts, stream))
+        if entry is None:
+            live = [e for e, count in enumerate(counts) if count > 0]
+            index = self.device.index or 0
+            if self.fused:
+                up_plan = native.Plan.grouped_dual_fp4(
+                    index, [(counts[e], self.inter, self.hidden) for e in live])
+            else:
+                up_plan = native.Plan.grouped(
+                    index, [(counts[e], 2 * self.inter, self.hidden) for e in live])
+            down_plan = native.Plan.grouped(
+                index, [(counts[e], self.hidden, self.inter) for e in live])
+            workspaces = []
+            for plan in (up_plan, down_plan):
+                ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8,
+                                 device=self.device)
+                plan.init_workspace(ws.data_ptr(), stream)
+                workspaces.append(ws)
+            entry = (up_plan, workspaces[0], down_plan, workspaces[1])
+            self._plans[(counts, stream)] = entry
+        return entry
+
+    def forward_rows(self, rows: torch.Tensor, counts: list[int], starts: list[int]) -> torch.Tensor:
+        """The experts applied to permuted rows: ``rows`` FP32 ``[R, H]`` grouped by expert
+        (expert e at ``starts[e]``, ``counts[e]`` rows, blocks padded to 128 rows). Returns
+        FP16 ``[R, H]`` (padding rows zero)."""
+        device, hidden, inter = self.device, self.hidden, self.inter
+        total = rows.shape[0]
+        y = torch.zeros((total, hidden), dtype=torch.float16, device=device)
+        live = [e for e, count in enumerate(counts) if count > 0]
+        if not live:
+            return y
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            up_plan, up_ws, down_plan, down_ws = self._entry(tuple(counts), stream)
+            a1, s1 = q.quantize_nvfp4_native(rows.unsqueeze(0).permute(1, 2, 0))
+            a1, s1 = a1.permute(2, 0, 1)[0], s1[0]
+            atoms_h, atoms_i = -(-hidden // 64), -(-inter // 64)
+            a_ptrs = [a1.data_ptr() + starts[e] * (hidden // 2) for e in live]
+            sa_ptrs = [s1.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_h * 512 for e in live]
+            if self.fused:
+                # Gate/up straight to the down projection's A operand.
+                a2 = torch.zeros((total, inter // 2), dtype=torch.uint8, device=device)
+                s2 = torch.zeros((total // ROW_BLOCK, atoms_i, 32, 4, 4), dtype=torch.uint8,
+                                 device=device)
+                up_plan.bind_dual_groups_fp4(
+                    a_ptrs,
+                    [self.w13[e].data_ptr() for e in live],
+                    [self.w13[e].data_ptr() + inter * (hidden // 2) for e in live],
+                    sa_ptrs,
+                    [self.w13_scales[e].data_ptr() for e in live],
+                    [self.w13_scales[e].data_ptr() + (inter // ROW_BLOCK) * atoms_h * 512
+                     for e in live],
+                    [a2.data_ptr() + starts[e] * (inter // 2) for e in live],
+                    [s2.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_i * 512 for e in live],
+                    up_ws.data_ptr(), stream)
+                up_plan.launch_groups(up_ws.data_ptr(), stream)
+            else:
+                h = torch.zeros((total, 2 * inter), dtype=torch.float16, device=device)
+                up_plan.bind_groups(
+                    a_ptrs, [self.w13[e].data_ptr() for e in live], sa_ptrs,
+                    [self.w13_scales[e].data_ptr() for e in live],
+                    [h.data_ptr() + starts[e] * 2 * inter * 2 for e in live],
+                    up_ws.data_ptr(), stream)
+                up_plan.launch_groups(up_ws.data_ptr(), stream)
+                act = torch.nn.functional.silu(h[:, :inter].float()) * h[:, inter:].float()
+                a2, s2 = q.quantize_nvfp4_native(act.unsqueeze(0).permute(1, 2, 0))
+                a2, s2 = a2.permute(2, 0, 1)[0], s2[0]
+            down_plan.bind_groups(
+                [a2.data_ptr() + starts[e] * (inter // 2) for e in live],
+                [self.w2[e].data_ptr() for e in live],
+                [s2.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_i * 512 for e in live],
+                [self.w2_scales[e].data_ptr() for e in live],
+                [y.data_ptr() + starts[e] * hidden * 2 for e in live],
+                down_ws.data_ptr(), stream)
+            down_plan.launch_groups(down_ws.data_ptr(), stream)
+            self._keepalive = (a1, s1, a2, s2)  # until the launches have run
+        return y
+
+    def check_status(self) -> None:
+        """Synchronise and raise ``native.NativeError`` if a kernel abandoned a wait."""
+        for (_, stream), (up_plan, up_ws, down_plan, down_ws) in self._plans.items():
+            up_plan.status(up_ws.data_ptr(), stream)
+            down_plan.status(down_ws.data_ptr(), stream)
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """``out[t] = sum_j weight[t, j] * down_e(silu(gate_e(x_t)) * up_e(x_t))`` with
+        ``e = topk_ids[t, j]``; ``x`` ``[T, H]`` FP32/BF16, result FP32 ``[T, H]``."""
+        if x.shape[1] != self.hidden:
+            raise ValueError("activations do not match the weights")
+        tokens, choices = topk_ids.shape
+        source, counts, starts = route_rows(topk_ids, self.experts)
+        y = self.forward_rows(_gather(x, source, choices), counts, starts)
         return _scatter(y, source, topk_weights, tokens)
 
 
-def moe_reference(x, topk_ids, topk_weights, w13, w13_scales, w2, w2_scales) -> torch.Tensor:
-    """The same layer with the torch quantiser and the torch GEMM reference, expert by
-    expert (any device). Scales are the logical ``[E, rows, k/16]`` tensors here."""
-    experts, two_i, half_h = w13.shape
-    hidden, inter = 2 * half_h, two_i // 2
-    tokens, choices = topk_ids.shape
+def moe_forward(x, topk_ids, topk_weights, w13, w13_scales, w2, w2_scales,
+                fused: bool | None = None) -> torch.Tensor:
+    """One forward of a throw-away ``MoELayer`` (keep the layer to keep its plans)."""
+    if x.device.type != "cuda" or not native.device_supported(x.device.index or 0):
+        raise RuntimeError(f"sm_100a code cannot run on {x.device}")
+    layer = MoELayer(w13, w13_scales, w2, w2_scales, fused)
+    try:
+        out = layer.forward(x, topk_ids, topk_weights)
+        layer.check_status()
+        return out
+    finally:
+        layer.close()
+
+
+def expert_reference(rows: torch.Tensor, w13_e, w13_scales_e, w2_e, w2_scales_e,
+                     fused: bool = True) -> torch.Tensor:
+    """One expert applied to FP32 ``rows`` with the torch quantiser and GEMM reference (any
+    device): packed ``w13_e`` ``[2I, H/2]`` / ``w2_e`` ``[H, I/2]`` with logical scales
+    ``[rows, k/16]``. ``fused`` follows the fused kernel (the gate is applied to the FP32
+    products); otherwise both products are rounded to FP16 first, as the unfused path does.
+    Returns FP16 ``[rows, H]``."""
+    inter = w13_e.shape[0] // 2
+    a1, s1 = q.quantize_nvfp4(rows.float().unsqueeze(0).permute(1, 2, 0))
+    h = q.fp4_matmul(a1, w13_e[None].permute(1, 2, 0), s1, w13_scales_e[None].permute(1, 2, 0),
+                     out_dtype=torch.float32 if fused else torch.float16)[:, :, 0]
+    act = torch.nn.functional.silu(h[:, :inter].float()) * h[:, inter:].float()
+    a2, s2 = q.quantize_nvfp4(act.unsqueeze(0).permute(1, 2, 0))
+    return q.fp4_matmul(a2, w2_e[None].permute(1, 2, 0), s2, w2_scales_e[None].permute(1, 2, 0),
+                        out_dtype=torch.float16)[:, :, 0]
+
+
+def moe_reference(x, topk_ids, topk_weights, w13, w13_scales, w2, w2_scales,
+                  fused: bool = False) -> torch.Tensor:
+    """The same layer expert by expert with ``expert_reference`` (any device). Scales are
+    the logical ``[E, rows, k/16]`` tensors here."""
+    experts, hidden = w13.shape[0], 2 * w13.shape[2]
+    tokens, _ = topk_ids.shape
     out = torch.zeros((tokens, hidden), dtype=torch.float32, device=x.device)
     for e in range(experts):
         token, choice = torch.nonzero(topk_ids == e, as_tuple=True)
         if token.numel() == 0:
             continue
-        a1, s1 = q.quantize_nvfp4(x[token].float().unsqueeze(0).permute(1, 2, 0))
-        h = q.fp4_matmul(a1, w13[e:e + 1].permute(1, 2, 0), s1, w13_scales[e:e + 1].permute(1, 2, 0),
-                         out_dtype=torch.float16)[:, :, 0]
-        act = torch.nn.functional.silu(h[:, :inter].float()) * h[:, inter:].float()
-        a2, s2 = q.quantize_nvfp4(act.unsqueeze(0).permute(1, 2, 0))
-        y = q.fp4_matmul(a2, w2[e:e + 1].permute(1, 2, 0), s2, w2_scales[e:e + 1].permute(1, 2, 0),
-                         out_dtype=torch.float16)[:, :, 0]
+        y = expert_reference(x[token], w13[e], w13_scales[e], w2[e], w2_scales[e], fused)
         out.index_add_(0, token, y.float() * topk_weights[token, choice].float()[:, None])
     return out
+
+
+# -- expert parallelism -------------------------------------------------------------------
+
+
+def expert_owner(expert: torch.Tensor, experts: int, world: int) -> torch.Tensor:
+    """Rank that owns each expert: contiguous blocks of ``ceil(E / W)`` experts."""
+    per_rank = -(-experts // world)
+    return expert // per_rank
+
+
+def moe_forward_ep(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                   experts: int,
+                   local_experts: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+                   group=None) -> torch.Tensor:
+    """Expert-parallel forward of this rank's tokens. ``experts`` is the global expert
+    count; ``local_experts(rows, local_ids)`` applies this rank's experts to FP32 ``rows``
+    ``[R, H]`` whose expert (numbered from 0 within the rank) is ``local_ids[R]`` and
+    returns ``[R, H]`` (on a GPU: ``ep_local_experts(layer)`` below; the CPU test passes the
+    torch reference). Two ``all_to_all_single`` exchanges carry the rows out and back; one
+    small one carries the row counts. Returns FP32 ``[T, H]``."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    tokens, choices = topk_ids.shape
+    hidden = x.shape[1]
+    per_rank = -(-experts // world)
+    flat = topk_ids.reshape(-1)
+    owner = expert_owner(flat, experts, world)
+    order = torch.argsort(owner, stable=True)          # pairs grouped by destination rank
+    send_counts = torch.bincount(owner, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    send_split, recv_split = send_counts.tolist(), recv_counts.tolist()
+    send_rows = x.float()[order // choices].contiguous()
+    send_ids = (flat[order] % per_rank).contiguous()
+    recv_rows = torch.empty((sum(recv_split), hidden), dtype=torch.float32, device=x.device)
+    recv_ids = torch.empty((sum(recv_split),), dtype=send_ids.dtype, device=x.device)
+    dist.all_to_all_single(recv_rows, send_rows, recv_split, send_split, group=group)
+    dist.all_to_all_single(recv_ids, send_ids, recv_split, send_split, group=group)
+    done = local_experts(recv_rows, recv_ids).float().contiguous()
+    back = torch.empty((sum(send_split), hidden), dtype=torch.float32, device=x.device)
+    dist.all_to_all_single(back, done, send_split, recv_split, group=group)
+    out = torch.zeros((tokens, hidden), dtype=torch.float32, device=x.device)
+    out.index_add_(0, order // choices, back * topk_weights.reshape(-1)[order].float()[:, None])
+    return out
+
+
+def ep_local_experts(layer: MoELayer) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
+    """``local_experts`` for ``moe_forward_ep`` on a GPU: the rank's ``MoELayer`` applied to
+    the received rows (each row has exactly one expert, weight 1)."""
+
+    def apply(rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
+        if rows.shape[0] == 0:
+            return rows
+        source, counts, starts = route_rows(local_ids[:, None], layer.experts)
+        y = layer.forward_rows(_gather(rows, source, 1), counts, starts)
+        out = torch.zeros_like(rows)
+        valid = source >= 0
+        out[source[valid]] = y[valid].float()
+        return out
+
+    return apply
