@@ -36,6 +36,10 @@ operand sets rotate so that together they exceed the 126 MB L2.
 * ``competitors``: library NVFP4 GEMMs on the same GPU, same timing method (cuBLASLt
   through ``torch._scaled_mm``, cuDNN and the prebuilt trtllm-gen kernels through FlashInfer
   ``mm_fp4``), for context; the package never imports them.
+* ``next_rows``: the rows beside the GEMM path, validated and timed the same way: the
+  activation quantiser, the GEMMs whose epilogue writes NVFP4 (dense and gate/up), BF16
+  output on weights in the trtllm-gen row order, and one rank's share of a DeepSeek-V3 MoE
+  layer on the grouped kernels.
 * ``--impl reference``: the reference arm, that CPU path alone on bounded samples.
 
 With N > 1 (launched by torch.distributed.run) the default is strong scaling: the
@@ -634,6 +638,26 @@ def measure_config(name, dist_info, device, scaling, steps, warmup, issue_tflops
         measured.close()
 
 
+def replay_us(fn, sets: int, iters: int) -> float:
+    """Microseconds per call of ``fn(i % sets)`` launched ``iters`` times back to back from a
+    CUDA graph between two CUDA events (five warm-up calls and one warm replay first)."""
+    for i in range(5):
+        fn(i % sets)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(iters):
+            fn(i % sets)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / iters
+
+
 def competitors(device, square_iters: int) -> list[dict]:
     """Library NVFP4 GEMMs on this GPU, same event method (graph replay over rotating operand
     sets): cuBLASLt through torch._scaled_mm (the call of the task's own reference,
@@ -655,22 +679,7 @@ def competitors(device, square_iters: int) -> list[dict]:
             out.append((a, b, sa, sb))
         return out
 
-    def timed(fn, sets, iters):
-        for i in range(5):
-            fn(i % sets)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for i in range(iters):
-                fn(i % sets)
-        graph.replay()
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        graph.replay()
-        stop.record()
-        torch.cuda.synchronize()
-        return start.elapsed_time(stop) * 1e3 / iters
+    timed = replay_us
 
     def scaled_mm(m, n, k, ops):
         f4, e4 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
@@ -720,6 +729,305 @@ def competitors(device, square_iters: int) -> list[dict]:
     return results
 
 
+def _hbm_line(byts: float, us: float) -> dict:
+    peak, peak_kind = measured_hbm_peak()
+    achieved = byts / (us * 1e-6) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "traffic": None,
+            "peak_source": f"{peak_kind} HBM copy bandwidth",
+            "algorithmic_bytes_per_launch": byts}
+
+
+def _tensor_line(flops: float, us: float) -> dict:
+    tf = flops / (us * 1e-6) / 1e12
+    return {"bound": "tensor", "achieved": tf, "peak": NOMINAL_FP4_TFLOPS, "unit": "TFLOP/s",
+            "frac": tf / NOMINAL_FP4_TFLOPS, "traffic": None,
+            "peak_source": "nominal dense FP4 (9 PFLOP/s per GPU)",
+            "algorithmic_flops_per_launch": flops}
+
+
+class _NativePlan:
+    """A plan with its workspace on the current stream, for the rows that go through the
+    C ABI directly (``harness/native.py``)."""
+
+    def __init__(self, plan, device):
+        self.plan, self.device = plan, device
+        self.workspace = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8,
+                                     device=device)
+        plan.init_workspace(self.workspace.data_ptr(), self.stream)
+        torch.cuda.synchronize(device)
+
+    @property
+    def stream(self) -> int:
+        """The stream current at the time of the call (a capturing stream inside a graph)."""
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def status(self) -> int:
+        return self.plan.status(self.workspace.data_ptr(), self.stream)
+
+    def close(self):
+        torch.cuda.synchronize()
+        self.plan.destroy()
+
+
+def row_quantiser(device) -> dict:
+    """The activation quantiser (``nvfp4_quantize``): BF16 [8192, 8192] to packed E2M1 and
+    blocked scales, against the torch quantiser on the first 1024 rows."""
+    from harness.workloads import quantization as q
+
+    rows, k, sets = 8192, 8192, 2
+    xs = [torch.randn((1, rows, k), generator=torch.Generator().manual_seed(70 + i))
+          .to(device=device, dtype=torch.bfloat16).permute(1, 2, 0) for i in range(sets)]
+    packed, blocked = q.quantize_nvfp4_native(xs[0])
+    want_packed, want_scales = q.quantize_nvfp4(xs[0][:1024].float())
+    ok = (torch.equal(packed[:1024], want_packed) and
+          torch.equal(blocked[:, :8].view(torch.uint8),
+                      q.to_blocked_scales(want_scales).view(torch.uint8)))
+    us = replay_us(lambda i: q.quantize_nvfp4_native(xs[i]), sets, 40)
+    byts = rows * k * 2 + rows * k // 2 + rows * k // 16
+    return {"row": "f1 activation quantiser", "entry": "nvfp4_quantize",
+            "workload": f"bf16 [{rows}, {k}] -> packed e2m1 + blocked ue4m3 scales",
+            "us_per_call": us, "validated": bool(ok), "roofline": _hbm_line(byts, us),
+            "note": "timed with its two output allocations from torch's caching allocator"}
+
+
+def row_fp4_output(device) -> list[dict]:
+    """GEMMs whose epilogue quantises D to NVFP4: the square shape and the dual shape. The
+    dense result must equal, byte for byte, the quantiser kernel applied to the FP32 output of
+    the same plan family; the dual result (approximate silu) is checked after dequantisation
+    against the FP16-output kernel."""
+    from harness import native
+    from harness.workloads import quantization as q
+
+    rows_out = []
+    index = device.index or 0
+    # Dense, 8192^3.
+    kind, shape = WORKLOADS["square"]
+    m, n, k = shape["m"], shape["n"], shape["k"]
+    sets = 3
+    operands = [make_operand_set(kind, shape, 40 + i, device) for i in range(sets)]
+    fp4 = _NativePlan(native.Plan.dense(index, native.OUT_FP4, m, n, k, 1), device)
+    f32 = _NativePlan(native.Plan.dense(index, native.OUT_F32, m, n, k, 1), device)
+    packed = [torch.empty((1, m, n // 2), dtype=torch.uint8, device=device) for _ in range(sets)]
+    scales = [torch.zeros((1, -(-m // 128), n // 64, 32, 4, 4), dtype=torch.uint8, device=device)
+              for _ in range(sets)]
+
+    def dense(i):
+        a, b, sfa, sfb, alpha = operands[i][:5]
+        fp4.plan.launch_dense_fp4(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                                  alpha.data_ptr(), packed[i].data_ptr(), scales[i].data_ptr(),
+                                  fp4.workspace.data_ptr(), fp4.stream)
+
+    dense(0)
+    a, b, sfa, sfb, alpha = operands[0][:5]
+    product = torch.empty((1, m, n), dtype=torch.float32, device=device)
+    f32.plan.launch_dense(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                          alpha.data_ptr(), product.data_ptr(), f32.workspace.data_ptr(),
+                          f32.stream)
+    want_packed, want_scales = q.quantize_nvfp4_native(product.permute(1, 2, 0))
+    ok = (fp4.status() == 0 and f32.status() == 0 and
+          torch.equal(packed[0], want_packed.permute(2, 0, 1)) and
+          torch.equal(scales[0], want_scales.view(torch.uint8)))
+    del product, want_packed, want_scales
+    us = replay_us(dense, sets, 30)
+    rows_out.append({"row": "f2 NVFP4-output epilogue, dense", "entry": "nvfp4_gemm_launch_fp4",
+                     "workload": f"square {shape}, D packed e2m1 + blocked scales",
+                     "us_per_call": us, "validated": bool(ok), "plan": fp4.plan.info(),
+                     "roofline": _tensor_line(2.0 * m * n * k, us)})
+    fp4.close()
+    f32.close()
+    del operands, packed, scales
+    torch.cuda.empty_cache()
+
+    # Dual (gate/up), the dual workload's shape.
+    kind, shape = WORKLOADS["dual"]
+    m, n, k = shape["m"], shape["n"], shape["k"]
+    sets = 4
+    # alpha = 1/32 keeps silu(h1) * h2 of N(0,1) operands inside FP16, which the check below
+    # compares with.
+    alpha = torch.full((1,), 1.0 / 32.0, device=device)
+    operands = [make_operand_set(kind, shape, 50 + i, device)[:6] + (alpha,) for i in range(sets)]
+    fp4 = _NativePlan(native.Plan.dual_fp4(index, m, n, k, 1), device)
+    f16 = _NativePlan(native.Plan.dual(index, m, n, k, 1), device)
+    packed = [torch.zeros((1, m, n // 2), dtype=torch.uint8, device=device) for _ in range(sets)]
+    scales = [torch.zeros((1, -(-m // 128), n // 64, 32, 4, 4), dtype=torch.uint8, device=device)
+              for _ in range(sets)]
+
+    def dual(i):
+        fp4.plan.launch_dual_fp4(*(t.data_ptr() for t in operands[i]), packed[i].data_ptr(),
+                                 scales[i].data_ptr(), fp4.workspace.data_ptr(), fp4.stream)
+
+    dual(0)
+    half = torch.empty((1, m, n), dtype=torch.float16, device=device)
+    f16.plan.launch_dual(*(t.data_ptr() for t in operands[0]), half.data_ptr(),
+                         f16.workspace.data_ptr(), f16.stream)
+    ok = fp4.status() == 0 and f16.status() == 0
+    logical = q.from_blocked_scales(scales[0].view(torch.float8_e4m3fn), m, n // 16)
+    got = q.dequant_fp4(packed[0].permute(1, 2, 0), logical)[..., 0]
+    want = half[0].float()
+    # One E2M1 step at a block's scale is amax/6 of the block; well inside it on average.
+    error = (got - want).norm().item() / max(want.norm().item(), 1e-30)
+    ok = ok and error < 0.12
+    us = replay_us(dual, sets, 200)
+    _, byts = algorithmic_work(kind, shape)
+    byts += -2.0 * m * n + m * n / 2 + m * n / 16
+    rows_out.append({"row": "f2 NVFP4-output epilogue, dual (gate/up)",
+                     "entry": "nvfp4_dual_gemm_launch_fp4",
+                     "workload": f"dual {shape}, D packed e2m1 + blocked scales",
+                     "us_per_call": us, "validated": bool(ok),
+                     "relative_error_to_fp16_output": error, "plan": fp4.plan.info(),
+                     "roofline": _hbm_line(byts, us)})
+    fp4.close()
+    f16.close()
+    del operands, packed, scales
+    torch.cuda.empty_cache()
+    return rows_out
+
+
+def row_shuffled(device) -> dict:
+    """BF16 output on weights in the trtllm row order, decode shape, through the operator
+    API (workload ``nvfp4_gemm_bf16_shuffled``) against its torch reference."""
+    from harness import get_workload
+
+    kind, shape = WORKLOADS["decode"]
+    sets = 4
+    workload = get_workload("nvfp4_gemm_bf16_shuffled").from_arch("sm_100a", device=device)
+    operands = [make_operand_set(kind, shape, 60 + i, device) for i in range(sets)]
+    prepared = [workload.prepare(inputs) for inputs in operands]
+    outputs = prepared[0][0]()
+    torch.cuda.synchronize()
+    ok = True
+    try:
+        workload.validate(workload.get_reference(operands[0]), outputs)
+        workload.check_status()
+    except AssertionError:
+        ok = False
+    us = replay_us(lambda i: prepared[i][0](), sets, 200)
+    _, byts = algorithmic_work(kind, shape)
+    info = workload.plan_info(operands[0])
+    workload.close()
+    return {"row": "f3 BF16 output on shuffled weights",
+            "entry": "nvfp4_gemm_plan_create_shuffled + nvfp4_gemm_launch",
+            "workload": f"decode {shape}, B rows in the trtllm-gen order (block 32), bf16 out",
+            "us_per_call": us, "validated": ok, "plan": info, "roofline": _hbm_line(byts, us)}
+
+
+def row_moe(device) -> list[dict]:
+    """One rank's share of a DeepSeek-V3 MoE layer under 8-way expert parallelism (32 local
+    experts, hidden 7168, intermediate 2048; the reference sizes its grouped cases the same
+    way, harness/workloads/nvfp4_group_gemm.py:751-785 there): the rows routed to this rank at
+    1,024 and 16,384 tokens, per-expert counts seeded log-normal. ``layer_us`` is
+    ``MoELayer.forward_rows`` (quantiser and two grouped launches on the pattern's bound
+    buffers); ``kernels_us`` the two grouped launches alone replayed from a graph. The busiest
+    expert's rows are checked against the stage-by-stage torch reference."""
+    from harness import moe
+    from harness.models import MODELS
+    from harness.throughput import skewed_lengths
+    from harness.workloads import quantization as q
+
+    spec = MODELS["deepseek_v3"]
+    local = 32
+    shapes = spec.linear_shapes()
+    (two_i, hidden), (_, inter) = shapes["expert_gate_up"], shapes["expert_down"]
+    gen = torch.Generator(device=device).manual_seed(90)
+
+    def weights(rows, k):
+        packed = torch.empty((local, rows, k // 2), dtype=torch.uint8, device=device)
+        blocked = torch.empty((local, -(-rows // 128), -(-k // 64), 32, 4, 4),
+                              dtype=torch.float8_e4m3fn, device=device)
+        for e in range(local):
+            w = torch.randn((1, rows, k), device=device, generator=gen) * 0.05
+            p, s = q.quantize_nvfp4_native(w.permute(1, 2, 0))
+            packed[e], blocked[e] = p[..., 0], s[0]
+        return packed, blocked
+
+    w13, w13_scales = weights(two_i, hidden)
+    w2, w2_scales = weights(hidden, inter)
+    layer = moe.MoELayer(w13, w13_scales, w2, w2_scales, fused=True)
+    out = []
+    for tokens in (1024, 16384):
+        routed = tokens * spec.top_k * local // spec.experts
+        counts = list(skewed_lengths(routed, local, seed=tokens, minimum=0))
+        starts, total = [], 0
+        for count in counts:
+            starts.append(total)
+            total += -(-count // 128) * 128
+        rows = torch.zeros((max(total, 128), hidden), dtype=torch.float32, device=device)
+        for e, count in enumerate(counts):
+            rows[starts[e]:starts[e] + count] = torch.randn((count, hidden), device=device,
+                                                            generator=gen)
+        y = layer.forward_rows(rows, counts, starts)
+        layer.check_status()
+        probe = max(range(local), key=lambda e: counts[e])
+        span = slice(starts[probe], starts[probe] + counts[probe])
+        want = moe.expert_reference(
+            rows[span], w13[probe],
+            q.from_blocked_scales(w13_scales[probe][None], two_i, hidden // 16)[..., 0],
+            w2[probe], q.from_blocked_scales(w2_scales[probe][None], hidden, inter // 16)[..., 0],
+            fused=True)
+        error = ((y[span].float() - want.float()).norm() / want.float().norm()).item()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            y = layer.forward_rows(rows, counts, starts)
+        torch.cuda.synchronize()
+        repeats = 10
+        start.record()
+        for _ in range(repeats):
+            y = layer.forward_rows(rows, counts, starts)
+        stop.record()
+        torch.cuda.synchronize()
+        layer_us = start.elapsed_time(stop) * 1e3 / repeats
+        pattern = layer._entry(tuple(counts), torch.cuda.current_stream(device).cuda_stream)
+
+        def kernels(_):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            pattern.up_plan.launch_groups(pattern.up_ws.data_ptr(), stream)
+            pattern.down_plan.launch_groups(pattern.down_ws.data_ptr(), stream)
+
+        kernels_us = replay_us(kernels, 1, 20)
+        layer.check_status()
+        del y
+        live = sum(1 for count in counts if count)
+        flops = 2.0 * routed * (two_i * hidden + hidden * inter)
+        weight_bytes = live * (two_i * hidden + hidden * inter) * (0.5 + 1.0 / 16)
+        row_bytes = routed * (hidden * (0.5 + 1.0 / 16) + 2 * inter * (0.5 + 1.0 / 16)
+                              + 2.0 * hidden)
+        byts = weight_bytes + row_bytes
+        line = (_tensor_line(flops, kernels_us) if flops / 9e15 > byts / 6.5e12
+                else _hbm_line(byts, kernels_us))
+        out.append({"row": "f4 MoE layer (expert-parallel shard)",
+                    "entry": "nvfp4_group_dual_gemm_bind_fp4 + nvfp4_group_gemm_bind + "
+                             "nvfp4_group_gemm_launch x2 + nvfp4_quantize",
+                    "workload": f"deepseek_v3 experts, {local} local of {spec.experts}, "
+                                f"{tokens} tokens -> {routed} routed rows, {live} live experts, "
+                                f"hidden {hidden}, intermediate {inter}",
+                    "layer_us": layer_us, "kernels_us": kernels_us,
+                    "us_per_call": kernels_us, "tflops": flops / kernels_us / 1e6,
+                    "validated": bool(error < 1e-2), "relative_error_of_probed_expert": error,
+                    "roofline": line,
+                    "note": "weights of one operand set (791 MB) exceed L2; kernels_us replays "
+                            "the bound launches on the same operands"})
+    layer.close()
+    del w13, w13_scales, w2, w2_scales
+    torch.cuda.empty_cache()
+    return out
+
+
+def next_rows(device) -> list[dict]:
+    """The rows beside the GEMM path (quantiser, NVFP4-output epilogues, shuffled weights, the
+    MoE layer), each validated and timed like ``configs``. A row that fails says so and the
+    others still run."""
+    rows = []
+    for make in (row_quantiser, row_fp4_output, row_shuffled, row_moe):
+        try:
+            made = make(device)
+            rows += made if isinstance(made, list) else [made]
+        except Exception as error:  # reported, not hidden
+            rows.append({"row": make.__name__, "failed": repr(error)[:400]})
+        torch.cuda.empty_cache()
+    return rows
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -731,6 +1039,8 @@ def main() -> None:
     parser.add_argument("--no-graph", action="store_true")
     parser.add_argument("--no-configs", action="store_true",
                         help="headline workload only (no configs array, no competitors)")
+    parser.add_argument("--next-rows-only", action="store_true",
+                        help="measure only the rows beside the GEMM path (one GPU)")
     parser.add_argument("--scaling", default="strong", choices=("strong", "weak"),
                         help="strong: the workload's N is split over the ranks; weak: every "
                              "rank runs the whole shape")
@@ -763,6 +1073,11 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=device)
 
     from harness import native, sharding
+
+    if args.next_rows_only:
+        if info.rank == 0:
+            print(json.dumps({"next_rows": next_rows(device)}), file=json_out, flush=True)
+        return
 
     issue_tflops = None
     try:
@@ -928,6 +1243,7 @@ def main() -> None:
         if world == 1 and not args.no_configs:
             line["competitors"] = competitors(
                 device, args.steps if name == "square" else 50)
+            line["next_rows"] = next_rows(device)
         line["cpu_baseline"] = None if args.no_cpu_baseline else cpu_baseline(kind, shape)
         print(json.dumps(line), file=json_out, flush=True)
     if world > 1:

@@ -23,8 +23,9 @@ Layout choices that keep every stage a plain kernel launch on whole buffers:
   blocked scales ``[E, 2I/128, ceil(H/64), 32, 4, 4]``; ``w2`` packed ``[E, H, I/2]``
   with ``[E, ceil(H/128), ceil(I/64), 32, 4, 4]``. With ``fused=True`` the intermediate size
   must be a multiple of 128 (the up projection's scales then start on an atom row).
-* Plans and workspaces are cached per tuple of expert row counts (``MoELayer``): a forward
-  with a routing pattern seen before creates nothing.
+* Plans, workspaces and the buffers between the stages are kept per tuple of expert row
+  counts and bound once (``MoELayer``): a forward with a routing pattern seen before is one
+  quantiser launch and two grouped GEMM launches, with nothing allocated, encoded or bound.
 
 Expert parallelism (``moe_forward_ep``): rank r owns experts ``[r E/W, (r+1) E/W)``. Every
 rank routes its own tokens, sends each (token, choice) row to the owner of its expert with
@@ -35,6 +36,7 @@ the results back with a second all-to-all; the weighted sum happens where the to
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from collections.abc import Callable
 
 import torch
@@ -43,6 +45,7 @@ from . import native
 from .workloads import quantization as q
 
 ROW_BLOCK = 128
+MAX_PATTERNS = 8  # routing patterns a layer keeps plans and buffers for
 
 
 def route_rows(topk_ids: torch.Tensor, experts: int) -> tuple[torch.Tensor, list[int], list[int]]:
@@ -85,6 +88,83 @@ def _scatter(y: torch.Tensor, source: torch.Tensor, weights: torch.Tensor, token
     return out
 
 
+class _Pattern:
+    """What one routing pattern (row count per expert) of a layer needs on one stream: the
+    two grouped plans with their workspaces, and the buffers between the stages, allocated
+    once and bound to the plans once. Every expert's block starts on a 128-row boundary, so
+    the buffers are whole tensors that each group addresses by offset:
+
+    * ``a1`` / ``s1``: the quantised rows (packed ``[R, H/2]``, blocked scales);
+    * ``a2`` / ``s2``: the gated intermediate in NVFP4 (written by the fused gate/up kernel,
+      or by the quantiser after ``h`` FP16 ``[R, 2I]`` when not fused). The kernels write
+      only rows that exist, so padding rows and their scales stay zero;
+    * ``y``: FP16 ``[R, H]``, padding rows zero."""
+
+    def __init__(self, layer: MoELayer, counts: tuple[int, ...], stream: int):
+        device, hidden, inter = layer.device, layer.hidden, layer.inter
+        live = [e for e, count in enumerate(counts) if count > 0]
+        self.starts, total = [], 0
+        for count in counts:
+            self.starts.append(total)
+            total += -(-count // ROW_BLOCK) * ROW_BLOCK
+        self.total = total
+        starts = self.starts
+        index = device.index or 0
+        if layer.fused:
+            self.up_plan = native.Plan.grouped_dual_fp4(
+                index, [(counts[e], inter, hidden) for e in live])
+        else:
+            self.up_plan = native.Plan.grouped(
+                index, [(counts[e], 2 * inter, hidden) for e in live])
+        self.down_plan = native.Plan.grouped(index, [(counts[e], hidden, inter) for e in live])
+        self.up_ws, self.down_ws = (
+            torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=device)
+            for plan in (self.up_plan, self.down_plan))
+        self.up_plan.init_workspace(self.up_ws.data_ptr(), stream)
+        self.down_plan.init_workspace(self.down_ws.data_ptr(), stream)
+
+        atoms_h, atoms_i = -(-hidden // 64), -(-inter // 64)
+        blocks = total // ROW_BLOCK
+        byte = dict(dtype=torch.uint8, device=device)
+        self.a1 = torch.zeros((total, hidden // 2), **byte)
+        self.s1 = torch.zeros((blocks, atoms_h, 32, 4, 4), **byte)
+        self.a2 = torch.zeros((total, inter // 2), **byte)
+        self.s2 = torch.zeros((blocks, atoms_i, 32, 4, 4), **byte)
+        self.y = torch.zeros((total, hidden), dtype=torch.float16, device=device)
+        self.h = None
+        a_ptrs = [self.a1.data_ptr() + starts[e] * (hidden // 2) for e in live]
+        sa_ptrs = [self.s1.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_h * 512 for e in live]
+        a2_ptrs = [self.a2.data_ptr() + starts[e] * (inter // 2) for e in live]
+        s2_ptrs = [self.s2.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_i * 512 for e in live]
+        w13, w13_scales = layer.w13, layer.w13_scales
+        if layer.fused:
+            # Gate/up straight to the down projection's A operand.
+            self.up_plan.bind_dual_groups_fp4(
+                a_ptrs,
+                [w13[e].data_ptr() for e in live],
+                [w13[e].data_ptr() + inter * (hidden // 2) for e in live],
+                sa_ptrs,
+                [w13_scales[e].data_ptr() for e in live],
+                [w13_scales[e].data_ptr() + (inter // ROW_BLOCK) * atoms_h * 512 for e in live],
+                a2_ptrs, s2_ptrs, self.up_ws.data_ptr(), stream)
+        else:
+            self.h = torch.zeros((total, 2 * inter), dtype=torch.float16, device=device)
+            self.up_plan.bind_groups(
+                a_ptrs, [w13[e].data_ptr() for e in live], sa_ptrs,
+                [w13_scales[e].data_ptr() for e in live],
+                [self.h.data_ptr() + starts[e] * 2 * inter * 2 for e in live],
+                self.up_ws.data_ptr(), stream)
+        self.down_plan.bind_groups(
+            a2_ptrs, [layer.w2[e].data_ptr() for e in live], s2_ptrs,
+            [layer.w2_scales[e].data_ptr() for e in live],
+            [self.y.data_ptr() + starts[e] * hidden * 2 for e in live],
+            self.down_ws.data_ptr(), stream)
+
+    def destroy(self) -> None:
+        self.up_plan.destroy()
+        self.down_plan.destroy()
+
+
 class MoELayer:
     """The experts of one layer on one GPU with their cached plans.
 
@@ -109,14 +189,13 @@ class MoELayer:
         self.device = w13.device
         if self.device.type != "cuda" or not native.device_supported(self.device.index or 0):
             raise RuntimeError(f"sm_100a code cannot run on {self.device}")
-        self._plans: dict[tuple, tuple] = {}
+        self._plans: OrderedDict[tuple, _Pattern] = OrderedDict()
 
     def close(self) -> None:
         if self._plans:
             torch.cuda.synchronize(self.device)
-        for up_plan, _, down_plan, _ in self._plans.values():
-            up_plan.destroy()
-            down_plan.destroy()
+        for pattern in self._plans.values():
+            pattern.destroy()
         self._plans.clear()
 
     def __del__(self):
@@ -125,92 +204,57 @@ class MoELayer:
         except Exception:
             pass
 
-    def _entry(self, counts: tuple[int, ...], stream: int):
-        """(gate/up plan, its workspace, down plan, its workspace) for this routing pattern."""
-        entry = self._plans.get((counts, stream))
-        if entry is None:
-            live = [e for e, count in enumerate(counts) if count > 0]
-            index = self.device.index or 0
-            if self.fused:
-                up_plan = native.Plan.grouped_dual_fp4(
-                    index, [(counts[e], self.inter, self.hidden) for e in live])
-            else:
-                up_plan = native.Plan.grouped(
-                    index, [(counts[e], 2 * self.inter, self.hidden) for e in live])
-            down_plan = native.Plan.grouped(
-                index, [(counts[e], self.hidden, self.inter) for e in live])
-            workspaces = []
-            for plan in (up_plan, down_plan):
-                ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8,
-                                 device=self.device)
-                plan.init_workspace(ws.data_ptr(), stream)
-                workspaces.append(ws)
-            entry = (up_plan, workspaces[0], down_plan, workspaces[1])
-            self._plans[(counts, stream)] = entry
-        return entry
+    def _entry(self, counts: tuple[int, ...], stream: int) -> _Pattern:
+        """Plans, workspaces and buffers of this routing pattern on this stream: created and
+        bound at the pattern's first forward, least recently used dropped beyond
+        ``MAX_PATTERNS``."""
+        key = (counts, stream)
+        pattern = self._plans.get(key)
+        if pattern is not None:
+            self._plans.move_to_end(key)
+            return pattern
+        while len(self._plans) >= MAX_PATTERNS:
+            _, oldest = self._plans.popitem(last=False)
+            torch.cuda.synchronize(self.device)
+            oldest.destroy()
+        pattern = _Pattern(self, counts, stream)
+        self._plans[key] = pattern
+        return pattern
 
     def forward_rows(self, rows: torch.Tensor, counts: list[int], starts: list[int]) -> torch.Tensor:
         """The experts applied to permuted rows: ``rows`` FP32 ``[R, H]`` grouped by expert
         (expert e at ``starts[e]``, ``counts[e]`` rows, blocks padded to 128 rows). Returns
-        FP16 ``[R, H]`` (padding rows zero)."""
-        device, hidden, inter = self.device, self.hidden, self.inter
-        total = rows.shape[0]
-        y = torch.zeros((total, hidden), dtype=torch.float16, device=device)
-        live = [e for e, count in enumerate(counts) if count > 0]
-        if not live:
-            return y
-        with torch.cuda.device(device):
-            stream = torch.cuda.current_stream(device).cuda_stream
-            up_plan, up_ws, down_plan, down_ws = self._entry(tuple(counts), stream)
-            a1, s1 = q.quantize_nvfp4_native(rows.unsqueeze(0).permute(1, 2, 0))
-            a1, s1 = a1.permute(2, 0, 1)[0], s1[0]
-            atoms_h, atoms_i = -(-hidden // 64), -(-inter // 64)
-            a_ptrs = [a1.data_ptr() + starts[e] * (hidden // 2) for e in live]
-            sa_ptrs = [s1.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_h * 512 for e in live]
-            if self.fused:
-                # Gate/up straight to the down projection's A operand.
-                a2 = torch.zeros((total, inter // 2), dtype=torch.uint8, device=device)
-                s2 = torch.zeros((total // ROW_BLOCK, atoms_i, 32, 4, 4), dtype=torch.uint8,
-                                 device=device)
-                up_plan.bind_dual_groups_fp4(
-                    a_ptrs,
-                    [self.w13[e].data_ptr() for e in live],
-                    [self.w13[e].data_ptr() + inter * (hidden // 2) for e in live],
-                    sa_ptrs,
-                    [self.w13_scales[e].data_ptr() for e in live],
-                    [self.w13_scales[e].data_ptr() + (inter // ROW_BLOCK) * atoms_h * 512
-                     for e in live],
-                    [a2.data_ptr() + starts[e] * (inter // 2) for e in live],
-                    [s2.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_i * 512 for e in live],
-                    up_ws.data_ptr(), stream)
-                up_plan.launch_groups(up_ws.data_ptr(), stream)
-            else:
-                h = torch.zeros((total, 2 * inter), dtype=torch.float16, device=device)
-                up_plan.bind_groups(
-                    a_ptrs, [self.w13[e].data_ptr() for e in live], sa_ptrs,
-                    [self.w13_scales[e].data_ptr() for e in live],
-                    [h.data_ptr() + starts[e] * 2 * inter * 2 for e in live],
-                    up_ws.data_ptr(), stream)
-                up_plan.launch_groups(up_ws.data_ptr(), stream)
+        FP16 ``[R, H]`` (padding rows zero): the pattern's own output buffer, which the next
+        forward with the same row counts on the same stream overwrites.
+
+        A pattern seen before costs one quantiser launch and two grouped GEMM launches:
+        nothing is allocated, encoded or bound."""
+        hidden, inter = self.hidden, self.inter
+        if not any(count > 0 for count in counts):
+            return torch.zeros((rows.shape[0], hidden), dtype=torch.float16, device=self.device)
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            pattern = self._entry(tuple(counts), stream)
+            if list(starts) != pattern.starts or rows.shape != (pattern.total, hidden):
+                raise ValueError("rows are not laid out in 128-row blocks per expert")
+            if rows.dtype != torch.float32 or not rows.is_contiguous():
+                rows = rows.float().contiguous()
+            native.quantize(rows.data_ptr(), native.IN_F32, pattern.a1.data_ptr(),
+                            pattern.s1.data_ptr(), pattern.total, hidden, 1, stream)
+            pattern.up_plan.launch_groups(pattern.up_ws.data_ptr(), stream)
+            if not self.fused:
+                h = pattern.h
                 act = torch.nn.functional.silu(h[:, :inter].float()) * h[:, inter:].float()
-                a2, s2 = q.quantize_nvfp4_native(act.unsqueeze(0).permute(1, 2, 0))
-                a2, s2 = a2.permute(2, 0, 1)[0], s2[0]
-            down_plan.bind_groups(
-                [a2.data_ptr() + starts[e] * (inter // 2) for e in live],
-                [self.w2[e].data_ptr() for e in live],
-                [s2.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_i * 512 for e in live],
-                [self.w2_scales[e].data_ptr() for e in live],
-                [y.data_ptr() + starts[e] * hidden * 2 for e in live],
-                down_ws.data_ptr(), stream)
-            down_plan.launch_groups(down_ws.data_ptr(), stream)
-            self._keepalive = (a1, s1, a2, s2)  # until the launches have run
-        return y
+                native.quantize(act.data_ptr(), native.IN_F32, pattern.a2.data_ptr(),
+                                pattern.s2.data_ptr(), pattern.total, inter, 1, stream)
+            pattern.down_plan.launch_groups(pattern.down_ws.data_ptr(), stream)
+        return pattern.y
 
     def check_status(self) -> None:
         """Synchronise and raise ``native.NativeError`` if a kernel abandoned a wait."""
-        for (_, stream), (up_plan, up_ws, down_plan, down_ws) in self._plans.items():
-            up_plan.status(up_ws.data_ptr(), stream)
-            down_plan.status(down_ws.data_ptr(), stream)
+        for (_, stream), pattern in self._plans.items():
+            pattern.up_plan.status(pattern.up_ws.data_ptr(), stream)
+            pattern.down_plan.status(pattern.down_ws.data_ptr(), stream)
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """``out[t] = sum_j weight[t, j] * down_e(silu(gate_e(x_t)) * up_e(x_t))`` with
