@@ -1013,12 +1013,15 @@ def row_moe(device) -> list[dict]:
     return out
 
 
-def next_rows(device) -> list[dict]:
+def next_rows(device, only: str = "") -> list[dict]:
     """The rows beside the GEMM path (quantiser, NVFP4-output epilogues, shuffled weights, the
     MoE layer), each validated and timed like ``configs``. A row that fails says so and the
     others still run."""
     rows = []
+    wanted = {name for name in only.split(",") if name}
     for make in (row_quantiser, row_fp4_output, row_shuffled, row_moe):
+        if wanted and make.__name__.removeprefix("row_") not in wanted:
+            continue
         try:
             made = make(device)
             rows += made if isinstance(made, list) else [made]
@@ -1041,6 +1044,9 @@ def main() -> None:
                         help="headline workload only (no configs array, no competitors)")
     parser.add_argument("--next-rows-only", action="store_true",
                         help="measure only the rows beside the GEMM path (one GPU)")
+    parser.add_argument("--rows", default="",
+                        help="with --next-rows-only: a comma-separated subset of quantiser, "
+                             "fp4_output, shuffled, moe")
     parser.add_argument("--scaling", default="strong", choices=("strong", "weak"),
                         help="strong: the workload's N is split over the ranks; weak: every "
                              "rank runs the whole shape")
@@ -1076,7 +1082,8 @@ def main() -> None:
 
     if args.next_rows_only:
         if info.rank == 0:
-            print(json.dumps({"next_rows": next_rows(device)}), file=json_out, flush=True)
+            print(json.dumps({"next_rows": next_rows(device, args.rows)}), file=json_out,
+                  flush=True)
         return
 
     issue_tflops = None

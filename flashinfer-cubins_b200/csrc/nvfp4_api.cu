@@ -1413,32 +1413,23 @@ int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int ro
   if (!aligned(x, 16) || !aligned(packed, 8) || !aligned(scales, 16)) {
     return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
   }
-  const long long total = static_cast<long long>(batches) * ceil_div(rows, 128) * 128 *
-                          ceil_div(k / 16, 4) * 4;
-  const int threads = 256;
-  const long long blocks =
-      std::min<long long>((total + threads - 1) / threads, 32ll * current_sm_count());
+  // One thread per 16-element block of the padded scale grid; see the kernel for the geometry.
+  const dim3 block(kQuantBlocksX, kQuantRowsY, 1);
+  const dim3 grid(static_cast<unsigned int>(ceil_div(rows, 128) * (128 / kQuantRowsPerCta)),
+                  static_cast<unsigned int>(ceil_div(ceil_div(k / 16, 4) * 4, kQuantBlocksX)),
+                  static_cast<unsigned int>(std::min(batches, 65535)));
+  if (grid.y > 65535u) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "k=%d is too large for the quantiser", k);
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const unsigned int grid = static_cast<unsigned int>(blocks);
   uint8_t* p8 = static_cast<uint8_t*>(packed);
   uint8_t* s8 = static_cast<uint8_t*>(scales);
-  // 32-bit indices while the grid-stride loop cannot overflow them.
-  const bool narrow = total + static_cast<long long>(grid) * threads < INT_MAX;
   if (x_kind == NVFP4_IN_F32) {
-    const float* in = static_cast<const float*>(x);
-    if (narrow) {
-      quantize_nvfp4_kernel<float, int><<<grid, threads, 0, s>>>(in, p8, s8, rows, k, batches);
-    } else {
-      quantize_nvfp4_kernel<float, long long><<<grid, threads, 0, s>>>(in, p8, s8, rows, k, batches);
-    }
+    quantize_nvfp4_kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(x), p8, s8, rows,
+                                                        k, batches);
   } else {
-    const __nv_bfloat16* in = static_cast<const __nv_bfloat16*>(x);
-    if (narrow) {
-      quantize_nvfp4_kernel<__nv_bfloat16, int><<<grid, threads, 0, s>>>(in, p8, s8, rows, k, batches);
-    } else {
-      quantize_nvfp4_kernel<__nv_bfloat16, long long><<<grid, threads, 0, s>>>(in, p8, s8, rows, k,
-                                                                               batches);
-    }
+    quantize_nvfp4_kernel<__nv_bfloat16><<<grid, block, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), p8, s8, rows, k, batches);
   }
   CUDA_TRY(cudaGetLastError());
   return 0;

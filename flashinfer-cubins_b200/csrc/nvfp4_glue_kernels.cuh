@@ -104,8 +104,14 @@ struct E2m1Boundaries {
 // UE4M3 bits of the scale of a 16-element block with the given absolute maximum:
 // amax / 6 rounded to nearest even, saturating at 448.
 __device__ __forceinline__ uint32_t nvfp4_scale_bits(float amax) {
+  // amax / 6 correctly rounded without the division: q = amax y with y = RN(1/6), then
+  // q + (amax - 6 q) y (see quantize_nvfp4_kernel). Infinity: the residual would be NaN, and
+  // the result saturates anyway.
+  constexpr float kSixth = 1.0f / 6.0f;
+  const float q = amax * kSixth;
+  const float sixth = amax <= 3.0e38f ? __fmaf_rn(__fmaf_rn(-6.0f, q, amax), kSixth, q) : amax;
   return static_cast<uint32_t>(
-      __nv_cvt_float_to_fp8(fminf(__fdiv_rn(amax, 6.0f), 448.0f), __NV_SATFINITE, __NV_E4M3));
+      __nv_cvt_float_to_fp8(fminf(sixth, 448.0f), __NV_SATFINITE, __NV_E4M3));
 }
 
 __device__ __forceinline__ float nvfp4_scale_value(uint32_t bits) {
@@ -114,85 +120,119 @@ __device__ __forceinline__ float nvfp4_scale_value(uint32_t bits) {
 }
 
 // FP32/BF16 [batches][rows][k] -> packed E2M1 [batches][rows][k/2] and UE4M3 scales in the
-// blocked layout [batches][rb][cb][32][4][4] (zero padded), one thread per 16-element block
-// of the padded scale grid: scale = e4m3(amax / 6) (round to nearest even, saturating),
-// element = E2M1 rounding of x / scale, zero scale -> zero codes.
-// `Index` is int when the padded scale grid has fewer than 2^31 entries (64-bit divisions
-// per thread would dominate the kernel), long long otherwise.
-template <typename In, typename Index>
-__global__ void quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
-                                      uint8_t* __restrict__ scales, int rows, int k,
-                                      int batches) {
+// blocked layout [batches][rb][cb][32][4][4] (zero padded): scale = e4m3(amax / 6) (round to
+// nearest even, saturating), element = E2M1 rounding of x / scale, zero scale -> zero codes.
+//
+// One thread per 16-element block of the padded scale grid and four rows, placed by the
+// launch geometry instead of by divisions: a CTA is 64 blocks of sixteen rows (threadIdx.x the
+// block, threadIdx.y + 4 i the row for i = 0..3), blockIdx.x the group of sixteen rows,
+// blockIdx.y the group of 64 blocks, blockIdx.z the batch. A thread issues the loads of its
+// four rows before it works on the first, so that enough bytes are in flight. A warp is 32
+// consecutive blocks of one row: it reads 1 KB (BF16) or 2 KB (FP32) and writes 256 B of
+// codes in a row, and the scale bytes of four neighbouring blocks, which are neighbours in
+// the blocked layout too, leave as one 32-bit word.
+constexpr int kQuantBlocksX = 64;
+constexpr int kQuantRowsY = 4;
+constexpr int kQuantRowsPerThread = 4;
+constexpr int kQuantRowsPerCta = kQuantRowsY * kQuantRowsPerThread;
+
+template <typename In>
+__global__ void __launch_bounds__(kQuantBlocksX* kQuantRowsY)
+quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
+                      uint8_t* __restrict__ scales, int rows, int k, int batches) {
+  constexpr int kVectors = sizeof(In) == 4 ? 4 : 2;  // 16-byte loads per block
   const int cols = k / 16;
   const int rb = (rows + 127) / 128;
   const int cb = (cols + 3) / 4;
-  const Index padded_cols = static_cast<Index>(cb) * 4;
-  const Index total = static_cast<Index>(batches) * rb * 128 * padded_cols;
-  for (Index i = blockIdx.x * static_cast<Index>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<Index>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>(i % padded_cols);
-    Index rest = i / padded_cols;
-    const int r = static_cast<int>(rest % (rb * 128));
-    const int batch = static_cast<int>(rest / (rb * 128));
-    const long long atom = (static_cast<long long>(batch) * rb + r / 128) * cb + c / 4;
-    uint8_t* scale_out = scales + atom * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4 + c % 4;
-    if (r >= rows || c >= cols) {
-      *scale_out = 0;
-      continue;
-    }
-    const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
-    float v[16];
-    if constexpr (sizeof(In) == 4) {
-      const float4* src = reinterpret_cast<const float4*>(x + element);
+  const int c = blockIdx.y * kQuantBlocksX + threadIdx.x;
+  const int r0 = blockIdx.x * kQuantRowsPerCta + threadIdx.y;
+  for (int batch = blockIdx.z; batch < batches; batch += gridDim.z) {
+    uint4 raw[kQuantRowsPerThread][kVectors];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float4 t = src[q];
-        v[4 * q] = t.x;
-        v[4 * q + 1] = t.y;
-        v[4 * q + 2] = t.z;
-        v[4 * q + 3] = t.w;
+    for (int i = 0; i < kQuantRowsPerThread; ++i) {
+      const int r = r0 + kQuantRowsY * i;
+      if (r < rows && c < cols) {
+        const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
+        const uint4* src = reinterpret_cast<const uint4*>(x + element);
+#pragma unroll
+        for (int q = 0; q < kVectors; ++q) raw[i][q] = src[q];
       }
-    } else {
-      const uint4* src = reinterpret_cast<const uint4*>(x + element);
+    }
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const uint4 t = src[q];
-        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+    for (int i = 0; i < kQuantRowsPerThread; ++i) {
+      const int r = r0 + kQuantRowsY * i;
+      uint32_t scale_bits = 0;
+      if (r < rows && c < cols) {
+        const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
+        float v[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          v[8 * q + 2 * j] = __uint_as_float(w[j] << 16);
-          v[8 * q + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        for (int q = 0; q < kVectors; ++q) {
+          const uint32_t w[4] = {raw[i][q].x, raw[i][q].y, raw[i][q].z, raw[i][q].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if constexpr (sizeof(In) == 4) {
+              v[4 * q + j] = __uint_as_float(w[j]);
+            } else {
+              v[8 * q + 2 * j] = __uint_as_float(w[j] << 16);
+              v[8 * q + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            }
+          }
         }
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        scale_bits = nvfp4_scale_bits(amax);
+        const float scale = nvfp4_scale_value(scale_bits);
+        uint32_t words[2] = {0u, 0u};
+        if (scale > 0.0f) {
+          // The correctly rounded quotient x / scale goes through the hardware conversion
+          // (round to nearest even, saturating). (A bare reciprocal multiply would break
+          // exact ties such as x / scale == 0.75.) With finite inputs the quotient comes from
+          // the correctly rounded reciprocal and two fused multiply-adds, q = x y,
+          // q' = q + (x - scale q) y, which is the correctly rounded quotient whenever the
+          // divisor's significand is not all ones (a scale has four significant bits): three
+          // instructions for each of the sixteen IEEE divisions, which had made this kernel
+          // instruction-bound. Blocks with an infinity take the division itself.
+          float quotient[16];
+          if (amax <= 3.0e38f) {
+            const float y = __frcp_rn(scale);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float q = v[j] * y;
+              quotient[j] = __fmaf_rn(__fmaf_rn(-scale, q, v[j]), y, q);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) quotient[j] = __fdiv_rn(v[j], scale);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t pair = __nv_cvt_float2_to_fp4x2(
+                make_float2(quotient[2 * j], quotient[2 * j + 1]), __NV_E2M1, cudaRoundNearest);
+            words[j / 4] |= pair << (8 * (j % 4));
+          }
+          // A negative value that rounds to zero gets code 0, not -0.
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t magnitude = words[h] & 0x77777777u;
+            const uint32_t nonzero =
+                (magnitude | (magnitude >> 1) | (magnitude >> 2)) & 0x11111111u;
+            words[h] = magnitude | (words[h] & (nonzero << 3));
+          }
+        }
+        *reinterpret_cast<uint2*>(packed + element / 2) = make_uint2(words[0], words[1]);
+      }
+      // Scale bytes of blocks c..c+3 (c a multiple of four) of row r are one aligned word of
+      // the atom; padding rows and columns of the grid get zeros.
+      uint32_t word = scale_bits << (8 * (threadIdx.x & 3));
+      word |= __shfl_xor_sync(0xFFFFFFFFu, word, 1);
+      word |= __shfl_xor_sync(0xFFFFFFFFu, word, 2);
+      if ((threadIdx.x & 3) == 0 && c < cb * 4) {
+        const long long atom = (static_cast<long long>(batch) * rb + r / 128) * cb + c / 4;
+        *reinterpret_cast<uint32_t*>(scales + atom * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4) =
+            word;
       }
     }
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    const uint32_t scale_bits = nvfp4_scale_bits(amax);
-    *scale_out = static_cast<uint8_t>(scale_bits);
-    const float scale = nvfp4_scale_value(scale_bits);
-    uint32_t words[2] = {0u, 0u};
-    if (scale > 0.0f) {
-      // The correctly rounded quotient goes through the hardware conversion (round to
-      // nearest even, saturating): the same decisions as comparing it with the E2M1
-      // boundaries, at a sixth of the instructions. (A reciprocal multiply instead of the
-      // division would break exact ties such as x / scale == 0.75.) A negative value that
-      // rounds to zero gets code 0, not -0.
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t pair = __nv_cvt_float2_to_fp4x2(
-            make_float2(__fdiv_rn(v[2 * j], scale), __fdiv_rn(v[2 * j + 1], scale)), __NV_E2M1,
-            cudaRoundNearest);
-        words[j / 4] |= pair << (8 * (j % 4));
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t magnitude = words[h] & 0x77777777u;
-        const uint32_t nonzero = (magnitude | (magnitude >> 1) | (magnitude >> 2)) & 0x11111111u;
-        words[h] = magnitude | (words[h] & (nonzero << 3));
-      }
-    }
-    *reinterpret_cast<uint2*>(packed + element / 2) = make_uint2(words[0], words[1]);
   }
 }
 

@@ -507,6 +507,35 @@ def test_quantiser_kernel_matches_torch_quantiser_bytes(rows, k, batches, dtype)
         assert np.array_equal(blocked.view(torch.uint8).cpu().numpy(), o.to_blocked(o_scales))
 
 
+def test_quantiser_kernel_on_ties_and_their_neighbours():
+    """Every E4M3 scale with every E2M1 rounding boundary: blocks whose maximum pins the scale
+    and whose other elements sit exactly on a boundary times the scale, and one float above
+    and below it, with both signs; plus infinities, which take the kernel's other division
+    path. Bytes must equal the torch quantiser's (a true division)."""
+    from harness.workloads import quantization as q
+    bits = torch.arange(1, 127, dtype=torch.uint8)
+    scales = bits.view(torch.float8_e4m3fn).float()                       # 126 positive scales
+    bounds = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    exact = (scales[:, None] * bounds[None, :]).reshape(-1)               # exact products
+    up = torch.nextafter(exact, torch.tensor(float("inf")))
+    down = torch.nextafter(exact, torch.tensor(0.0))
+    values = torch.stack([exact, up, down, -exact, -up, -down], dim=1)    # [126 * 7, 6]
+    blocks = torch.zeros(values.shape[0], 16)
+    blocks[:, 0] = 6.0 * scales.repeat_interleave(7)                      # amax / 6 == scale
+    blocks[:, 1:7] = values
+    blocks[:, 7:] = torch.randn(values.shape[0], 9) * scales.repeat_interleave(7)[:, None]
+    k = 16 * 7
+    x = blocks.reshape(126, k)
+    special = torch.randn(2, k)
+    special[0, 3], special[0, 40], special[1, 100] = float("inf"), float("-inf"), float("inf")
+    x = torch.cat([x, special]).reshape(1, 128, k).cuda().permute(1, 2, 0)
+    packed, blocked = q.quantize_nvfp4_native(x)
+    torch.cuda.synchronize()
+    want_packed, want_scales = q.quantize_nvfp4(x)
+    assert torch.equal(blocked.view(torch.uint8), q.to_blocked_scales(want_scales).view(torch.uint8))
+    assert torch.equal(packed, want_packed)
+
+
 def _fp4_out_inputs(m, n, k, batches, scales, seed):
     from harness.workloads import quantization as q
     workload = get_workload("nvfp4_gemm")(None, device="cuda")
