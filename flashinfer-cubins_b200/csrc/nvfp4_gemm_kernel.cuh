@@ -1070,25 +1070,20 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             uint32_t words[4];
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
+              float v[16];
               float amax = 0.0f;
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                amax = fmaxf(amax, fabsf(__uint_as_float(r1[16 * blk + i])));
+                v[i] = __uint_as_float(r1[16 * blk + i]);
+                amax = fmaxf(amax, fabsf(v[i]));
               }
               const uint32_t bits = nvfp4_scale_bits(amax);
               const float scale = nvfp4_scale_value(bits);
               scale_word |= bits << (8 * (2 * half + blk));
-              uint32_t w0 = 0, w1 = 0;
-              if (scale > 0.0f) {
-                const E2m1Boundaries boundaries(scale);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  w0 |= boundaries.code(__uint_as_float(r1[16 * blk + i])) << (4 * i);
-                  w1 |= boundaries.code(__uint_as_float(r1[16 * blk + 8 + i])) << (4 * i);
-                }
-              }
-              words[2 * blk] = w0;
-              words[2 * blk + 1] = w1;
+              const uint2 codes =
+                  scale > 0.0f ? nvfp4_block_codes(v, amax, scale) : make_uint2(0u, 0u);
+              words[2 * blk] = codes.x;
+              words[2 * blk + 1] = codes.y;
             }
             if (grow < pd.m && n0 + c * 32 < pd.n) {
               *reinterpret_cast<uint4*>(d_row + (n0 + c * 32) / 2) =

@@ -74,33 +74,6 @@ __global__ void pack_scales_kernel(const uint8_t* __restrict__ scales,
   }
 }
 
-// The seven E2M1 rounding boundaries (ties to even: 0.25 -> 0, 0.75 -> 1, ...) times a block's
-// scale. A scale has four significant bits and a boundary three, so the products are exact,
-// and comparing x with them decides exactly as comparing the correctly rounded quotient
-// x / scale with the boundaries does (division is monotone and exact at the boundary) -
-// without sixteen IEEE divisions per block, which made the quantiser ALU-bound.
-struct E2m1Boundaries {
-  float b[7];
-  __device__ __forceinline__ explicit E2m1Boundaries(float scale) {
-    b[0] = 0.25f * scale;
-    b[1] = 0.75f * scale;
-    b[2] = 1.25f * scale;
-    b[3] = 1.75f * scale;
-    b[4] = 2.5f * scale;
-    b[5] = 3.5f * scale;
-    b[6] = 5.0f * scale;
-  }
-  // Round-to-nearest-even E2M1 code of x / scale (saturating at +-6; values that round to
-  // zero get code 0 whatever their sign).
-  __device__ __forceinline__ uint32_t code(float x) const {
-    const float m = fabsf(x);
-    uint32_t c = (m > b[0]) + (m >= b[1]) + (m > b[2]) + (m >= b[3]) + (m > b[4]) + (m >= b[5]) +
-                 (m > b[6]);
-    if (x < 0.0f && c != 0) c |= 8u;
-    return c;
-  }
-};
-
 // UE4M3 bits of the scale of a 16-element block with the given absolute maximum:
 // amax / 6 rounded to nearest even, saturating at 448.
 __device__ __forceinline__ uint32_t nvfp4_scale_bits(float amax) {
@@ -117,6 +90,48 @@ __device__ __forceinline__ uint32_t nvfp4_scale_bits(float amax) {
 __device__ __forceinline__ float nvfp4_scale_value(uint32_t bits) {
   return __half2float(
       __half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(bits), __NV_E4M3)));
+}
+
+// The sixteen E2M1 codes of a block with absolute maximum `amax` and scale `scale` > 0
+// (x = low word: elements 0-7, y = elements 8-15; element i in nibble i % 8): the correctly
+// rounded quotient x / scale goes through the hardware conversion (round to nearest even,
+// saturating at +-6). (A bare reciprocal multiply would break exact ties such as
+// x / scale == 0.75.) With finite inputs the quotient comes from the correctly rounded
+// reciprocal and two fused multiply-adds, q = x y, q' = q + (x - scale q) y, which is the
+// correctly rounded quotient whenever the divisor's significand is not all ones (a scale has
+// four significant bits): three instructions in place of an IEEE division. Blocks with an
+// infinity take the division itself. A negative value that rounds to zero gets code 0, not -0.
+// Used by the quantiser kernel and by the GEMM epilogues that write NVFP4, so that both produce
+// the same bytes from the same FP32 values.
+__device__ __forceinline__ uint2 nvfp4_block_codes(const float (&v)[16], float amax, float scale) {
+  float quotient[16];
+  if (amax <= 3.0e38f) {
+    const float y = __frcp_rn(scale);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float q = v[j] * y;
+      quotient[j] = __fmaf_rn(__fmaf_rn(-scale, q, v[j]), y, q);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) quotient[j] = __fdiv_rn(v[j], scale);
+  }
+  uint32_t words[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t pair = __nv_cvt_float2_to_fp4x2(
+        make_float2(quotient[2 * j], quotient[2 * j + 1]), __NV_E2M1, cudaRoundNearest);
+    words[j / 4] |= pair << (8 * (j % 4));
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    // A nibble's magnitude m is 0..7: m + 7 sets bit 3 exactly when m is not zero, without a
+    // carry into the next nibble.
+    const uint32_t magnitude = words[h] & 0x77777777u;
+    const uint32_t nonzero = (magnitude + 0x77777777u) & 0x88888888u;
+    words[h] = magnitude | (words[h] & nonzero);
+  }
+  return make_uint2(words[0], words[1]);
 }
 
 // FP32/BF16 [batches][rows][k] -> packed E2M1 [batches][rows][k/2] and UE4M3 scales in the
@@ -183,44 +198,8 @@ quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
         for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
         scale_bits = nvfp4_scale_bits(amax);
         const float scale = nvfp4_scale_value(scale_bits);
-        uint32_t words[2] = {0u, 0u};
-        if (scale > 0.0f) {
-          // The correctly rounded quotient x / scale goes through the hardware conversion
-          // (round to nearest even, saturating). (A bare reciprocal multiply would break
-          // exact ties such as x / scale == 0.75.) With finite inputs the quotient comes from
-          // the correctly rounded reciprocal and two fused multiply-adds, q = x y,
-          // q' = q + (x - scale q) y, which is the correctly rounded quotient whenever the
-          // divisor's significand is not all ones (a scale has four significant bits): three
-          // instructions for each of the sixteen IEEE divisions, which had made this kernel
-          // instruction-bound. Blocks with an infinity take the division itself.
-          float quotient[16];
-          if (amax <= 3.0e38f) {
-            const float y = __frcp_rn(scale);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float q = v[j] * y;
-              quotient[j] = __fmaf_rn(__fmaf_rn(-scale, q, v[j]), y, q);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) quotient[j] = __fdiv_rn(v[j], scale);
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t pair = __nv_cvt_float2_to_fp4x2(
-                make_float2(quotient[2 * j], quotient[2 * j + 1]), __NV_E2M1, cudaRoundNearest);
-            words[j / 4] |= pair << (8 * (j % 4));
-          }
-          // A negative value that rounds to zero gets code 0, not -0.
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t magnitude = words[h] & 0x77777777u;
-            const uint32_t nonzero =
-                (magnitude | (magnitude >> 1) | (magnitude >> 2)) & 0x11111111u;
-            words[h] = magnitude | (words[h] & (nonzero << 3));
-          }
-        }
-        *reinterpret_cast<uint2*>(packed + element / 2) = make_uint2(words[0], words[1]);
+        const uint2 codes = scale > 0.0f ? nvfp4_block_codes(v, amax, scale) : make_uint2(0u, 0u);
+        *reinterpret_cast<uint2*>(packed + element / 2) = codes;
       }
       // Scale bytes of blocks c..c+3 (c a multiple of four) of row r are one aligned word of
       // the atom; padding rows and columns of the grid get zeros.

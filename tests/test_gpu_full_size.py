@@ -158,3 +158,106 @@ def test_C5_grouped_config_with_normal_operands_and_column_slices():
             workload.check_status()
             expected = tuple(ref[g][:, start:stop].contiguous() for g, start, stop in spans)
             workload.validate(expected, tuple(p.contiguous() for p in pieces))
+
+
+def test_C3_nvfp4_output_equals_the_quantiser_on_the_fp32_output():
+    """8192^3 with D quantised in the epilogue (many tiles per CTA): packed codes and blocked
+    scales equal, byte for byte, the quantiser kernel applied to the FP32-output GEMM of the
+    same operands, whose values are checked against the torch reference on a band of rows."""
+    from harness import native
+    m = n = k = 8192
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    a, sa = normal_operand(m, k, 1, dev)
+    b, sb = normal_operand(n, k, 2, dev)
+    sfa, sfb = to_task_scales(sa), to_task_scales(sb)
+    alpha = torch.ones(1, device=dev)
+    plans = {kind: native.Plan.dense(0, kind, m, n, k, 1) for kind in (native.OUT_FP4, native.OUT_F32)}
+    spaces = {}
+    for kind, plan in plans.items():
+        spaces[kind] = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(spaces[kind].data_ptr(), stream)
+    packed = torch.empty((1, m, n // 2), dtype=torch.uint8, device=dev)
+    scales = torch.zeros((1, m // 128, n // 64, 32, 4, 4), dtype=torch.uint8, device=dev)
+    product = torch.empty((1, m, n), dtype=torch.float32, device=dev)
+    plans[native.OUT_FP4].launch_dense_fp4(
+        a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), alpha.data_ptr(),
+        packed.data_ptr(), scales.data_ptr(), spaces[native.OUT_FP4].data_ptr(), stream)
+    plans[native.OUT_F32].launch_dense(
+        a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), alpha.data_ptr(),
+        product.data_ptr(), spaces[native.OUT_F32].data_ptr(), stream)
+    for kind, plan in plans.items():
+        assert plan.status(spaces[kind].data_ptr(), stream) == 0
+    want_packed, want_scales = q.quantize_nvfp4_native(product.permute(1, 2, 0))
+    assert torch.equal(packed, want_packed.permute(2, 0, 1))
+    assert torch.equal(scales, want_scales.view(torch.uint8))
+    band = slice(4000, 4256)
+    ref = q.fp4_matmul(a[band], b, sa[band], sb, out_dtype=torch.float32)
+    torch.testing.assert_close(product[0, band], ref[..., 0], rtol=1e-3, atol=1e-3)
+    for plan in plans.values():
+        plan.destroy()
+
+
+def test_C2_decode_config_on_shuffled_weights():
+    """The decode shape with B in the trtllm-gen row order and BF16 output, N(0,1) operands."""
+    m, n, k = 128, 7168, 16384
+    dev = torch.device("cuda")
+    with get_workload("nvfp4_gemm_bf16_shuffled").from_arch("sm_100a", device="cuda") as workload:
+        a, sa = normal_operand(m, k, 1, dev)
+        b, sb = normal_operand(n, k, 2, dev)
+        inputs = (a, b, to_task_scales(sa), to_task_scales(sb), torch.ones(1, device=dev))
+        ref = workload.get_reference(inputs)
+        out = workload.run(inputs)
+        torch.cuda.synchronize()
+        workload.check_status()
+        workload.validate(ref, out)
+
+
+def test_moe_shard_at_model_size_matches_every_expert():
+    """One rank's share of a DeepSeek-V3 MoE layer (32 local experts, hidden 7168,
+    intermediate 2048, 1,024 routed rows with skewed counts, some experts empty): every
+    expert's rows against the stage-by-stage torch reference."""
+    from harness import moe
+    from harness.throughput import skewed_lengths
+    dev = torch.device("cuda:0")
+    local, hidden, inter, routed = 32, 7168, 2048, 1024
+    gen = torch.Generator(device=dev).manual_seed(7)
+
+    def weights(rows, k):
+        packed = torch.empty((local, rows, k // 2), dtype=torch.uint8, device=dev)
+        blocked = torch.empty((local, rows // 128, k // 64, 32, 4, 4), dtype=torch.float8_e4m3fn,
+                              device=dev)
+        for e in range(local):
+            w = torch.randn((1, rows, k), device=dev, generator=gen) * 0.05
+            p, s = q.quantize_nvfp4_native(w.permute(1, 2, 0))
+            packed[e], blocked[e] = p[..., 0], s[0]
+        return packed, blocked
+
+    w13, w13_scales = weights(2 * inter, hidden)
+    w2, w2_scales = weights(hidden, inter)
+    counts = list(skewed_lengths(routed, local, seed=routed, minimum=0))
+    assert 0 in counts and sum(counts) == routed
+    starts, total = [], 0
+    for count in counts:
+        starts.append(total)
+        total += -(-count // 128) * 128
+    rows = torch.zeros((total, hidden), device=dev)
+    for e, count in enumerate(counts):
+        rows[starts[e]:starts[e] + count] = torch.randn((count, hidden), device=dev, generator=gen)
+    layer = moe.MoELayer(w13, w13_scales, w2, w2_scales, fused=True)
+    y = layer.forward_rows(rows, counts, starts).clone()
+    again = layer.forward_rows(rows, counts, starts)
+    layer.check_status()
+    assert torch.equal(y, again) and len(layer._plans) == 1
+    for e, count in enumerate(counts):
+        block = slice(starts[e], starts[e] + -(-count // 128) * 128)
+        span = slice(starts[e], starts[e] + count)
+        assert not y[block][count:].any(), "padding rows must stay zero"
+        if count == 0:
+            continue
+        want = moe.expert_reference(
+            rows[span], w13[e], q.from_blocked_scales(w13_scales[e][None], 2 * inter, hidden // 16)[..., 0],
+            w2[e], q.from_blocked_scales(w2_scales[e][None], hidden, inter // 16)[..., 0], fused=True)
+        error = (y[span].float() - want.float()).norm() / want.float().norm()
+        assert torch.isfinite(want).all() and error.item() <= 3e-3, (e, count, error.item())
+    layer.close()
