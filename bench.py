@@ -118,14 +118,21 @@ def measured_hbm_peak() -> tuple[float, str]:
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def recorded_traffic(name: str):
-    """``dram_bytes_per_launch: <int>`` from the workload's ncu summary, or None."""
-    file = TRAFFIC_SUMMARY.get(name)
-    path = REPO / "profiles" / file if file else None
-    if path is None or not path.is_file():
+def summary_traffic(file: str):
+    """The ``dram_bytes_per_launch:`` line of an ncu summary under ``profiles/``: the sum of
+    its byte counts (one per kernel of the step), or None."""
+    path = REPO / "profiles" / file
+    if not path.is_file():
         return None
-    found = re.search(r"dram_bytes_per_launch:\s*([0-9][0-9_,]*)", path.read_text())
-    return int(re.sub(r"[_,]", "", found.group(1))) if found else None
+    found = re.search(r"dram_bytes_per_launch:([^\n]*)", path.read_text())
+    counts = re.findall(r"\b[0-9][0-9_,]{5,}\b", found.group(1)) if found else []
+    return sum(int(re.sub(r"[_,]", "", c)) for c in counts) or None
+
+
+def recorded_traffic(name: str):
+    """DRAM bytes of one launch from the workload's ncu summary, or None."""
+    file = TRAFFIC_SUMMARY.get(name)
+    return summary_traffic(file) if file else None
 
 
 # -- synthetic operands ---------------------------------------------------------------------
@@ -730,11 +737,11 @@ def competitors(device, square_iters: int) -> list[dict]:
     return results
 
 
-def _hbm_line(byts: float, us: float) -> dict:
+def _hbm_line(byts: float, us: float, traffic=None) -> dict:
     peak, peak_kind = measured_hbm_peak()
     achieved = byts / (us * 1e-6) / 1e9
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "traffic": None,
+            "frac": achieved / peak, "traffic": traffic,
             "peak_source": f"{peak_kind} HBM copy bandwidth",
             "algorithmic_bytes_per_launch": byts}
 
@@ -788,7 +795,8 @@ def row_quantiser(device) -> dict:
     byts = rows * k * 2 + rows * k // 2 + rows * k // 16
     return {"row": "f1 activation quantiser", "entry": "nvfp4_quantize",
             "workload": f"bf16 [{rows}, {k}] -> packed e2m1 + blocked ue4m3 scales",
-            "us_per_call": us, "validated": bool(ok), "roofline": _hbm_line(byts, us),
+            "us_per_call": us, "validated": bool(ok),
+            "roofline": _hbm_line(byts, us, summary_traffic("nvfp4_quantize_bf16_8192x8192.md")),
             "note": "timed with its two output allocations from torch's caching allocator"}
 
 
@@ -994,8 +1002,10 @@ def row_moe(device) -> list[dict]:
         row_bytes = routed * (hidden * (0.5 + 1.0 / 16) + 2 * inter * (0.5 + 1.0 / 16)
                               + 2.0 * hidden)
         byts = weight_bytes + row_bytes
+        traffic = (summary_traffic("nvfp4_moe_shard_deepseek_v3_1024_tokens.md")
+                   if tokens == 1024 else None)
         line = (_tensor_line(flops, kernels_us) if flops / 9e15 > byts / 6.5e12
-                else _hbm_line(byts, kernels_us))
+                else _hbm_line(byts, kernels_us, traffic))
         out.append({"row": "f4 MoE layer (expert-parallel shard)",
                     "entry": "nvfp4_group_dual_gemm_bind_fp4 + nvfp4_group_gemm_bind + "
                              "nvfp4_group_gemm_launch x2 + nvfp4_quantize",
