@@ -761,8 +761,11 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
         env_int("NVFP4_TILE_N", 0) > 0 || env_int("NVFP4_SCHEDULE", 0) > 0 ||
         env_int("NVFP4_CTAS", 0) > 0;
     const long long pair_waves = (pair_tiles + sms / 2 - 1) / (sms / 2);
+    // Beside the waves of tiles, a launch of pairs costs about 2.5 us more than a launch of
+    // single CTAs (cluster launch, the pair's barriers at both ends): on 2048^3, one wave
+    // either way, the pairs take 9.8 us and 128 x 256 tiles 7.8 us.
     const double pair_us =
-        static_cast<double>(pair_waves) * (ceil_div(k, 256) * kPairStepUs + 1.2);
+        static_cast<double>(pair_waves) * (ceil_div(k, 256) * kPairStepUs + 1.2) + 2.5;
     plan->pair = want_pair > 0 || (want_pair == 0 && !explicit_choice && kPairByDefault &&
                                    pair_tiles >= sms / 4 && pair_us < chosen_us);
     if (plan->pair) {
