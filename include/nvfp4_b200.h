@@ -231,7 +231,9 @@ int nvfp4_group_dual_gemm_bind_fp4(const nvfp4_plan* plan, const void* const* a,
 
 /* One launch covering every group, reading the group table that
  * nvfp4_group_gemm_bind wrote into `workspace` (one plan may be bound to several
- * workspaces, one per operand set). Replaces NVFP4GroupGEMM._launch
+ * workspaces, one per operand set). The table holds the operands' addresses: every buffer
+ * named at the bind must stay allocated while launches on that workspace can still run.
+ * Replaces NVFP4GroupGEMM._launch
  * (harness/workloads/nvfp4_group_gemm.py:593-600). */
 int nvfp4_group_gemm_launch(const nvfp4_plan* plan, void* workspace, void* stream);
 
