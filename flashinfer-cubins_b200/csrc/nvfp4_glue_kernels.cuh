@@ -99,28 +99,33 @@ __device__ __forceinline__ float nvfp4_scale_value(uint32_t bits) {
 // x / scale == 0.75.) With finite inputs the quotient comes from the correctly rounded
 // reciprocal and two fused multiply-adds, q = x y, q' = q + (x - scale q) y, which is the
 // correctly rounded quotient whenever the divisor's significand is not all ones (a scale has
-// four significant bits): three instructions in place of an IEEE division. Blocks with an
-// infinity take the division itself. A negative value that rounds to zero gets code 0, not -0.
+// four significant bits): three instructions (packed, for two quotients at a time) in place
+// of an IEEE division. Blocks with an infinity take the division itself. A negative value that rounds to zero gets code 0, not -0.
 // Used by the quantiser kernel and by the GEMM epilogues that write NVFP4, so that both produce
 // the same bytes from the same FP32 values.
 __device__ __forceinline__ uint2 nvfp4_block_codes(const float (&v)[16], float amax, float scale) {
-  float quotient[16];
+  float2 quotient[8];
   if (amax <= 3.0e38f) {
+    // Two quotients per instruction (packed FP32 multiply and fused multiply-add).
     const float y = __frcp_rn(scale);
+    const float2 y2 = make_float2(y, y);
+    const float2 minus_scale = make_float2(-scale, -scale);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float q = v[j] * y;
-      quotient[j] = __fmaf_rn(__fmaf_rn(-scale, q, v[j]), y, q);
+    for (int j = 0; j < 8; ++j) {
+      const float2 x = make_float2(v[2 * j], v[2 * j + 1]);
+      const float2 q = __fmul2_rn(x, y2);
+      quotient[j] = __ffma2_rn(__ffma2_rn(minus_scale, q, x), y2, q);
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) quotient[j] = __fdiv_rn(v[j], scale);
+    for (int j = 0; j < 8; ++j) {
+      quotient[j] = make_float2(__fdiv_rn(v[2 * j], scale), __fdiv_rn(v[2 * j + 1], scale));
+    }
   }
   uint32_t words[2] = {0u, 0u};
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const uint32_t pair = __nv_cvt_float2_to_fp4x2(
-        make_float2(quotient[2 * j], quotient[2 * j + 1]), __NV_E2M1, cudaRoundNearest);
+    const uint32_t pair = __nv_cvt_float2_to_fp4x2(quotient[j], __NV_E2M1, cudaRoundNearest);
     words[j / 4] |= pair << (8 * (j % 4));
   }
 #pragma unroll
