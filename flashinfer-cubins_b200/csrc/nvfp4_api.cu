@@ -483,10 +483,12 @@ int default_tile_n(const nvfp4_config* config, int fallback) {
 
 int prepare_kernel(nvfp4_plan* plan) {
   if (plan->pair && plan->kind == kDual) {
-    plan->kernel = make_pair_choice<PairConfig<__half, true>>();
+    plan->kernel = plan->out_kind == NVFP4_OUT_FP4 ? make_pair_choice<PairConfig<Fp4Out, true>>()
+                                                   : make_pair_choice<PairConfig<__half, true>>();
   } else if (plan->pair) {
     plan->kernel = plan->out_kind == NVFP4_OUT_F16    ? make_pair_choice<PairConfig<__half>>()
                    : plan->out_kind == NVFP4_OUT_BF16 ? make_pair_choice<PairConfig<__nv_bfloat16>>()
+                   : plan->out_kind == NVFP4_OUT_FP4  ? make_pair_choice<PairConfig<Fp4Out>>()
                                                       : make_pair_choice<PairConfig<float>>();
   } else {
     plan->kernel = select_kernel(plan->kind, plan->out_kind, plan->tile_n);
@@ -679,11 +681,13 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
     return rc;
   }
   // The NVFP4-output epilogue quantises whole rows of a finished tile: such plans keep
-  // every tile's K in one CTA (data parallel, single-CTA kernel).
+  // every tile's K in one CTA or one pair of CTAs (data parallel).
   nvfp4_config whole_tiles = {};
+  const bool fp4_schedule_left_open =
+      out_kind == NVFP4_OUT_FP4 && (config == nullptr || config->schedule == 0);
   if (out_kind == NVFP4_OUT_FP4) {
     if (config != nullptr) whole_tiles = *config;
-    if (whole_tiles.pair > 0 || whole_tiles.schedule > 1) {
+    if (whole_tiles.schedule > 1) {
       return fail(NVFP4_E_INVALID_ARGUMENT, "NVFP4 output supports the data-parallel schedule only");
     }
     whole_tiles.schedule = 1;
@@ -746,7 +750,6 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
         static_cast<long long>(ceil_div(m, 256)) * ceil_div(n, pair_out_n) * l;
     int want_pair = config != nullptr ? config->pair : 0;
     if (want_pair == 0) want_pair = env_int("NVFP4_PAIR", 0);
-    if (out_kind == NVFP4_OUT_FP4) want_pair = -1;  // whole tiles in one CTA, single-CTA kernel
     // The 2-CTA kernel stores 16-bit output through a tensor map: rows 16-byte aligned.
     if (out_kind != NVFP4_OUT_F32 && n % 8 != 0) {
       if (want_pair > 0) {
@@ -756,8 +759,10 @@ int create_dense_like(nvfp4_plan** out, int kind, int device, int out_kind, int 
       }
       want_pair = -1;
     }
+    // (The data-parallel schedule that NVFP4 output forces above is not the caller's choice.)
     const bool explicit_choice =
-        (config != nullptr && (config->tile_n > 0 || config->schedule > 0 || config->ctas > 0)) ||
+        (config != nullptr && (config->tile_n > 0 || (config->schedule > 0 && !fp4_schedule_left_open) ||
+                               config->ctas > 0)) ||
         env_int("NVFP4_TILE_N", 0) > 0 || env_int("NVFP4_SCHEDULE", 0) > 0 ||
         env_int("NVFP4_CTAS", 0) > 0;
     const long long pair_waves = (pair_tiles + sms / 2 - 1) / (sms / 2);
@@ -1194,7 +1199,7 @@ int launch_dual(const nvfp4_plan* plan, const void* a, const void* b1, const voi
           return rc;
         }
         fresh.map_d = fresh.map_a;
-        if (plan->pair) {
+        if (plan->pair && plan->out_kind != NVFP4_OUT_FP4) {
           if (int rc = encode_output_map(&fresh.map_d, d, pd.m, pd.n, pd.batches)) return rc;
         }
         pd.sfa = static_cast<const uint8_t*>(sfa);

@@ -109,7 +109,11 @@ struct PairConfig {
   static constexpr int THREADS = 448;
   // 16-bit outputs leave through staged tensor stores; FP32 through per-thread stores.
   static constexpr bool TMA_STORE = sizeof(OutT_) == 2;
-  static constexpr int STAGING_BYTES = TMA_STORE ? 2 * 16384 : 4 * 2048;
+  // D quantised to NVFP4 (Fp4Out, the one one-byte tag): per-thread stores of packed codes
+  // and scale words, both epilogue groups at work as for 16-bit output.
+  static constexpr bool FP4_OUT = sizeof(OutT_) == 1;
+  static constexpr bool TWO_GROUPS = TMA_STORE || FP4_OUT;
+  static constexpr int STAGING_BYTES = TMA_STORE ? 2 * 16384 : FP4_OUT ? 1024 : 4 * 2048;
   static_assert(SF_COL + STAGES * SF_STAGE_COLS <= TMEM_COLS, "tensor memory exceeded");
 };
 
@@ -146,7 +150,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
     }
     mbar_init(smem_u32(&bar_acc_full), 1);
     // One arrival per epilogue warp of both CTAs (16-bit output: eight warps per CTA).
-    mbar_init(smem_u32(&bar_acc_empty), Cfg::TMA_STORE ? 16 : 8);
+    mbar_init(smem_u32(&bar_acc_empty), Cfg::TWO_GROUPS ? 16 : 8);
     abort_flag = 0;
     mbar_fence_init();
   }
@@ -388,6 +392,106 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ KernelParams p) {
           sf_smem = smem_base + Cfg::A_BYTES + Cfg::B_BYTES;
           t_sf = tmem_base + lane_base + Cfg::SF_COL;
         }
+      }
+    }
+  } else if (Cfg::FP4_OUT) {
+    // ------------------------------------------------------------------ epilogue, NVFP4 D
+    // Two groups of four warps, each owning half of the tile's output columns; a thread owns
+    // one row of them. Per 32 columns: two block scales and 32 codes with the quantiser
+    // kernel's arithmetic (nvfp4_block_codes), so the bytes equal quantising the FP32 result.
+    // The accumulator goes back to the MMA issuer once the group's last chunk is in
+    // registers; packed codes (16 bytes per 32 columns) and scale words (four scale bytes per
+    // 64 columns, contiguous in the blocked layout) are stored by the thread itself.
+    if constexpr (Cfg::FP4_OUT) {
+      const int group = warp >= 10 ? 1 : 0;
+      const int quarter = warp & 3;
+      const int row = quarter * 32 + lane;
+      const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
+      const uint32_t leader_acc_empty = cluster_map_shared(smem_u32(&bar_acc_empty), 0);
+      constexpr int GROUP_COLS = Cfg::DUAL ? 64 : 128;
+      constexpr int CHUNKS = GROUP_COLS / 32;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(group * GROUP_COLS);
+      uint32_t acc_phase = 0;
+      for (long long t = first_tile; t < tiles; t += pairs) {
+        int batch, m_tile, n_tile;
+        decode(t, batch, m_tile, n_tile);
+        if (!mbar_wait(smem_u32(&bar_acc_full), acc_phase, abort_ptr)) {
+          report_failure(p, abort_ptr, kStatusEpilogueTimeout);
+          break;
+        }
+        tc_fence_after_sync();
+        const int row_block = m_tile * 2 + static_cast<int>(rank);  // 128-row block of D
+        const int grow = row_block * 128 + row;
+        const int col0 = n_tile * Cfg::OUT_N + group * GROUP_COLS;
+        uint32_t words[CHUNKS][4];
+        uint32_t scale_word[CHUNKS / 2];
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          uint32_t r1[32];
+          tmem_load_32(taddr + c * 32, r1);
+          if constexpr (Cfg::DUAL) {
+            uint32_t r2[32];
+            tmem_load_32(taddr + 128 + c * 32, r2);
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              r1[i] = __float_as_uint(silu_f32(__uint_as_float(r1[i]) * alpha) *
+                                      (__uint_as_float(r2[i]) * alpha));
+            }
+          } else {
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r1[i] = __float_as_uint(__uint_as_float(r1[i]) * alpha);
+          }
+          if (c == CHUNKS - 1) {
+            // Everything this warp needs has left tensor memory: hand the accumulator back.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_peer(leader_acc_empty);
+          }
+          if (c % 2 == 0) scale_word[c / 2] = 0;
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            float v[16];
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              v[i] = __uint_as_float(r1[16 * blk + i]);
+              amax = fmaxf(amax, fabsf(v[i]));
+            }
+            const uint32_t bits = nvfp4_scale_bits(amax);
+            const float scale = nvfp4_scale_value(bits);
+            scale_word[c / 2] |= bits << (8 * (2 * (c % 2) + blk));
+            const uint2 codes =
+                scale > 0.0f ? nvfp4_block_codes(v, amax, scale) : make_uint2(0u, 0u);
+            words[c][2 * blk] = codes.x;
+            words[c][2 * blk + 1] = codes.y;
+          }
+        }
+        if (grow < pd.m) {
+          uint8_t* d_row = static_cast<uint8_t*>(pd.d) +
+                           (static_cast<long long>(batch) * pd.m + grow) * (pd.n / 2);
+          const int sf_cb = (pd.n + 63) / 64;
+          uint8_t* sf_row = pd.sfd +
+                            (static_cast<long long>(batch) * pd.sf_mb + row_block) * sf_cb * 512 +
+                            (row % 32) * 16 + ((row / 32) % 4) * 4;
+#pragma unroll
+          for (int c = 0; c < CHUNKS; ++c) {
+            if (col0 + c * 32 < pd.n) {
+              *reinterpret_cast<uint4*>(d_row + (col0 + c * 32) / 2) =
+                  make_uint4(words[c][0], words[c][1], words[c][2], words[c][3]);
+            }
+          }
+#pragma unroll
+          for (int h = 0; h < CHUNKS / 2; ++h) {
+            if (col0 + h * 64 < pd.n) {
+              *reinterpret_cast<uint32_t*>(sf_row + static_cast<long long>((col0 + h * 64) / 64) * 512) =
+                  scale_word[h];
+            }
+          }
+        }
+        acc_phase ^= 1u;
       }
     }
   } else if (Cfg::TMA_STORE) {

@@ -651,6 +651,80 @@ def test_mma_issue_peak_measurement_is_plausible():
         native.measure_mma_peak(0, 0)
 
 
+@pytest.mark.parametrize("m,n,k,batches", [(256, 256, 256, 1), (300, 576, 608, 2), (1024, 2048, 1024, 1)])
+@pytest.mark.parametrize("scales", ("int0_3", "uniform"))
+def test_pair_kernel_with_nvfp4_output(m, n, k, batches, scales):
+    """The 2-CTA kernel's NVFP4 epilogue (partial tiles in M, N and K, batches): packed codes
+    and blocked scales equal, byte for byte, the quantiser kernel applied to the FP32 output
+    of the same kernel, and (integer scales: sums exact in any order) the single-CTA plan's."""
+    from harness.workloads import quantization as q
+    a, b, sa, sb = _fp4_out_inputs(m, n, k, batches, scales, seed=m + n + k + 1)
+    alpha = torch.tensor([0.25], dtype=torch.float32, device=a.device)
+    sfa, sfb = q.to_blocked_scales(sa), q.to_blocked_scales(sb)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run(out_kind, **config):
+        plan = native.Plan.dense(0, out_kind, m, n, k, batches, **config)
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=a.device)
+        plan.init_workspace(ws.data_ptr(), stream)
+        if out_kind == native.OUT_FP4:
+            packed = torch.full((batches, m, n // 2), 0xEE, dtype=torch.uint8, device=a.device)
+            blocked = torch.zeros((batches, -(-m // 128), n // 64, 32, 4, 4), dtype=torch.uint8,
+                                  device=a.device)
+            plan.launch_dense_fp4(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                                  alpha.data_ptr(), packed.data_ptr(), blocked.data_ptr(),
+                                  ws.data_ptr(), stream)
+            out = (packed, blocked)
+        else:
+            d = torch.empty((batches, m, n), dtype=torch.float32, device=a.device)
+            plan.launch_dense(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                              alpha.data_ptr(), d.data_ptr(), ws.data_ptr(), stream)
+            out = d
+        assert plan.status(ws.data_ptr(), stream) == 0
+        info = plan.info()
+        plan.destroy()
+        return out, info
+
+    (packed, blocked), info = run(native.OUT_FP4, pair=1)
+    assert info["tile_m"] == 256 and info["tile_n"] == 256, info
+    product, _ = run(native.OUT_F32, pair=1)
+    want_packed, want_scales = q.quantize_nvfp4_native(product.permute(1, 2, 0))
+    assert torch.equal(packed, want_packed.permute(2, 0, 1))
+    assert torch.equal(blocked, want_scales.view(torch.uint8))
+    if scales == "int0_3":
+        (single_packed, single_blocked), single = run(native.OUT_FP4, pair=-1)
+        assert single["tile_m"] == 128
+        assert torch.equal(packed, single_packed) and torch.equal(blocked, single_blocked)
+
+
+@pytest.mark.parametrize("m,n,k,l", [(256, 128, 256, 1), (300, 320, 608, 2), (512, 1024, 2080, 1)])
+def test_dual_pair_kernel_with_nvfp4_output(m, n, k, l):  # noqa: E741
+    """Gate/up dual GEMM with NVFP4 output on the 2-CTA kernel against the single-CTA plan:
+    integer scales, so both epilogues see the same FP32 sums and must write the same bytes."""
+    from harness import CaseSpec
+    workload = get_workload("nvfp4_dual_gemm")(None, device="cuda")
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    case = CaseSpec("dual_fp4_pair", {"m": m, "n": n, "k": k, "l": l, "alpha": 0.0625,
+                                      "scales": "int0_3"}, 52)
+    inputs = workload.get_inputs(case)
+    results = []
+    for config in ({"pair": 1}, {"pair": -1}):
+        plan = native.Plan.dual_fp4(0, m, n, k, l, **config)
+        ws = torch.empty(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=dev)
+        plan.init_workspace(ws.data_ptr(), stream)
+        packed = torch.zeros((l, m, n // 2), dtype=torch.uint8, device=dev)
+        blocked = torch.zeros((l, -(-m // 128), n // 64, 32, 4, 4), dtype=torch.uint8, device=dev)
+        plan.launch_dual_fp4(*(t.data_ptr() for t in inputs), packed.data_ptr(),
+                             blocked.data_ptr(), ws.data_ptr(), stream)
+        assert plan.status(ws.data_ptr(), stream) == 0
+        results.append((packed, blocked, plan.info()))
+        plan.destroy()
+    assert results[0][2]["tile_m"] == 256 and results[1][2]["tile_m"] == 128
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    assert results[0][0].any()
+
+
 @pytest.mark.parametrize("m,n,k,l,tile_n", [(256, 512, 1024, 1, 0), (200, 192, 2080, 2, 128), (130, 320, 512, 1, 256)])
 def test_dual_gemm_with_nvfp4_output(m, n, k, l, tile_n):  # noqa: E741
     """Gate/up dual GEMM quantised to NVFP4 in its epilogue. The kernel's silu uses
