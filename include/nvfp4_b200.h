@@ -60,8 +60,8 @@ typedef struct nvfp4_config {
                    through the workspace), 3 = cluster split-K (partials through peer
                    shared memory; dense and dual GEMM with fewer tiles than SMs only) */
   int ctas;     /* persistent grid size, at most the SM count */
-  int pair;     /* dense GEMM: 1 = 256 x 256 tiles on pairs of CTAs (tcgen05.mma
-                   cta_group::2), -1 = never, 0 = automatic */
+  int pair;     /* dense and dual GEMM: 1 = 256 x 256 tiles (dual: 256 x 128 output tiles) on
+                   pairs of CTAs (tcgen05.mma cta_group::2), -1 = never, 0 = automatic */
 } nvfp4_config;
 
 /* What a plan decided; filled by nvfp4_plan_info. */
@@ -145,7 +145,8 @@ int nvfp4_gemm_launch(const nvfp4_plan* plan, const void* a, const void* b, cons
 
 /* Dense GEMM whose output is quantised to NVFP4 in the epilogue, so that it can be the A
  * operand of the next GEMM without an FP16 round trip (plan created with NVFP4_OUT_FP4;
- * n % 64 == 0; data-parallel schedule). The reference has no such kernel on this path: its
+ * n % 64 == 0; data-parallel schedule, on single CTAs or on pairs). The reference has no
+ * such kernel on this path: its
  * NVFP4 convention for a quantised tensor (scale = e4m3(amax / 6) per 16 elements, RNE
  * E2M1 codes, blocked scales: harness/workloads/quantization.py:66-116 and 39-63) is what
  * the bytes follow. `d_packed` is [l][m][n/2] bytes, `d_scales` the blocked layout
@@ -157,8 +158,8 @@ int nvfp4_gemm_launch_fp4(const nvfp4_plan* plan, const void* a, const void* b, 
 
 /* The fused dual GEMM with its gated output quantised to NVFP4 in the epilogue: gate/up
  * projection -> packed E2M1 + blocked scales that the down projection's GEMM takes as its A
- * operand. Same conventions as nvfp4_gemm_launch_fp4 (n % 64 == 0, data-parallel schedule,
- * single-CTA kernel); silu is evaluated with ex2.approx / rcp.approx, so codes at E2M1
+ * operand. Same conventions as nvfp4_gemm_launch_fp4 (n % 64 == 0, data-parallel
+ * schedule); silu is evaluated with ex2.approx / rcp.approx, so codes at E2M1
  * rounding boundaries can differ from an exactly rounded silu. No counterpart in the
  * reference. */
 int nvfp4_dual_gemm_plan_create_fp4(nvfp4_plan** plan, int device, int m, int n, int k, int l,
