@@ -944,7 +944,8 @@ def row_moe(device) -> list[dict]:
     way, harness/workloads/nvfp4_group_gemm.py:751-785 there): the rows routed to this rank at
     1,024 and 16,384 tokens, per-expert counts seeded log-normal. ``layer_us`` is
     ``MoELayer.forward_rows`` (quantiser and two grouped launches on the pattern's bound
-    buffers); ``kernels_us`` the two grouped launches alone replayed from a graph. The busiest
+    buffers) called from Python, ``layer_graph_us`` the same forward replayed from a CUDA
+    graph; ``kernels_us`` the two grouped launches alone replayed from a graph. The busiest
     expert's rows are checked against the stage-by-stage torch reference."""
     from harness import moe
     from harness.models import MODELS
@@ -1011,6 +1012,24 @@ def row_moe(device) -> list[dict]:
             pattern.down_plan.launch_groups(pattern.down_ws.data_ptr(), stream)
 
         kernels_us = replay_us(kernels, 1, 20)
+        # The whole forward of a known pattern is three launches on bound buffers, so it can be
+        # captured: the layer without the host's share.
+        side = torch.cuda.Stream(device)
+        with torch.cuda.stream(side):
+            layer.forward_rows(rows, counts, starts)  # the pattern's buffers on this stream
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    layer.forward_rows(rows, counts, starts)
+            graph.replay()
+            side.synchronize()
+            start.record(side)
+            graph.replay()
+            stop.record(side)
+            side.synchronize()
+        layer_graph_us = start.elapsed_time(stop) * 1e3 / 20
+        del graph
         layer.check_status()
         del y
         live = sum(1 for count in counts if count)
@@ -1029,7 +1048,8 @@ def row_moe(device) -> list[dict]:
                     "workload": f"deepseek_v3 experts, {local} local of {spec.experts}, "
                                 f"{tokens} tokens -> {routed} routed rows, {live} live experts, "
                                 f"hidden {hidden}, intermediate {inter}",
-                    "layer_us": layer_us, "kernels_us": kernels_us,
+                    "layer_us": layer_us, "layer_graph_us": layer_graph_us,
+                    "kernels_us": kernels_us,
                     "us_per_call": kernels_us, "tflops": flops / kernels_us / 1e6,
                     "validated": bool(error < 1e-2), "relative_error_of_probed_expert": error,
                     "roofline": line,

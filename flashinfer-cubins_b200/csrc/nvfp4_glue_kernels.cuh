@@ -156,22 +156,31 @@ constexpr int kQuantRowsY = 4;
 constexpr int kQuantRowsPerThread = 4;
 constexpr int kQuantRowsPerCta = kQuantRowsY * kQuantRowsPerThread;
 
-template <typename In>
+template <typename In, bool RAGGED>
 __global__ void __launch_bounds__(kQuantBlocksX* kQuantRowsY)
 quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
-                      uint8_t* __restrict__ scales, int rows, int k, int batches) {
+                      uint8_t* __restrict__ scales, int rows, int k, int batches,
+                      const int* __restrict__ block_rows) {
   constexpr int kVectors = sizeof(In) == 4 ? 4 : 2;  // 16-byte loads per block
   const int cols = k / 16;
   const int rb = (rows + 127) / 128;
   const int cb = (cols + 3) / 4;
   const int c = blockIdx.y * kQuantBlocksX + threadIdx.x;
   const int r0 = blockIdx.x * kQuantRowsPerCta + threadIdx.y;
+  // Ragged rows (one batch): only the first block_rows[b] rows of 128-row block b hold data;
+  // the others are neither read nor written (their codes and scales stay as they are). A
+  // CTA's sixteen rows lie in one block.
+  int live_rows = rows;
+  if constexpr (RAGGED) {
+    live_rows = min(rows, (r0 / 128) * 128 + __ldg(block_rows + r0 / 128));
+    if (static_cast<int>(blockIdx.x) * kQuantRowsPerCta >= live_rows) return;
+  }
   for (int batch = blockIdx.z; batch < batches; batch += gridDim.z) {
     uint4 raw[kQuantRowsPerThread][kVectors];
 #pragma unroll
     for (int i = 0; i < kQuantRowsPerThread; ++i) {
       const int r = r0 + kQuantRowsY * i;
-      if (r < rows && c < cols) {
+      if (r < live_rows && c < cols) {
         const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
         const uint4* src = reinterpret_cast<const uint4*>(x + element);
 #pragma unroll
@@ -182,7 +191,7 @@ quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
     for (int i = 0; i < kQuantRowsPerThread; ++i) {
       const int r = r0 + kQuantRowsY * i;
       uint32_t scale_bits = 0;
-      if (r < rows && c < cols) {
+      if (r < live_rows && c < cols) {
         const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
         float v[16];
 #pragma unroll
@@ -211,7 +220,7 @@ quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
       uint32_t word = scale_bits << (8 * (threadIdx.x & 3));
       word |= __shfl_xor_sync(0xFFFFFFFFu, word, 1);
       word |= __shfl_xor_sync(0xFFFFFFFFu, word, 2);
-      if ((threadIdx.x & 3) == 0 && c < cb * 4) {
+      if ((threadIdx.x & 3) == 0 && c < cb * 4 && (!RAGGED || r < live_rows)) {
         const long long atom = (static_cast<long long>(batch) * rb + r / 128) * cb + c / 4;
         *reinterpret_cast<uint32_t*>(scales + atom * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4) =
             word;

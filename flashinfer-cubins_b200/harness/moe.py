@@ -94,7 +94,8 @@ class _Pattern:
     once and bound to the plans once. Every expert's block starts on a 128-row boundary, so
     the buffers are whole tensors that each group addresses by offset:
 
-    * ``a1`` / ``s1``: the quantised rows (packed ``[R, H/2]``, blocked scales);
+    * ``a1`` / ``s1``: the quantised rows (packed ``[R, H/2]``, blocked scales), written by
+      the quantiser for the rows that hold data only (``block_rows``);
     * ``a2`` / ``s2``: the gated intermediate in NVFP4 (written by the fused gate/up kernel,
       or by the quantiser after ``h`` FP16 ``[R, 2I]`` when not fused). The kernels write
       only rows that exist, so padding rows and their scales stay zero;
@@ -132,6 +133,13 @@ class _Pattern:
         self.s2 = torch.zeros((blocks, atoms_i, 32, 4, 4), **byte)
         self.y = torch.zeros((total, hidden), dtype=torch.float16, device=device)
         self.h = None
+        # Rows that hold data in every 128-row block, for the quantiser: padding rows are
+        # zero in these buffers from the start and are never read or written again.
+        filled = []
+        for count in counts:
+            blocks_of = -(-count // ROW_BLOCK)
+            filled += [min(ROW_BLOCK, count - ROW_BLOCK * b) for b in range(blocks_of)]
+        self.block_rows = torch.tensor(filled, dtype=torch.int32, device=device)
         a_ptrs = [self.a1.data_ptr() + starts[e] * (hidden // 2) for e in live]
         sa_ptrs = [self.s1.data_ptr() + (starts[e] // ROW_BLOCK) * atoms_h * 512 for e in live]
         a2_ptrs = [self.a2.data_ptr() + starts[e] * (inter // 2) for e in live]
@@ -239,14 +247,16 @@ class MoELayer:
                 raise ValueError("rows are not laid out in 128-row blocks per expert")
             if rows.dtype != torch.float32 or not rows.is_contiguous():
                 rows = rows.float().contiguous()
-            native.quantize(rows.data_ptr(), native.IN_F32, pattern.a1.data_ptr(),
-                            pattern.s1.data_ptr(), pattern.total, hidden, 1, stream)
+            native.quantize_blocks(rows.data_ptr(), native.IN_F32, pattern.a1.data_ptr(),
+                                   pattern.s1.data_ptr(), pattern.total, hidden,
+                                   pattern.block_rows.data_ptr(), stream)
             pattern.up_plan.launch_groups(pattern.up_ws.data_ptr(), stream)
             if not self.fused:
                 h = pattern.h
                 act = torch.nn.functional.silu(h[:, :inter].float()) * h[:, inter:].float()
-                native.quantize(act.data_ptr(), native.IN_F32, pattern.a2.data_ptr(),
-                                pattern.s2.data_ptr(), pattern.total, inter, 1, stream)
+                native.quantize_blocks(act.data_ptr(), native.IN_F32, pattern.a2.data_ptr(),
+                                       pattern.s2.data_ptr(), pattern.total, inter,
+                                       pattern.block_rows.data_ptr(), stream)
             pattern.down_plan.launch_groups(pattern.down_ws.data_ptr(), stream)
         return pattern.y
 

@@ -279,6 +279,14 @@ int nvfp4_pack_scales(const void* scales, void* packed, int rows, int cols, int 
 int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
                    int batches, void* stream);
 
+/* The same for rows that come in 128-row blocks of which only the first block_rows[b] rows
+ * hold data (the permuted rows of a mixture-of-experts layer, every expert's rows padded to
+ * whole blocks): `block_rows` is a device array of ceil(rows / 128) counts in [0, 128]. Rows
+ * beyond a block's count are neither read nor written: their codes and scales keep what the
+ * buffers held (zeros, in buffers that were zeroed once). One batch. */
+int nvfp4_quantize_blocks(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
+                          const int* block_rows, void* stream);
+
 /* out[i] = half(silu(h1[i]) * h2[i]) over `size` FP32 elements. Replaces the
  * silu_product kernel (impls/nvfp4_dual_gemm/kernels/silu_product.cu:7-9,
  * harness/workloads/nvfp4_dual_gemm.py:352-367). */

@@ -71,6 +71,42 @@ def test_moe_layer_matches_stagewise_reference(tokens, hidden, inter, experts, c
         moe.MoELayer(w13, w13_blocked, w2[:, :, :-8], w2_blocked)
 
 
+def test_forward_of_a_known_pattern_can_be_captured_in_a_graph():
+    """A forward with a routing pattern seen before allocates, encodes and binds nothing: it
+    can be captured in a CUDA graph, and the replay gives the same bits on new activations."""
+    device = torch.device("cuda:0")
+    tokens, hidden, inter, experts, choices = 300, 512, 256, 5, 2
+    ids, _ = routing(tokens, experts, choices, 8, device)
+    w13, _, w13_blocked = quantised_weights(experts, 2 * inter, hidden, 1, device)
+    w2, _, w2_blocked = quantised_weights(experts, hidden, inter, 2, device)
+    layer = moe.MoELayer(w13, w13_blocked, w2, w2_blocked)
+    source, counts, starts = moe.route_rows(ids, experts)
+    gen = torch.Generator().manual_seed(9)
+    first = moe._gather(torch.randn(tokens, hidden, generator=gen).to(device), source, choices)
+    second = moe._gather(torch.randn(tokens, hidden, generator=gen).to(device), source, choices)
+    rows = first.clone()
+    side = torch.cuda.Stream(device)
+    with torch.cuda.stream(side):
+        want_first = layer.forward_rows(rows, counts, starts).clone()   # creates the pattern
+        rows.copy_(second)
+        want_second = layer.forward_rows(rows, counts, starts).clone()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            y = layer.forward_rows(rows, counts, starts)
+        rows.copy_(first)
+        graph.replay()
+        side.synchronize()
+        assert torch.equal(y, want_first)
+        rows.copy_(second)
+        graph.replay()
+        side.synchronize()
+        assert torch.equal(y, want_second) and not torch.equal(want_first, want_second)
+    layer.check_status()
+    assert len(layer._plans) == 1
+    layer.close()
+
+
 def test_fused_and_unfused_layers_agree():
     device = torch.device("cuda:0")
     tokens, hidden, inter, experts, choices = 300, 512, 256, 5, 2

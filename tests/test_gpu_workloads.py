@@ -536,6 +536,38 @@ def test_quantiser_kernel_on_ties_and_their_neighbours():
     assert torch.equal(packed, want_packed)
 
 
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
+def test_quantiser_on_ragged_blocks_leaves_the_other_rows_alone(dtype):
+    """nvfp4_quantize_blocks: the leading rows of every 128-row block are quantised exactly as
+    nvfp4_quantize does; rows beyond a block's count keep what the buffers held (here a
+    marker), in the codes and in the scales."""
+    from harness.workloads import quantization as q
+    filled = [128, 5, 0, 77, 128, 1]
+    rows, k = 128 * len(filled), 7168
+    x = torch.randn((1, rows, k), generator=torch.Generator().manual_seed(3)).to(dtype).cuda()
+    want_packed, want_blocked = q.quantize_nvfp4_native(x.permute(1, 2, 0))
+    packed = torch.full((rows, k // 2), 0xAB, dtype=torch.uint8, device="cuda")
+    blocked = torch.full((len(filled), k // 64, 32, 4, 4), 0xCD, dtype=torch.uint8, device="cuda")
+    counts = torch.tensor(filled, dtype=torch.int32, device="cuda")
+    native.quantize_blocks(x.data_ptr(), native.IN_F32 if dtype == torch.float32 else native.IN_BF16,
+                           packed.data_ptr(), blocked.data_ptr(), rows, k, counts.data_ptr(),
+                           torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    live = torch.zeros(rows, dtype=torch.bool, device="cuda")
+    for b, count in enumerate(filled):
+        live[128 * b:128 * b + count] = True
+    assert torch.equal(packed[live], want_packed[..., 0][live])
+    assert (packed[~live] == 0xAB).all()
+    # Scale byte (r, c) sits at [r / 128][c / 4][r % 32][(r / 32) % 4][c % 4].
+    got = blocked.permute(0, 3, 2, 1, 4).reshape(rows, k // 16)      # [block][r/32%4][r%32] -> row
+    want = want_blocked.view(torch.uint8)[0].permute(0, 3, 2, 1, 4).reshape(rows, k // 16)
+    assert torch.equal(got[live], want[live])
+    assert (got[~live] == 0xCD).all()
+    with pytest.raises(ValueError):
+        native.quantize_blocks(x.data_ptr(), native.IN_F32, packed.data_ptr(), blocked.data_ptr(),
+                               rows, k, 0, 0)
+
+
 def _fp4_out_inputs(m, n, k, batches, scales, seed):
     from harness.workloads import quantization as q
     workload = get_workload("nvfp4_gemm")(None, device="cuda")
