@@ -1406,27 +1406,23 @@ int nvfp4_pack_scales(const void* scales, void* packed, int rows, int cols, int 
   return 0;
 }
 
+}  // extern "C"
+
 namespace {
-int quantize_launch(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
-                    int batches, const int* block_rows, void* stream);
-}
-
-int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
-                   int batches, void* stream) {
-  return quantize_launch(x, x_kind, packed, scales, rows, k, batches, nullptr, stream);
-}
-
-int nvfp4_quantize_blocks(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
-                          const int* block_rows, void* stream) {
-  if (block_rows == nullptr || !aligned(block_rows, 4)) {
-    return fail(NVFP4_E_INVALID_ARGUMENT, "block_rows is null or misaligned");
+template <typename In>
+void quantize_dispatch(dim3 grid, dim3 block, cudaStream_t s, int mode, const In* in, uint8_t* p8,
+                       uint8_t* s8, int rows, int k, int batches, const int* info) {
+  if (mode == kQuantBlocks) {
+    quantize_nvfp4_kernel<In, kQuantBlocks><<<grid, block, 0, s>>>(in, p8, s8, rows, k, batches, info);
+  } else if (mode == kQuantGather) {
+    quantize_nvfp4_kernel<In, kQuantGather><<<grid, block, 0, s>>>(in, p8, s8, rows, k, batches, info);
+  } else {
+    quantize_nvfp4_kernel<In, kQuantDense><<<grid, block, 0, s>>>(in, p8, s8, rows, k, batches, nullptr);
   }
-  return quantize_launch(x, x_kind, packed, scales, rows, k, 1, block_rows, stream);
 }
 
-namespace {
 int quantize_launch(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
-                    int batches, const int* block_rows, void* stream) {
+                    int batches, int mode, const int* info, void* stream) {
   if (x == nullptr || packed == nullptr || scales == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
   }
@@ -1452,28 +1448,40 @@ int quantize_launch(const void* x, int x_kind, void* packed, void* scales, int r
   uint8_t* p8 = static_cast<uint8_t*>(packed);
   uint8_t* s8 = static_cast<uint8_t*>(scales);
   if (x_kind == NVFP4_IN_F32) {
-    const float* in = static_cast<const float*>(x);
-    if (block_rows != nullptr) {
-      quantize_nvfp4_kernel<float, true><<<grid, block, 0, s>>>(in, p8, s8, rows, k, batches,
-                                                                block_rows);
-    } else {
-      quantize_nvfp4_kernel<float, false><<<grid, block, 0, s>>>(in, p8, s8, rows, k, batches,
-                                                                 nullptr);
-    }
+    quantize_dispatch(grid, block, s, mode, static_cast<const float*>(x), p8, s8, rows, k, batches,
+                      info);
   } else {
-    const __nv_bfloat16* in = static_cast<const __nv_bfloat16*>(x);
-    if (block_rows != nullptr) {
-      quantize_nvfp4_kernel<__nv_bfloat16, true><<<grid, block, 0, s>>>(in, p8, s8, rows, k,
-                                                                        batches, block_rows);
-    } else {
-      quantize_nvfp4_kernel<__nv_bfloat16, false><<<grid, block, 0, s>>>(in, p8, s8, rows, k,
-                                                                         batches, nullptr);
-    }
+    quantize_dispatch(grid, block, s, mode, static_cast<const __nv_bfloat16*>(x), p8, s8, rows, k,
+                      batches, info);
   }
   CUDA_TRY(cudaGetLastError());
   return 0;
 }
 }  // namespace
+
+extern "C" {
+
+int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
+                   int batches, void* stream) {
+  return quantize_launch(x, x_kind, packed, scales, rows, k, batches, kQuantDense, nullptr, stream);
+}
+
+int nvfp4_quantize_blocks(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
+                          const int* block_rows, void* stream) {
+  if (block_rows == nullptr || !aligned(block_rows, 4)) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "block_rows is null or misaligned");
+  }
+  return quantize_launch(x, x_kind, packed, scales, rows, k, 1, kQuantBlocks, block_rows, stream);
+}
+
+int nvfp4_quantize_gather(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
+                          const int* source_rows, void* stream) {
+  if (source_rows == nullptr || !aligned(source_rows, 4)) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "source_rows is null or misaligned");
+  }
+  return quantize_launch(x, x_kind, packed, scales, rows, k, 1, kQuantGather, source_rows, stream);
+}
+
 
 int nvfp4_measure_mma_peak(int device, int iters, double* tflops) {
   if (tflops == nullptr || iters < 1 || iters > (1 << 22)) {

@@ -156,32 +156,48 @@ constexpr int kQuantRowsY = 4;
 constexpr int kQuantRowsPerThread = 4;
 constexpr int kQuantRowsPerCta = kQuantRowsY * kQuantRowsPerThread;
 
-template <typename In, bool RAGGED>
+// MODE 0: every row of x[batches][rows][k]. MODE 1 (one batch): rows come in 128-row blocks of
+// which only the first info[b] rows hold data. MODE 2 (one batch): output row r is input row
+// info[r] of x, or nothing if info[r] < 0 (a gather: the permuted rows of a mixture-of-experts
+// layer straight from the token activations). In modes 1 and 2 the rows without data are
+// neither read nor written: their codes and scales keep what the buffers held.
+constexpr int kQuantDense = 0, kQuantBlocks = 1, kQuantGather = 2;
+
+template <typename In, int MODE>
 __global__ void __launch_bounds__(kQuantBlocksX* kQuantRowsY)
 quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
                       uint8_t* __restrict__ scales, int rows, int k, int batches,
-                      const int* __restrict__ block_rows) {
+                      const int* __restrict__ info) {
   constexpr int kVectors = sizeof(In) == 4 ? 4 : 2;  // 16-byte loads per block
   const int cols = k / 16;
   const int rb = (rows + 127) / 128;
   const int cb = (cols + 3) / 4;
   const int c = blockIdx.y * kQuantBlocksX + threadIdx.x;
   const int r0 = blockIdx.x * kQuantRowsPerCta + threadIdx.y;
-  // Ragged rows (one batch): only the first block_rows[b] rows of 128-row block b hold data;
-  // the others are neither read nor written (their codes and scales stay as they are). A
-  // CTA's sixteen rows lie in one block.
   int live_rows = rows;
-  if constexpr (RAGGED) {
-    live_rows = min(rows, (r0 / 128) * 128 + __ldg(block_rows + r0 / 128));
+  if constexpr (MODE == kQuantBlocks) {
+    // A CTA's sixteen rows lie in one block.
+    live_rows = min(rows, (r0 / 128) * 128 + __ldg(info + r0 / 128));
     if (static_cast<int>(blockIdx.x) * kQuantRowsPerCta >= live_rows) return;
+  }
+  // The input row of each of this thread's rows, or -1.
+  int source[kQuantRowsPerThread];
+#pragma unroll
+  for (int i = 0; i < kQuantRowsPerThread; ++i) {
+    const int r = r0 + kQuantRowsY * i;
+    if constexpr (MODE == kQuantGather) {
+      source[i] = r < rows ? __ldg(info + r) : -1;
+    } else {
+      source[i] = r < live_rows ? r : -1;
+    }
   }
   for (int batch = blockIdx.z; batch < batches; batch += gridDim.z) {
     uint4 raw[kQuantRowsPerThread][kVectors];
 #pragma unroll
     for (int i = 0; i < kQuantRowsPerThread; ++i) {
-      const int r = r0 + kQuantRowsY * i;
-      if (r < live_rows && c < cols) {
-        const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
+      if (source[i] >= 0 && c < cols) {
+        const long long element =
+            (static_cast<long long>(batch) * rows + source[i]) * k + c * 16;
         const uint4* src = reinterpret_cast<const uint4*>(x + element);
 #pragma unroll
         for (int q = 0; q < kVectors; ++q) raw[i][q] = src[q];
@@ -191,7 +207,7 @@ quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
     for (int i = 0; i < kQuantRowsPerThread; ++i) {
       const int r = r0 + kQuantRowsY * i;
       uint32_t scale_bits = 0;
-      if (r < live_rows && c < cols) {
+      if (source[i] >= 0 && c < cols) {
         const long long element = (static_cast<long long>(batch) * rows + r) * k + c * 16;
         float v[16];
 #pragma unroll
@@ -216,11 +232,11 @@ quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
         *reinterpret_cast<uint2*>(packed + element / 2) = codes;
       }
       // Scale bytes of blocks c..c+3 (c a multiple of four) of row r are one aligned word of
-      // the atom; padding rows and columns of the grid get zeros.
+      // the atom; in mode 0 padding rows and columns of the grid get zeros.
       uint32_t word = scale_bits << (8 * (threadIdx.x & 3));
       word |= __shfl_xor_sync(0xFFFFFFFFu, word, 1);
       word |= __shfl_xor_sync(0xFFFFFFFFu, word, 2);
-      if ((threadIdx.x & 3) == 0 && c < cb * 4 && (!RAGGED || r < live_rows)) {
+      if ((threadIdx.x & 3) == 0 && c < cb * 4 && (MODE == kQuantDense || source[i] >= 0)) {
         const long long atom = (static_cast<long long>(batch) * rb + r / 128) * cb + c / 4;
         *reinterpret_cast<uint32_t*>(scales + atom * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4) =
             word;

@@ -1,7 +1,7 @@
 """A mixture-of-experts feed-forward layer on the NVFP4 kernels of this package, on one GPU
 or expert-parallel over several.
 
-    tokens -> route -> permute by expert -> quantise
+    tokens -> route -> quantise into rows permuted by expert (one gathering launch)
            -> grouped gate/up dual GEMM, gated and re-quantised in its epilogue   (one launch)
            -> grouped down GEMM                                                  (one launch)
            -> weighted un-permutation
@@ -229,27 +229,19 @@ class MoELayer:
         self._plans[key] = pattern
         return pattern
 
-    def forward_rows(self, rows: torch.Tensor, counts: list[int], starts: list[int]) -> torch.Tensor:
-        """The experts applied to permuted rows: ``rows`` FP32 ``[R, H]`` grouped by expert
-        (expert e at ``starts[e]``, ``counts[e]`` rows, blocks padded to 128 rows). Returns
-        FP16 ``[R, H]`` (padding rows zero): the pattern's own output buffer, which the next
-        forward with the same row counts on the same stream overwrites.
-
-        A pattern seen before costs one quantiser launch and two grouped GEMM launches:
-        nothing is allocated, encoded or bound."""
+    def _run(self, counts: list[int], starts: list[int], total: int,
+             quantise: Callable[[_Pattern, int], None]) -> torch.Tensor:
+        """One forward on the pattern of ``counts``: ``quantise(pattern, stream)`` fills the
+        pattern's ``a1`` / ``s1``; then the two grouped launches. Returns the pattern's ``y``."""
         hidden, inter = self.hidden, self.inter
         if not any(count > 0 for count in counts):
-            return torch.zeros((rows.shape[0], hidden), dtype=torch.float16, device=self.device)
+            return torch.zeros((total, hidden), dtype=torch.float16, device=self.device)
         with torch.cuda.device(self.device):
             stream = torch.cuda.current_stream(self.device).cuda_stream
             pattern = self._entry(tuple(counts), stream)
-            if list(starts) != pattern.starts or rows.shape != (pattern.total, hidden):
+            if list(starts) != pattern.starts or total != pattern.total:
                 raise ValueError("rows are not laid out in 128-row blocks per expert")
-            if rows.dtype != torch.float32 or not rows.is_contiguous():
-                rows = rows.float().contiguous()
-            native.quantize_blocks(rows.data_ptr(), native.IN_F32, pattern.a1.data_ptr(),
-                                   pattern.s1.data_ptr(), pattern.total, hidden,
-                                   pattern.block_rows.data_ptr(), stream)
+            quantise(pattern, stream)
             pattern.up_plan.launch_groups(pattern.up_ws.data_ptr(), stream)
             if not self.fused:
                 h = pattern.h
@@ -259,6 +251,47 @@ class MoELayer:
                                        pattern.block_rows.data_ptr(), stream)
             pattern.down_plan.launch_groups(pattern.down_ws.data_ptr(), stream)
         return pattern.y
+
+    def forward_rows(self, rows: torch.Tensor, counts: list[int], starts: list[int]) -> torch.Tensor:
+        """The experts applied to permuted rows: ``rows`` FP32 ``[R, H]`` grouped by expert
+        (expert e at ``starts[e]``, ``counts[e]`` rows, blocks padded to 128 rows). Returns
+        FP16 ``[R, H]`` (padding rows zero): the pattern's own output buffer, which the next
+        forward with the same row counts on the same stream overwrites.
+
+        A pattern seen before costs one quantiser launch and two grouped GEMM launches:
+        nothing is allocated, encoded or bound."""
+        if rows.dim() != 2 or rows.shape[1] != self.hidden:
+            raise ValueError("rows do not match the weights")
+        if rows.dtype != torch.float32 or not rows.is_contiguous():
+            rows = rows.float().contiguous()
+
+        def quantise(pattern: _Pattern, stream: int) -> None:
+            native.quantize_blocks(rows.data_ptr(), native.IN_F32, pattern.a1.data_ptr(),
+                                   pattern.s1.data_ptr(), pattern.total, self.hidden,
+                                   pattern.block_rows.data_ptr(), stream)
+
+        return self._run(counts, starts, rows.shape[0], quantise)
+
+    def forward_gathered(self, x: torch.Tensor, source_rows: torch.Tensor, counts: list[int],
+                         starts: list[int]) -> torch.Tensor:
+        """``forward_rows`` without the permuted copy: permuted row r is row
+        ``source_rows[r]`` of ``x`` (``[T, H]`` FP32 or BF16, contiguous), or padding where
+        ``source_rows[r] < 0`` (int32 ``[R]`` on the device). The quantiser reads the token
+        rows where they are."""
+        if x.dim() != 2 or x.shape[1] != self.hidden:
+            raise ValueError("activations do not match the weights")
+        if x.dtype not in (torch.float32, torch.bfloat16) or not x.is_contiguous():
+            x = x.float().contiguous()
+        kind = native.IN_F32 if x.dtype == torch.float32 else native.IN_BF16
+        if source_rows.dtype != torch.int32 or not source_rows.is_contiguous():
+            source_rows = source_rows.to(torch.int32).contiguous()
+
+        def quantise(pattern: _Pattern, stream: int) -> None:
+            native.quantize_gather(x.data_ptr(), kind, pattern.a1.data_ptr(),
+                                   pattern.s1.data_ptr(), pattern.total, self.hidden,
+                                   source_rows.data_ptr(), stream)
+
+        return self._run(counts, starts, source_rows.numel(), quantise)
 
     def check_status(self) -> None:
         """Synchronise and raise ``native.NativeError`` if a kernel abandoned a wait."""
@@ -273,7 +306,8 @@ class MoELayer:
             raise ValueError("activations do not match the weights")
         tokens, choices = topk_ids.shape
         source, counts, starts = route_rows(topk_ids, self.experts)
-        y = self.forward_rows(_gather(x, source, choices), counts, starts)
+        token_of_row = torch.where(source >= 0, source // choices, source).to(torch.int32)
+        y = self.forward_gathered(x, token_of_row, counts, starts)
         return _scatter(y, source, topk_weights, tokens)
 
 
@@ -378,7 +412,7 @@ def ep_local_experts(layer: MoELayer) -> Callable[[torch.Tensor, torch.Tensor], 
         if rows.shape[0] == 0:
             return rows
         source, counts, starts = route_rows(local_ids[:, None], layer.experts)
-        y = layer.forward_rows(_gather(rows, source, 1), counts, starts)
+        y = layer.forward_gathered(rows, source.to(torch.int32), counts, starts)
         out = torch.zeros_like(rows)
         valid = source >= 0
         out[source[valid]] = y[valid].float()

@@ -133,6 +133,9 @@ _PROTOTYPES = {
     "nvfp4_quantize_blocks": (
         ctypes.c_int, [_P, ctypes.c_int, _P, _P, ctypes.c_int, ctypes.c_int, _P, _P],
     ),
+    "nvfp4_quantize_gather": (
+        ctypes.c_int, [_P, ctypes.c_int, _P, _P, ctypes.c_int, ctypes.c_int, _P, _P],
+    ),
     "nvfp4_silu_product": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P]),
     "nvfp4_measure_mma_peak": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
 }
@@ -370,6 +373,13 @@ def quantize_blocks(x: int, x_kind: int, packed: int, scales: int, rows: int, k:
     """``quantize`` of rows in 128-row blocks whose leading ``block_rows[b]`` rows hold data
     (a device array of int32); the other rows are left untouched in both outputs."""
     check(load().nvfp4_quantize_blocks(x, x_kind, packed, scales, rows, k, block_rows, stream))
+
+
+def quantize_gather(x: int, x_kind: int, packed: int, scales: int, rows: int, k: int,
+                    source_rows: int, stream: int) -> None:
+    """Output row r = quantised row ``source_rows[r]`` of x (device int32 array; negative:
+    the output row is left untouched)."""
+    check(load().nvfp4_quantize_gather(x, x_kind, packed, scales, rows, k, source_rows, stream))
 
 
 def measure_mma_peak(device: int, iters: int = 4096) -> float:

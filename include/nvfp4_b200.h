@@ -287,6 +287,14 @@ int nvfp4_quantize(const void* x, int x_kind, void* packed, void* scales, int ro
 int nvfp4_quantize_blocks(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
                           const int* block_rows, void* stream);
 
+/* Gather and quantise: output row r (of `rows`) is the quantised row source_rows[r] of x
+ * ([any number of rows][k]), or, where source_rows[r] < 0, nothing: such rows are neither read
+ * nor written. `source_rows` is a device array of `rows` ints. The dispatch of a
+ * mixture-of-experts layer (token rows permuted by expert, blocks padded to 128 rows) without
+ * a permuted copy of the activations. */
+int nvfp4_quantize_gather(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
+                          const int* source_rows, void* stream);
+
 /* out[i] = half(silu(h1[i]) * h2[i]) over `size` FP32 elements. Replaces the
  * silu_product kernel (impls/nvfp4_dual_gemm/kernels/silu_product.cu:7-9,
  * harness/workloads/nvfp4_dual_gemm.py:352-367). */

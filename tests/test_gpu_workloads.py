@@ -568,6 +568,33 @@ def test_quantiser_on_ragged_blocks_leaves_the_other_rows_alone(dtype):
                                rows, k, 0, 0)
 
 
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
+def test_gathering_quantiser(dtype):
+    """nvfp4_quantize_gather: output row r is the quantised row source[r] of x (rows used
+    several times, in any order), rows with source[r] < 0 keep what the buffers held."""
+    from harness.workloads import quantization as q
+    tokens, rows, k = 300, 640, 2048
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn((tokens, k), generator=g).to(dtype).cuda()
+    source = torch.randint(-1, tokens, (rows,), generator=g, dtype=torch.int32)
+    source[128:256] = -1                                   # a whole block without data
+    source = source.cuda()
+    packed = torch.full((rows, k // 2), 0xAB, dtype=torch.uint8, device="cuda")
+    blocked = torch.full((rows // 128, k // 64, 32, 4, 4), 0xCD, dtype=torch.uint8, device="cuda")
+    native.quantize_gather(x.data_ptr(), native.IN_F32 if dtype == torch.float32 else native.IN_BF16,
+                           packed.data_ptr(), blocked.data_ptr(), rows, k, source.data_ptr(),
+                           torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    live = source >= 0
+    gathered = x[source.clamp(min=0).long()].float()
+    want_packed, want_scales = q.quantize_nvfp4(gathered[..., None])
+    assert torch.equal(packed[live], want_packed[..., 0][live])
+    assert (packed[~live] == 0xAB).all()
+    got = blocked.permute(0, 3, 2, 1, 4).reshape(rows, k // 16)
+    assert torch.equal(got[live], want_scales[..., 0].view(torch.uint8)[live])
+    assert (got[~live] == 0xCD).all()
+
+
 def _fp4_out_inputs(m, n, k, batches, scales, seed):
     from harness.workloads import quantization as q
     workload = get_workload("nvfp4_gemm")(None, device="cuda")
