@@ -945,7 +945,9 @@ def row_moe(device) -> list[dict]:
     1,024 and 16,384 tokens, per-expert counts seeded log-normal. ``layer_us`` is
     ``MoELayer.forward_rows`` (quantiser and two grouped launches on the pattern's bound
     buffers) called from Python, ``layer_graph_us`` the same forward replayed from a CUDA
-    graph; ``kernels_us`` the two grouped launches alone replayed from a graph. The busiest
+    graph; ``kernels_us`` the two grouped launches alone replayed from a graph;
+    ``shard_forward_us`` everything a rank does with the rows an all-to-all delivered (route,
+    gather-quantise, both GEMMs, un-permute; ``moe.ep_local_experts``). The busiest
     expert's rows are checked against the stage-by-stage torch reference."""
     from harness import moe
     from harness.models import MODELS
@@ -1030,6 +1032,24 @@ def row_moe(device) -> list[dict]:
             side.synchronize()
         layer_graph_us = start.elapsed_time(stop) * 1e3 / 20
         del graph
+        # What the rank does with the rows an all-to-all delivered (BF16 rows in arrival order,
+        # one expert each): route, gather-quantise, both GEMMs, un-permute; the row counts are
+        # read back on the host.
+        arrived = torch.randn((routed, hidden), device=device, generator=gen).to(torch.bfloat16)
+        expert_of_row = torch.repeat_interleave(
+            torch.arange(local, device=device), torch.tensor(counts, device=device))
+        expert_of_row = expert_of_row[torch.randperm(routed, device=device, generator=gen)]
+        shard = moe.ep_local_experts(layer)
+        for _ in range(3):
+            shard(arrived, expert_of_row)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(repeats):
+            shard(arrived, expert_of_row)
+        stop.record()
+        torch.cuda.synchronize()
+        shard_us = start.elapsed_time(stop) * 1e3 / repeats
+        del arrived
         layer.check_status()
         del y
         live = sum(1 for count in counts if count)
@@ -1049,6 +1069,7 @@ def row_moe(device) -> list[dict]:
                                 f"{tokens} tokens -> {routed} routed rows, {live} live experts, "
                                 f"hidden {hidden}, intermediate {inter}",
                     "layer_us": layer_us, "layer_graph_us": layer_graph_us,
+                    "shard_forward_us": shard_us,
                     "kernels_us": kernels_us,
                     "us_per_call": kernels_us, "tflops": flops / kernels_us / 1e6,
                     "validated": bool(error < 1e-2), "relative_error_of_probed_expert": error,

@@ -48,28 +48,49 @@ ROW_BLOCK = 128
 MAX_PATTERNS = 8  # routing patterns a layer keeps plans and buffers for
 
 
-def route_rows(topk_ids: torch.Tensor, experts: int) -> tuple[torch.Tensor, list[int], list[int]]:
-    """Order the (token, choice) pairs by expert. Returns ``source`` (for every padded
-    permuted row the flat pair index ``token * K + choice``, or -1 for padding), the row
-    count per expert and each expert's first padded row. One host read (the counts: the
-    plan's shapes depend on them); everything else stays on the device."""
+class Routing:
+    """Where every (token, choice) pair goes when the pairs are ordered by expert and every
+    expert's block is padded to whole 128-row blocks: ``source`` (for every padded permuted
+    row the flat pair index ``token * K + choice``, or -1 for padding), ``row_of_pair`` (the
+    inverse: the permuted row of every pair), the row count per expert and each expert's
+    first padded row."""
+
+    __slots__ = ("source", "row_of_pair", "counts", "starts")
+
+    def __init__(self, source, row_of_pair, counts, starts):
+        self.source, self.row_of_pair, self.counts, self.starts = source, row_of_pair, counts, starts
+
+
+def route(topk_ids: torch.Tensor, experts: int) -> Routing:
+    """Order the (token, choice) pairs by expert. One host read (the counts: the plans' shapes
+    depend on them); everything else stays on the device, without masked indexing."""
     flat = topk_ids.reshape(-1)
+    device = flat.device
     order = torch.argsort(flat, stable=True)
     counts_t = torch.bincount(flat, minlength=experts)
-    padded_t = (counts_t + ROW_BLOCK - 1) // ROW_BLOCK * ROW_BLOCK
-    starts_t = torch.cumsum(padded_t, 0) - padded_t
     counts = counts_t.tolist()
-    starts = starts_t.tolist()
-    total = starts[-1] + -(-counts[-1] // ROW_BLOCK) * ROW_BLOCK if experts else 0
-    source = torch.full((max(total, ROW_BLOCK),), -1, dtype=torch.int64, device=topk_ids.device)
+    starts, total = [], 0
+    for count in counts:
+        starts.append(total)
+        total += -(-count // ROW_BLOCK) * ROW_BLOCK
+    source = torch.full((max(total, ROW_BLOCK),), -1, dtype=torch.int64, device=device)
+    row_of_pair = torch.empty_like(order)
     if flat.numel():
         # Pair i of the sorted order belongs to expert flat[order[i]] and is that expert's
         # (i - first sorted position of the expert)-th row.
-        sorted_expert = flat[order]
+        starts_t = torch.tensor(starts, dtype=torch.int64, device=device)
         first = torch.cumsum(counts_t, 0) - counts_t
-        position = torch.arange(flat.numel(), device=flat.device) - first[sorted_expert]
-        source[starts_t[sorted_expert] + position] = order
-    return source, counts, starts
+        sorted_expert = flat[order]
+        rows = (starts_t - first)[sorted_expert] + torch.arange(flat.numel(), device=device)
+        source[rows] = order
+        row_of_pair[order] = rows
+    return Routing(source, row_of_pair, counts, starts)
+
+
+def route_rows(topk_ids: torch.Tensor, experts: int) -> tuple[torch.Tensor, list[int], list[int]]:
+    """``route`` as the tuple ``(source, counts, starts)``."""
+    routing = route(topk_ids, experts)
+    return routing.source, routing.counts, routing.starts
 
 
 def _gather(x: torch.Tensor, source: torch.Tensor, choices: int) -> torch.Tensor:
@@ -79,13 +100,12 @@ def _gather(x: torch.Tensor, source: torch.Tensor, choices: int) -> torch.Tensor
     return rows
 
 
-def _scatter(y: torch.Tensor, source: torch.Tensor, weights: torch.Tensor, tokens: int) -> torch.Tensor:
-    valid = source >= 0
-    pairs = source[valid]
-    out = torch.zeros((tokens, y.shape[1]), dtype=torch.float32, device=y.device)
-    out.index_add_(0, pairs // weights.shape[1],
-                   y[valid].float() * weights.reshape(-1)[pairs].float()[:, None])
-    return out
+def _combine(y: torch.Tensor, row_of_pair: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * y[row of pair (t, j)]`` in FP32: one gather of the
+    pairs' rows and one batched product, no atomics."""
+    tokens, choices = weights.shape
+    picked = y.index_select(0, row_of_pair).view(tokens, choices, y.shape[1])
+    return torch.bmm(weights.float().unsqueeze(1), picked.float()).squeeze(1)
 
 
 class _Pattern:
@@ -304,11 +324,12 @@ class MoELayer:
         ``e = topk_ids[t, j]``; ``x`` ``[T, H]`` FP32/BF16, result FP32 ``[T, H]``."""
         if x.shape[1] != self.hidden:
             raise ValueError("activations do not match the weights")
-        tokens, choices = topk_ids.shape
-        source, counts, starts = route_rows(topk_ids, self.experts)
-        token_of_row = torch.where(source >= 0, source // choices, source).to(torch.int32)
-        y = self.forward_gathered(x, token_of_row, counts, starts)
-        return _scatter(y, source, topk_weights, tokens)
+        choices = topk_ids.shape[1]
+        routing = route(topk_ids, self.experts)
+        # (-1 // choices is -1: padding stays padding.)
+        token_of_row = torch.div(routing.source, choices, rounding_mode="floor").to(torch.int32)
+        y = self.forward_gathered(x, token_of_row, routing.counts, routing.starts)
+        return _combine(y, routing.row_of_pair, topk_weights)
 
 
 def moe_forward(x, topk_ids, topk_weights, w13, w13_scales, w2, w2_scales,
@@ -372,10 +393,10 @@ def moe_forward_ep(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.
                    local_experts: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
                    group=None) -> torch.Tensor:
     """Expert-parallel forward of this rank's tokens. ``experts`` is the global expert
-    count; ``local_experts(rows, local_ids)`` applies this rank's experts to FP32 ``rows``
-    ``[R, H]`` whose expert (numbered from 0 within the rank) is ``local_ids[R]`` and
-    returns ``[R, H]`` (on a GPU: ``ep_local_experts(layer)`` below; the CPU test passes the
-    torch reference). Two ``all_to_all_single`` exchanges carry the rows out and back; one
+    count; ``local_experts(rows, local_ids)`` applies this rank's experts to ``rows``
+    ``[R, H]`` (in the type of ``x``) whose expert (numbered from 0 within the rank) is
+    ``local_ids[R]`` and returns ``[R, H]``, every rank in the same type (on a GPU:
+    ``ep_local_experts(layer)`` below, FP16; the CPU test passes the torch reference). Two ``all_to_all_single`` exchanges carry the rows out and back; one
     small one carries the row counts. Returns FP32 ``[T, H]``."""
     import torch.distributed as dist
 
@@ -390,17 +411,24 @@ def moe_forward_ep(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.
     recv_counts = torch.empty_like(send_counts)
     dist.all_to_all_single(recv_counts, send_counts, group=group)
     send_split, recv_split = send_counts.tolist(), recv_counts.tolist()
-    send_rows = x.float()[order // choices].contiguous()
+    # Rows travel in the activations' own type (BF16 activations as BF16) and come back in the
+    # experts' output type (FP16 from the GPU kernels).
+    send_rows = x[order // choices].contiguous()
     send_ids = (flat[order] % per_rank).contiguous()
-    recv_rows = torch.empty((sum(recv_split), hidden), dtype=torch.float32, device=x.device)
+    recv_rows = torch.empty((sum(recv_split), hidden), dtype=send_rows.dtype, device=x.device)
     recv_ids = torch.empty((sum(recv_split),), dtype=send_ids.dtype, device=x.device)
     dist.all_to_all_single(recv_rows, send_rows, recv_split, send_split, group=group)
     dist.all_to_all_single(recv_ids, send_ids, recv_split, send_split, group=group)
-    done = local_experts(recv_rows, recv_ids).float().contiguous()
-    back = torch.empty((sum(send_split), hidden), dtype=torch.float32, device=x.device)
+    done = local_experts(recv_rows, recv_ids)
+    if done.device.type == "cpu":
+        done = done.float()   # gloo has no half-precision all-to-all
+    done = done.contiguous()
+    back = torch.empty((sum(send_split), hidden), dtype=done.dtype, device=x.device)
     dist.all_to_all_single(back, done, send_split, recv_split, group=group)
-    out = torch.zeros((tokens, hidden), dtype=torch.float32, device=x.device)
-    out.index_add_(0, order // choices, back * topk_weights.reshape(-1)[order].float()[:, None])
+    # back[i] is the result of pair order[i]: put the pairs back in token order and combine.
+    place = torch.empty_like(order)
+    place[order] = torch.arange(order.numel(), device=order.device)
+    out = _combine(back, place, topk_weights)
     return out
 
 
@@ -410,12 +438,10 @@ def ep_local_experts(layer: MoELayer) -> Callable[[torch.Tensor, torch.Tensor], 
 
     def apply(rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
         if rows.shape[0] == 0:
-            return rows
-        source, counts, starts = route_rows(local_ids[:, None], layer.experts)
-        y = layer.forward_gathered(rows, source.to(torch.int32), counts, starts)
-        out = torch.zeros_like(rows)
-        valid = source >= 0
-        out[source[valid]] = y[valid].float()
-        return out
+            return torch.empty((0, rows.shape[1]), dtype=torch.float16, device=rows.device)
+        routing = route(local_ids[:, None], layer.experts)
+        y = layer.forward_gathered(rows, routing.source.to(torch.int32), routing.counts,
+                                   routing.starts)
+        return y.index_select(0, routing.row_of_pair)   # FP16, in the order the rows came
 
     return apply
