@@ -1531,6 +1531,71 @@ int nvfp4_measure_mma_peak(int device, int iters, double* tflops) {
   return 0;
 }
 
+int nvfp4_moe_count(const void* ids, int ids_are_64bit, long long pairs, int experts, int* counts,
+                    void* stream) {
+  if (ids == nullptr || counts == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  if (pairs < 0 || experts < 1 || experts > kMoeMaxExperts) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "unsupported routing: %lld pairs, %d experts (at most %d)",
+                pairs, experts, kMoeMaxExperts);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * static_cast<size_t>(experts), s));
+  if (pairs == 0) return 0;
+  const int threads = 256;
+  const unsigned int blocks = static_cast<unsigned int>(
+      std::min<long long>((pairs + threads - 1) / threads, 4ll * current_sm_count()));
+  if (ids_are_64bit) {
+    moe_count_kernel<long long><<<blocks, threads, 0, s>>>(static_cast<const long long*>(ids), pairs,
+                                                           experts, counts);
+  } else {
+    moe_count_kernel<int><<<blocks, threads, 0, s>>>(static_cast<const int*>(ids), pairs, experts,
+                                                     counts);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int choices, int experts,
+                    const int* first_rows, int rows, int* cursors, int* row_of_pair,
+                    int* token_of_row, void* stream) {
+  if (ids == nullptr || first_rows == nullptr || cursors == nullptr || row_of_pair == nullptr ||
+      token_of_row == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  }
+  if (pairs < 0 || choices < 1 || rows < 0 || experts < 1 || experts > kMoeMaxExperts) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "unsupported routing: %lld pairs, %d experts (at most %d)",
+                pairs, experts, kMoeMaxExperts);
+  }
+  MoeStarts starts = {};
+  for (int e = 0; e < experts; ++e) {
+    if (first_rows[e] < 0 || first_rows[e] > rows) {
+      return fail(NVFP4_E_INVALID_ARGUMENT, "expert %d: first row %d outside [0, %d]", e,
+                  first_rows[e], rows);
+    }
+    starts.first_row[e] = first_rows[e];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUDA_TRY(cudaMemsetAsync(cursors, 0, sizeof(int) * static_cast<size_t>(experts), s));
+  if (rows > 0) {
+    CUDA_TRY(cudaMemsetAsync(token_of_row, 0xFF, sizeof(int) * static_cast<size_t>(rows), s));
+  }
+  if (pairs == 0) return 0;
+  const int threads = 256;
+  const unsigned int blocks = static_cast<unsigned int>(
+      std::min<long long>((pairs + threads - 1) / threads, 4ll * current_sm_count()));
+  if (ids_are_64bit) {
+    moe_place_kernel<long long><<<blocks, threads, 0, s>>>(static_cast<const long long*>(ids), pairs,
+                                                           choices, experts, starts, cursors,
+                                                           row_of_pair, token_of_row);
+  } else {
+    moe_place_kernel<int><<<blocks, threads, 0, s>>>(static_cast<const int*>(ids), pairs, choices,
+                                                     experts, starts, cursors, row_of_pair,
+                                                     token_of_row);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
 int nvfp4_silu_product(const float* h1, const float* h2, void* out, int64_t size, void* stream) {
   if (h1 == nullptr || h2 == nullptr || out == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");

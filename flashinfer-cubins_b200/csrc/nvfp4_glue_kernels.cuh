@@ -245,6 +245,55 @@ quantize_nvfp4_kernel(const In* __restrict__ x, uint8_t* __restrict__ packed,
   }
 }
 
+// Routing of a mixture-of-experts layer, in two launches around the one host read that the
+// grouped plans need (the row count per expert):
+//   moe_count_kernel: counts[e] = number of (token, choice) pairs whose expert is e;
+//   moe_place_kernel: every pair gets a row in its expert's block (first row starts[e], the
+//     host's prefix over the counts padded to whole 128-row blocks) - row_of_pair[i] for the
+//     combine, token_of_row[row] = i / choices for the gathering quantiser. Rows inside a
+//     block are handed out by an atomic counter: which pair gets which row differs from run
+//     to run, the result of the layer does not (every row is computed on its own).
+// Ids outside [0, experts) get no row (row_of_pair = -1).
+constexpr int kMoeMaxExperts = 512;
+
+struct MoeStarts {
+  int first_row[kMoeMaxExperts];
+};
+
+template <typename Id>
+__global__ void moe_count_kernel(const Id* __restrict__ ids, long long pairs, int experts,
+                                 int* __restrict__ counts) {
+  __shared__ int local[kMoeMaxExperts];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) local[e] = 0;
+  __syncthreads();
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pairs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = static_cast<long long>(ids[i]);
+    if (e >= 0 && e < experts) atomicAdd(&local[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    if (local[e] != 0) atomicAdd(&counts[e], local[e]);
+  }
+}
+
+template <typename Id>
+__global__ void moe_place_kernel(const Id* __restrict__ ids, long long pairs, int choices,
+                                 int experts, const __grid_constant__ MoeStarts starts,
+                                 int* __restrict__ cursors, int* __restrict__ row_of_pair,
+                                 int* __restrict__ token_of_row) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pairs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = static_cast<long long>(ids[i]);
+    int row = -1;
+    if (e >= 0 && e < experts) {
+      row = starts.first_row[e] + atomicAdd(&cursors[e], 1);
+      token_of_row[row] = static_cast<int>(i / choices);
+    }
+    row_of_pair[i] = row;
+  }
+}
+
 // silu(a) * b with ex2.approx and rcp.approx (no slow path when exp(-a) overflows).
 __device__ __forceinline__ float silu_gate(float a, float b) {
   float e, r;

@@ -87,6 +87,41 @@ def route(topk_ids: torch.Tensor, experts: int) -> Routing:
     return Routing(source, row_of_pair, counts, starts)
 
 
+class DeviceRouting:
+    """``route`` by the library's two routing kernels (``nvfp4_moe_count`` /
+    ``nvfp4_moe_place``) for ids on a GPU: ``token_of_row`` (int32, the token of every padded
+    permuted row, -1 for padding; what ``MoELayer.forward_gathered`` takes), ``row_of_pair``
+    (int32), the row count per expert and each expert's first padded row. Two launches and
+    one host read instead of a sort and a dozen indexing kernels; which pair gets which row
+    inside an expert's block is not fixed from run to run (the layer's result is)."""
+
+    __slots__ = ("token_of_row", "row_of_pair", "counts", "starts", "_scratch")
+
+    def __init__(self, topk_ids: torch.Tensor, experts: int):
+        ids = topk_ids.contiguous()
+        if ids.dtype not in (torch.int32, torch.int64):
+            ids = ids.to(torch.int64)
+        device = ids.device
+        pairs, choices = ids.numel(), ids.shape[1]
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            scratch = torch.empty((2, experts), dtype=torch.int32, device=device)
+            native.moe_count(ids.data_ptr(), ids.dtype == torch.int64, pairs, experts,
+                             scratch[0].data_ptr(), stream)
+            self.counts = scratch[0].tolist()
+            self.starts, total = [], 0
+            for count in self.counts:
+                self.starts.append(total)
+                total += -(-count // ROW_BLOCK) * ROW_BLOCK
+            rows = max(total, ROW_BLOCK)
+            self.row_of_pair = torch.empty((pairs,), dtype=torch.int32, device=device)
+            self.token_of_row = torch.empty((rows,), dtype=torch.int32, device=device)
+            native.moe_place(ids.data_ptr(), ids.dtype == torch.int64, pairs, choices, self.starts,
+                             rows, scratch[1].data_ptr(), self.row_of_pair.data_ptr(),
+                             self.token_of_row.data_ptr(), stream)
+            self._scratch = scratch  # until the launches have run
+
+
 def route_rows(topk_ids: torch.Tensor, experts: int) -> tuple[torch.Tensor, list[int], list[int]]:
     """``route`` as the tuple ``(source, counts, starts)``."""
     routing = route(topk_ids, experts)
@@ -324,11 +359,8 @@ class MoELayer:
         ``e = topk_ids[t, j]``; ``x`` ``[T, H]`` FP32/BF16, result FP32 ``[T, H]``."""
         if x.shape[1] != self.hidden:
             raise ValueError("activations do not match the weights")
-        choices = topk_ids.shape[1]
-        routing = route(topk_ids, self.experts)
-        # (-1 // choices is -1: padding stays padding.)
-        token_of_row = torch.div(routing.source, choices, rounding_mode="floor").to(torch.int32)
-        y = self.forward_gathered(x, token_of_row, routing.counts, routing.starts)
+        routing = DeviceRouting(topk_ids, self.experts)
+        y = self.forward_gathered(x, routing.token_of_row, routing.counts, routing.starts)
         return _combine(y, routing.row_of_pair, topk_weights)
 
 
@@ -439,9 +471,8 @@ def ep_local_experts(layer: MoELayer) -> Callable[[torch.Tensor, torch.Tensor], 
     def apply(rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
         if rows.shape[0] == 0:
             return torch.empty((0, rows.shape[1]), dtype=torch.float16, device=rows.device)
-        routing = route(local_ids[:, None], layer.experts)
-        y = layer.forward_gathered(rows, routing.source.to(torch.int32), routing.counts,
-                                   routing.starts)
+        routing = DeviceRouting(local_ids[:, None], layer.experts)
+        y = layer.forward_gathered(rows, routing.token_of_row, routing.counts, routing.starts)
         return y.index_select(0, routing.row_of_pair)   # FP16, in the order the rows came
 
     return apply

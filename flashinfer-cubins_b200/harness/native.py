@@ -136,6 +136,13 @@ _PROTOTYPES = {
     "nvfp4_quantize_gather": (
         ctypes.c_int, [_P, ctypes.c_int, _P, _P, ctypes.c_int, ctypes.c_int, _P, _P],
     ),
+    "nvfp4_moe_count": (
+        ctypes.c_int, [_P, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, _P, _P],
+    ),
+    "nvfp4_moe_place": (
+        ctypes.c_int, [_P, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, _P,
+                       ctypes.c_int, _P, _P, _P, _P],
+    ),
     "nvfp4_silu_product": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P]),
     "nvfp4_measure_mma_peak": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
 }
@@ -380,6 +387,20 @@ def quantize_gather(x: int, x_kind: int, packed: int, scales: int, rows: int, k:
     """Output row r = quantised row ``source_rows[r]`` of x (device int32 array; negative:
     the output row is left untouched)."""
     check(load().nvfp4_quantize_gather(x, x_kind, packed, scales, rows, k, source_rows, stream))
+
+
+def moe_count(ids: int, ids_are_64bit: bool, pairs: int, experts: int, counts: int,
+              stream: int) -> None:
+    """``counts[e]`` (device int32) = number of ``ids`` equal to e."""
+    check(load().nvfp4_moe_count(ids, int(ids_are_64bit), pairs, experts, counts, stream))
+
+
+def moe_place(ids: int, ids_are_64bit: bool, pairs: int, choices: int, first_rows: list[int],
+              rows: int, cursors: int, row_of_pair: int, token_of_row: int, stream: int) -> None:
+    """Give every pair a row of its expert's block (``first_rows``: host list, one per expert)."""
+    starts = (ctypes.c_int * len(first_rows))(*first_rows)
+    check(load().nvfp4_moe_place(ids, int(ids_are_64bit), pairs, choices, len(first_rows), starts,
+                                 rows, cursors, row_of_pair, token_of_row, stream))
 
 
 def measure_mma_peak(device: int, iters: int = 4096) -> float:

@@ -295,6 +295,25 @@ int nvfp4_quantize_blocks(const void* x, int x_kind, void* packed, void* scales,
 int nvfp4_quantize_gather(const void* x, int x_kind, void* packed, void* scales, int rows, int k,
                           const int* source_rows, void* stream);
 
+/* Routing of a mixture-of-experts layer whose experts' rows are kept in blocks padded to
+ * whole 128-row blocks (what the grouped plans and nvfp4_quantize_gather take), around the
+ * one host read that the plans' shapes need. `ids` is a device array of `pairs` expert ids
+ * (int32, or int64 if ids_are_64bit), pair i = (token i / choices, choice i % choices); at most
+ * 512 experts.
+ *   nvfp4_moe_count: counts[e] (device, `experts` ints) = number of pairs with id e.
+ *   nvfp4_moe_place: with first_rows[e] (HOST array: the caller's prefix over the counts
+ *     padded to 128) every pair gets a row of its expert's block: row_of_pair[i] (device,
+ *     `pairs` ints) and token_of_row[row] = i / choices (device, `rows` ints, -1 for the rows
+ *     that hold no pair). `cursors` is device scratch of `experts` ints. Which pair gets which
+ *     row of a block may differ from run to run; the layer's result does not depend on it.
+ * The reference routes on the host (harness/workloads/moe.py:1-33 describes its FP8 layer's
+ * stages); no counterpart on this path. */
+int nvfp4_moe_count(const void* ids, int ids_are_64bit, long long pairs, int experts, int* counts,
+                    void* stream);
+int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int choices, int experts,
+                    const int* first_rows, int rows, int* cursors, int* row_of_pair,
+                    int* token_of_row, void* stream);
+
 /* out[i] = half(silu(h1[i]) * h2[i]) over `size` FP32 elements. Replaces the
  * silu_product kernel (impls/nvfp4_dual_gemm/kernels/silu_product.cu:7-9,
  * harness/workloads/nvfp4_dual_gemm.py:352-367). */

@@ -107,6 +107,35 @@ def test_forward_of_a_known_pattern_can_be_captured_in_a_graph():
     layer.close()
 
 
+@pytest.mark.parametrize("tokens,experts,choices,dtype", [
+    (1000, 8, 2, torch.int64), (37, 5, 1, torch.int32), (4096, 256, 8, torch.int64), (1, 3, 1, torch.int64)])
+def test_device_routing_places_every_pair_in_its_experts_block(tokens, experts, choices, dtype):
+    """nvfp4_moe_count / nvfp4_moe_place: counts equal a bincount; every pair gets its own row
+    inside its expert's 128-row-padded block; the rows remember their token; all other rows
+    are padding."""
+    g = torch.Generator().manual_seed(tokens + experts)
+    scores = torch.rand(tokens, experts, generator=g)
+    if experts > 2:
+        scores[:, 1] = -1.0                                  # an expert without any pair
+    ids = torch.topk(scores, choices, dim=1).indices.to(dtype).cuda()
+    routing = moe.DeviceRouting(ids, experts)
+    torch.cuda.synchronize()
+    flat = ids.reshape(-1).long()
+    assert routing.counts == torch.bincount(flat, minlength=experts).tolist()
+    assert all(start % 128 == 0 for start in routing.starts)
+    rows = routing.row_of_pair.long()
+    starts = torch.tensor(routing.starts, device="cuda")[flat]
+    counts = torch.tensor(routing.counts, device="cuda")[flat]
+    assert ((rows >= starts) & (rows < starts + counts)).all()
+    assert rows.unique().numel() == rows.numel()
+    pairs = torch.arange(flat.numel(), device="cuda")
+    assert torch.equal(routing.token_of_row[rows].long(), pairs // choices)
+    padding = torch.ones_like(routing.token_of_row, dtype=torch.bool)
+    padding[rows] = False
+    assert (routing.token_of_row[padding] == -1).all()
+    assert routing.token_of_row.numel() == max(128, sum(-(-c // 128) * 128 for c in routing.counts))
+
+
 def test_fused_and_unfused_layers_agree():
     device = torch.device("cuda:0")
     tokens, hidden, inter, experts, choices = 300, 512, 256, 5, 2
