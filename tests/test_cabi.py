@@ -57,6 +57,23 @@ def test_invalid_arguments_are_rejected_without_cuda(library):
     assert library.nvfp4_silu_product(16, 16, 16, 0, None) == native.E_UNSUPPORTED_SHAPE
     assert library.nvfp4_silu_product(18, 16, 16, 4, None) == native.E_MISALIGNED
     assert library.nvfp4_plan_workspace_bytes(None) == 0
+    # The quantisers and the routing kernels check their arguments before they touch CUDA.
+    assert library.nvfp4_quantize(None, 0, 16, 16, 8, 32, 1, None) == native.E_INVALID_ARGUMENT
+    assert library.nvfp4_quantize(16, 5, 16, 16, 8, 32, 1, None) == native.E_INVALID_ARGUMENT
+    assert library.nvfp4_quantize(16, 0, 16, 16, 8, 24, 1, None) == native.E_UNSUPPORTED_SHAPE
+    assert library.nvfp4_quantize(24, 0, 16, 16, 8, 32, 1, None) == native.E_MISALIGNED
+    assert library.nvfp4_quantize_blocks(16, 0, 16, 16, 8, 32, None, None) == native.E_INVALID_ARGUMENT
+    assert library.nvfp4_quantize_gather(16, 0, 16, 16, 8, 32, 6, None) == native.E_INVALID_ARGUMENT
+    assert library.nvfp4_moe_count(None, 1, 8, 4, 16, None) == native.E_INVALID_ARGUMENT
+    assert library.nvfp4_moe_count(16, 1, 8, 513, 16, None) == native.E_UNSUPPORTED_SHAPE
+    assert library.nvfp4_moe_count(16, 1, -1, 4, 16, None) == native.E_UNSUPPORTED_SHAPE
+    starts = (ctypes.c_int * 2)(0, 256)
+    assert library.nvfp4_moe_place(16, 1, 8, 0, 2, starts, 128, 16, 16, 16, None) == \
+        native.E_UNSUPPORTED_SHAPE
+    assert library.nvfp4_moe_place(16, 1, 8, 2, 2, starts, 128, 16, 16, 16, None) == \
+        native.E_INVALID_ARGUMENT      # an expert's first row beyond the rows
+    assert library.nvfp4_moe_place(16, 1, 8, 2, 2, None, 128, 16, 16, 16, None) == \
+        native.E_INVALID_ARGUMENT
     with pytest.raises(ValueError):
         native.check(native.E_UNSUPPORTED_SHAPE)
     with pytest.raises(RuntimeError):
