@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 SETS = 3       # operand sets that rotate (more than L2 for the large shapes)
 LAUNCHES = 30  # per timed graph replay
-TOLERANCE = 1.20
+TOLERANCE = 1.30  # candidates within 15 % of each other swap places from GPU to GPU
 
 
 def random_operands(kind, m, n, k, device):
