@@ -1082,6 +1082,94 @@ def row_moe(device) -> list[dict]:
     return out
 
 
+def row_expert_parallel(info, device) -> dict:
+    """The MoE layer expert-parallel over the ranks of this run: DeepSeek-V3's 256 experts
+    (hidden 7168, intermediate 2048) in contiguous blocks per rank, 2,048 BF16 tokens per rank
+    routed top-8 over all experts; one forward = route, two all-to-all exchanges (rows out as
+    BF16, back as FP16), the local experts on the grouped kernels, weighted combine. Expert e's
+    weights come from seed e on whichever rank owns it, so rank 0 can rebuild any expert and
+    checks a few of its tokens against the stage-by-stage torch reference."""
+    from harness import moe
+    from harness.models import MODELS
+    from harness.workloads import quantization as q
+
+    spec = MODELS["deepseek_v3"]
+    world, rank = info.world, info.rank
+    experts, hidden = spec.experts, spec.hidden
+    (two_i, _), (_, inter) = spec.linear_shapes()["expert_gate_up"], spec.linear_shapes()["expert_down"]
+    per_rank = -(-experts // world)
+    tokens, choices = 2048, spec.top_k
+
+    def expert_weights(e: int):
+        g = torch.Generator(device=device).manual_seed(5000 + e)
+        out = []
+        for rows, k in ((two_i, hidden), (hidden, inter)):
+            w = torch.randn((1, rows, k), device=device, generator=g) * 0.05
+            p, blocked = q.quantize_nvfp4_native(w.permute(1, 2, 0))
+            out += [p[..., 0], blocked[0].view(torch.uint8)]
+        return out  # w13, w13 scales (blocked bytes), w2, w2 scales (blocked bytes)
+
+    mine = range(rank * per_rank, min(experts, (rank + 1) * per_rank))
+    parts = [expert_weights(e) for e in mine]
+    layer = moe.MoELayer(*(torch.stack([p[i] for p in parts]) for i in range(4)), fused=True)
+    del parts
+    g = torch.Generator(device=device).manual_seed(7000 + rank)
+    x = torch.randn((tokens, hidden), device=device, generator=g).to(torch.bfloat16)
+    scores = torch.rand((tokens, experts), device=device, generator=g)
+    weights, ids = torch.topk(scores, choices, dim=1)
+    weights = weights / weights.sum(dim=1, keepdim=True)
+    local = moe.ep_local_experts(layer)
+
+    def forward():
+        return moe.moe_forward_ep(x, ids, weights, experts, local)
+
+    out = forward()
+    layer.check_status()
+    ok = bool(torch.isfinite(out).all())
+    if rank == 0:
+        sample = slice(0, 4)
+        want = torch.zeros((4, hidden), dtype=torch.float32, device=device)
+        for t in range(4):
+            for j in range(choices):
+                e = int(ids[t, j])
+                w13, s13, w2, s2 = expert_weights(e)
+                y = moe.expert_reference(
+                    x[t:t + 1].float(), w13,
+                    q.from_blocked_scales(s13[None].view(torch.float8_e4m3fn), two_i, hidden // 16)[..., 0],
+                    w2, q.from_blocked_scales(s2[None].view(torch.float8_e4m3fn), hidden, inter // 16)[..., 0],
+                    fused=True)
+                want[t] += weights[t, j] * y[0].float()
+        error = ((out[sample] - want).norm() / want.norm()).item()
+        ok = ok and error < 1e-2
+    else:
+        error = 0.0
+    for _ in range(2):
+        forward()
+    info.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    repeats = 10
+    start.record()
+    for _ in range(repeats):
+        forward()
+    stop.record()
+    info.barrier()
+    us, = info.max_over_ranks([start.elapsed_time(stop) * 1e3 / repeats], device)
+    ok_all, = info.max_over_ranks([0.0 if ok else 1.0], device)
+    layer.check_status()
+    layer.close()
+    torch.cuda.empty_cache()
+    flops = 2.0 * tokens * world * choices * (two_i * hidden + hidden * inter)
+    return {"config": "moe_expert_parallel",
+            "workload": f"deepseek_v3 experts: {experts} over {world} ranks ({per_rank} each), "
+                        f"{tokens} bf16 tokens per rank, top-{choices}, hidden {hidden}, "
+                        f"intermediate {inter}",
+            "us_per_forward": us, "tflops": flops / us / 1e6,
+            "validated": ok_all == 0.0, "relative_error_of_sampled_tokens": error,
+            "exchange": "torch.distributed all_to_all_single over NCCL: rows out as BF16, back as "
+                        "FP16; no peer-memory kernel",
+            "timing": "CUDA events around 10 forwards called from Python, max over ranks"}
+
+
 def next_rows(device, only: str = "") -> list[dict]:
     """The rows beside the GEMM path (quantiser, NVFP4-output epilogues, shuffled weights, the
     MoE layer), each validated and timed like ``configs``. A row that fails says so and the
@@ -1330,6 +1418,11 @@ def main() -> None:
                     configs.append(measure_config(other, info, device, args.scaling, steps, 20,
                                                   issue_tflops, placement="lpt",
                                                   use_graph=not args.no_graph))
+            if world > 1:
+                try:
+                    configs.append(row_expert_parallel(info, device))
+                except Exception as error:  # reported, not hidden; every rank raises or none
+                    configs.append({"config": "moe_expert_parallel", "failed": repr(error)[:400]})
         all_clock = clocks.summary()
 
     if info.rank == 0:
