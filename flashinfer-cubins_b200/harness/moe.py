@@ -420,6 +420,36 @@ def expert_owner(expert: torch.Tensor, experts: int, world: int) -> torch.Tensor
     return expert // per_rank
 
 
+def _group_by(keys: torch.Tensor, groups: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Positions that put equal ``keys`` (in ``[0, groups)``) next to each other, groups in
+    order: ``(order, place, counts)`` with ``order[p]`` the item at position p, ``place`` its
+    inverse and ``counts`` the items per group (a device tensor). On a GPU the library's
+    routing kernels do it in two launches (the order inside a group is then not fixed); on the
+    CPU a stable sort."""
+    if keys.is_cuda:
+        device, items = keys.device, keys.numel()
+        keys = keys.contiguous()
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            scratch = torch.empty((2, groups), dtype=torch.int32, device=device)
+            wide = keys.dtype == torch.int64
+            native.moe_count(keys.data_ptr(), wide, items, groups, scratch[0].data_ptr(), stream)
+            counts = scratch[0].tolist()
+            firsts, total = [], 0
+            for count in counts:
+                firsts.append(total)
+                total += count
+            place = torch.empty((items,), dtype=torch.int32, device=device)
+            order = torch.empty((max(items, 1),), dtype=torch.int32, device=device)
+            native.moe_place(keys.data_ptr(), wide, items, 1, firsts, items, scratch[1].data_ptr(),
+                             place.data_ptr(), order.data_ptr(), stream)
+        return order[:items].long(), place.long(), scratch[0].long()
+    order = torch.argsort(keys, stable=True)
+    place = torch.empty_like(order)
+    place[order] = torch.arange(order.numel(), device=order.device)
+    return order, place, torch.bincount(keys, minlength=groups)
+
+
 def moe_forward_ep(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
                    experts: int,
                    local_experts: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
@@ -438,8 +468,9 @@ def moe_forward_ep(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.
     per_rank = -(-experts // world)
     flat = topk_ids.reshape(-1)
     owner = expert_owner(flat, experts, world)
-    order = torch.argsort(owner, stable=True)          # pairs grouped by destination rank
-    send_counts = torch.bincount(owner, minlength=world)
+    # Pairs grouped by destination rank: `order` (the pair at every position of the send
+    # buffer) and `place` (its inverse).
+    order, place, send_counts = _group_by(owner, world)
     recv_counts = torch.empty_like(send_counts)
     dist.all_to_all_single(recv_counts, send_counts, group=group)
     send_split, recv_split = send_counts.tolist(), recv_counts.tolist()
@@ -458,10 +489,7 @@ def moe_forward_ep(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.
     back = torch.empty((sum(send_split), hidden), dtype=done.dtype, device=x.device)
     dist.all_to_all_single(back, done, send_split, recv_split, group=group)
     # back[i] is the result of pair order[i]: put the pairs back in token order and combine.
-    place = torch.empty_like(order)
-    place[order] = torch.arange(order.numel(), device=order.device)
-    out = _combine(back, place, topk_weights)
-    return out
+    return _combine(back, place, topk_weights)
 
 
 def ep_local_experts(layer: MoELayer) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
