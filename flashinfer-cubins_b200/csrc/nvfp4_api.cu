@@ -1596,6 +1596,29 @@ int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int cho
   return 0;
 }
 
+int nvfp4_moe_combine(const void* y, const int* row_of_pair, const float* weights, float* out,
+                      int tokens, int choices, int hidden, void* stream) {
+  if (y == nullptr || row_of_pair == nullptr || weights == nullptr || out == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  }
+  if (tokens < 0 || choices < 1 || hidden < 8 || hidden % 8 != 0) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "unsupported combine: %d tokens, %d choices, hidden %d",
+                tokens, choices, hidden);
+  }
+  if (!aligned(y, 16) || !aligned(out, 16) || !aligned(row_of_pair, 4) || !aligned(weights, 4)) {
+    return fail(NVFP4_E_MISALIGNED, "misaligned operand address");
+  }
+  if (tokens == 0) return 0;
+  const int threads = 256;
+  const long long work = static_cast<long long>(tokens) * (hidden / 8);
+  const unsigned int blocks = static_cast<unsigned int>(
+      std::min<long long>((work + threads - 1) / threads, 16ll * current_sm_count()));
+  moe_combine_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(y), row_of_pair, weights, out, tokens, choices, hidden);
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
 int nvfp4_silu_product(const float* h1, const float* h2, void* out, int64_t size, void* stream) {
   if (h1 == nullptr || h2 == nullptr || out == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");

@@ -294,6 +294,39 @@ __global__ void moe_place_kernel(const Id* __restrict__ ids, long long pairs, in
   }
 }
 
+// The combine of a mixture-of-experts layer: out[t][:] = sum_j weights[t][j] * y[row(t, j)][:]
+// in FP32, y FP16 rows picked by row_of_pair[t * choices + j] (a negative row contributes
+// nothing). One thread per token and eight columns: `choices` 16-byte loads, two 16-byte
+// stores; every row of y is read once.
+__global__ void moe_combine_kernel(const __half* __restrict__ y, const int* __restrict__ row_of_pair,
+                                   const float* __restrict__ weights, float* __restrict__ out,
+                                   int tokens, int choices, int hidden) {
+  const int chunks = hidden / 8;
+  const long long total = static_cast<long long>(tokens) * chunks;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / chunks);
+    const int c = static_cast<int>(i % chunks);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < choices; ++j) {
+      const int row = __ldg(row_of_pair + static_cast<long long>(t) * choices + j);
+      if (row < 0) continue;
+      const float w = __ldg(weights + static_cast<long long>(t) * choices + j);
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + static_cast<long long>(row) * hidden) + c);
+      const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&words[q]));
+        acc[2 * q] = fmaf(w, f.x, acc[2 * q]);
+        acc[2 * q + 1] = fmaf(w, f.y, acc[2 * q + 1]);
+      }
+    }
+    float4* dst = reinterpret_cast<float4*>(out + static_cast<long long>(t) * hidden) + 2 * c;
+    dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
 // silu(a) * b with ex2.approx and rcp.approx (no slow path when exp(-a) overflows).
 __device__ __forceinline__ float silu_gate(float a, float b) {
   float e, r;

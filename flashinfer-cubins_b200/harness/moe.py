@@ -136,10 +136,20 @@ def _gather(x: torch.Tensor, source: torch.Tensor, choices: int) -> torch.Tensor
 
 
 def _combine(y: torch.Tensor, row_of_pair: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
-    """``out[t] = sum_j weights[t, j] * y[row of pair (t, j)]`` in FP32: one gather of the
-    pairs' rows and one batched product, no atomics."""
+    """``out[t] = sum_j weights[t, j] * y[row of pair (t, j)]`` in FP32, no atomics: on a GPU
+    the library's combine kernel (every row of ``y`` read once), elsewhere one gather and one
+    batched product."""
     tokens, choices = weights.shape
-    picked = y.index_select(0, row_of_pair).view(tokens, choices, y.shape[1])
+    hidden = y.shape[1]
+    if y.is_cuda and y.dtype == torch.float16 and hidden % 8 == 0 and y.is_contiguous():
+        rows = row_of_pair.to(torch.int32).contiguous()
+        w = weights.float().contiguous()
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device=y.device)
+        with torch.cuda.device(y.device):
+            native.moe_combine(y.data_ptr(), rows.data_ptr(), w.data_ptr(), out.data_ptr(), tokens,
+                               choices, hidden, torch.cuda.current_stream(y.device).cuda_stream)
+        return out
+    picked = y.index_select(0, row_of_pair).view(tokens, choices, hidden)
     return torch.bmm(weights.float().unsqueeze(1), picked.float()).squeeze(1)
 
 

@@ -143,6 +143,9 @@ _PROTOTYPES = {
         ctypes.c_int, [_P, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, _P,
                        ctypes.c_int, _P, _P, _P, _P],
     ),
+    "nvfp4_moe_combine": (
+        ctypes.c_int, [_P, _P, _P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
+    ),
     "nvfp4_silu_product": (ctypes.c_int, [_P, _P, _P, ctypes.c_int64, _P]),
     "nvfp4_measure_mma_peak": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
 }
@@ -401,6 +404,12 @@ def moe_place(ids: int, ids_are_64bit: bool, pairs: int, choices: int, first_row
     starts = (ctypes.c_int * len(first_rows))(*first_rows)
     check(load().nvfp4_moe_place(ids, int(ids_are_64bit), pairs, choices, len(first_rows), starts,
                                  rows, cursors, row_of_pair, token_of_row, stream))
+
+
+def moe_combine(y: int, row_of_pair: int, weights: int, out: int, tokens: int, choices: int,
+                hidden: int, stream: int) -> None:
+    """``out[t] = sum_j weights[t, j] * y[row_of_pair[t * choices + j]]`` (FP16 rows, FP32 out)."""
+    check(load().nvfp4_moe_combine(y, row_of_pair, weights, out, tokens, choices, hidden, stream))
 
 
 def measure_mma_peak(device: int, iters: int = 4096) -> float:

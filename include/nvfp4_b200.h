@@ -314,6 +314,13 @@ int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int cho
                     const int* first_rows, int rows, int* cursors, int* row_of_pair,
                     int* token_of_row, void* stream);
 
+/* The combine of that layer: out[t][:] = sum over j of weights[t][j] * y[row_of_pair[t * choices
+ * + j]][:] in FP32 (`out` [tokens][hidden] FP32, `y` FP16 rows of `hidden` columns, `weights`
+ * [tokens][choices] FP32, `row_of_pair` as nvfp4_moe_place wrote it; a negative row adds
+ * nothing). hidden % 8 == 0; y and out 16-byte aligned. */
+int nvfp4_moe_combine(const void* y, const int* row_of_pair, const float* weights, float* out,
+                      int tokens, int choices, int hidden, void* stream);
+
 /* out[i] = half(silu(h1[i]) * h2[i]) over `size` FP32 elements. Replaces the
  * silu_product kernel (impls/nvfp4_dual_gemm/kernels/silu_product.cu:7-9,
  * harness/workloads/nvfp4_dual_gemm.py:352-367). */

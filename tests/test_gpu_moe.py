@@ -136,6 +136,30 @@ def test_device_routing_places_every_pair_in_its_experts_block(tokens, experts, 
     assert routing.token_of_row.numel() == max(128, sum(-(-c // 128) * 128 for c in routing.counts))
 
 
+def test_combine_kernel_matches_a_gather_and_a_batched_product():
+    """nvfp4_moe_combine: the weighted sum of each token's rows in FP32, padding rows (-1)
+    adding nothing."""
+    device = torch.device("cuda:0")
+    tokens, choices, hidden, rows = 333, 4, 1032, 2000
+    g = torch.Generator().manual_seed(11)
+    y = torch.randn(rows, hidden, generator=g).half().to(device)
+    picks = torch.randint(0, rows, (tokens, choices), generator=g, dtype=torch.int32)
+    picks[5, 1] = -1
+    picks = picks.to(device)
+    weights = torch.rand(tokens, choices, generator=g).to(device)
+    out = torch.full((tokens, hidden), float("nan"), device=device)
+    native.moe_combine(y.data_ptr(), picks.data_ptr(), weights.data_ptr(), out.data_ptr(), tokens,
+                       choices, hidden, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    picked = y.float()[picks.clamp(min=0).long().reshape(-1)].view(tokens, choices, hidden)
+    used = (picks >= 0).float() * weights
+    want = torch.einsum("tk,tkh->th", used.double(), picked.double())
+    assert torch.allclose(out.double(), want, rtol=1e-6, atol=1e-6)
+    with pytest.raises(ValueError):
+        native.moe_combine(y.data_ptr(), picks.data_ptr(), weights.data_ptr(), out.data_ptr(),
+                           tokens, choices, 1030, 0)
+
+
 def test_fused_and_unfused_layers_agree():
     device = torch.device("cuda:0")
     tokens, hidden, inter, experts, choices = 300, 512, 256, 5, 2
