@@ -257,6 +257,11 @@ struct nvfp4_plan {
   long long total_tiles = 0, total_units = 0;
   long long slot_floats = 0;
   size_t off_counters = 0, off_table = 0, off_maps = 0, off_partials = 0, ws_bytes = 0;
+  // Routed groups (nvfp4_moe_plan_create): every group's row count is decided on the device
+  // before each launch; the groups share A, D and scale buffers of `routed_rows` rows.
+  bool routed = false;
+  int routed_rows = 0;
+  size_t off_routed = 0;  // RoutedHeader in the workspace
   // Everything above is fixed once the plan has been created. The only state a launch may
   // touch is this cache of encoded kernel parameters (tensor maps are ~2 us each to encode),
   // keyed by the operand and workspace addresses and guarded by `mutex`; a launch copies its
@@ -540,9 +545,13 @@ void fill_common_params(const nvfp4_plan* plan, KernelParams& kp, void* workspac
   for (const ProblemDesc& pd : plan->problems) {
     if (pd.tiles_m > 1) streams = false;
   }
+  if (plan->routed) streams = false;  // the groups' sizes are not known here
   kp.b_streams = streams ? 1 : 0;
   kp.b_shuffle = plan->b_shuffle;
   kp.maps_per_group = plan->maps_per_group;
+  kp.routed_tiles =
+      plan->routed ? &reinterpret_cast<const RoutedHeader*>(ws + plan->off_routed)->total_tiles
+                   : nullptr;
 }
 
 // The kernel parameters of a dense or dual launch on the operands named by `key`: taken from
@@ -946,6 +955,65 @@ int nvfp4_group_dual_gemm_plan_create_fp4(nvfp4_plan** out, int device, int grou
   return 0;
 }
 
+int nvfp4_moe_plan_create(nvfp4_plan** out, int device, int experts, int n, int k, int max_rows,
+                          int out_kind, const nvfp4_config* config) {
+  if (out == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "plan is null");
+  *out = nullptr;
+  const bool dual = out_kind == NVFP4_OUT_FP4;
+  if (out_kind != NVFP4_OUT_F16 && !dual) {
+    return fail(NVFP4_E_INVALID_ARGUMENT,
+                "a routed plan is the gate/up projection with NVFP4 output or a GEMM with FP16 output");
+  }
+  if (experts < 1 || experts > kMoeMaxExperts) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE, "1 to %d experts", kMoeMaxExperts);
+  }
+  if (n < 1 || k < 32 || k % 32 != 0 || n % (dual ? 64 : 8) != 0 || max_rows < 128 ||
+      max_rows % 128 != 0) {
+    return fail(NVFP4_E_UNSUPPORTED_SHAPE,
+                "unsupported routed problem n=%d k=%d rows=%d (rows a multiple of 128)", n, k,
+                max_rows);
+  }
+  if (config != nullptr && (config->schedule > 1 || config->pair > 0)) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "routed plans are data parallel on single CTAs");
+  }
+  int sms = 0;
+  if (int rc = check_device(device, &sms)) return rc;
+  nvfp4_plan* plan = new (std::nothrow) nvfp4_plan();
+  if (plan == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "out of host memory");
+  plan->kind = kGrouped;
+  plan->device = device;
+  plan->out_kind = out_kind;
+  plan->sm_count = sms;
+  plan->maps_per_group = dual ? 3 : 2;
+  plan->tile_n = default_tile_n(config, 256);
+  if ((plan->tile_n != 128 && plan->tile_n != 256) && (dual || plan->tile_n != 64)) {
+    delete plan;
+    return fail(NVFP4_E_INVALID_ARGUMENT, "no kernel for tile_n=%d", plan->tile_n);
+  }
+  plan->out_tile_n = dual ? plan->tile_n / 2 : plan->tile_n;
+  plan->problems.resize(experts);
+  for (int g = 0; g < experts; ++g) {
+    fill_problem(&plan->problems[g], 0, n, k, 1, plan->out_tile_n);
+  }
+  nvfp4_config whole_tiles = {};
+  if (config != nullptr) whole_tiles = *config;
+  whole_tiles.schedule = 1;
+  finish_schedule(plan, &whole_tiles);
+  // The groups' sizes are known on the device only: every SM gets a CTA, and the table that
+  // the layout kernel fills in follows the maps in the workspace.
+  plan->ctas = config != nullptr && config->ctas > 0 ? std::min(config->ctas, sms) : sms;
+  plan->routed = true;
+  plan->routed_rows = max_rows;
+  plan->off_routed = round_up(plan->ws_bytes, 256);
+  plan->ws_bytes = plan->off_routed + round_up(sizeof(RoutedHeader), 256);
+  if (int rc = prepare_kernel(plan)) {
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return 0;
+}
+
 void nvfp4_plan_destroy(nvfp4_plan* plan) { delete plan; }
 
 size_t nvfp4_plan_workspace_bytes(const nvfp4_plan* plan) {
@@ -1249,6 +1317,23 @@ namespace {
 // Behind nvfp4_group_gemm_bind and nvfp4_group_dual_gemm_bind_fp4 (`b2`, `sfb2`, `sfd` null
 // for the former): checks the pointers, encodes the groups' tensor maps and writes the
 // group table into the workspace.
+// Host bytes into device memory as kernel parameters, 3.5 KB per launch: parameters are copied
+// when a launch is enqueued, so the source may go out of scope when this returns. (An
+// asynchronous copy from pageable memory may still be reading its source then.) `bytes` is
+// rounded up to 16; the destination has room for that.
+int deliver_bytes(uint8_t* dst, const void* src, size_t bytes, void* stream) {
+  const uint8_t* from = static_cast<const uint8_t*>(src);
+  for (size_t done = 0; done < bytes; done += ParamBlob::kBytes) {
+    ParamBlob blob = {};
+    const size_t part = std::min<size_t>(ParamBlob::kBytes, bytes - done);
+    std::memcpy(blob.data, from + done, part);
+    write_blob_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        dst + done, blob, static_cast<int>((part + 15) / 16 * 16));
+    CUDA_TRY(cudaGetLastError());
+  }
+  return 0;
+}
+
 int bind_groups(const nvfp4_plan* plan, const void* const* a, const void* const* b,
                 const void* const* b2, const void* const* sfa, const void* const* sfb,
                 const void* const* sfb2, void* const* d, void* const* sfd, void* workspace,
@@ -1301,18 +1386,75 @@ int bind_groups(const nvfp4_plan* plan, const void* const* a, const void* const*
       std::memcpy(slot + 2 * sizeof(tmp), &tmp, sizeof(tmp));
     }
   }
-  // Into the workspace as kernel parameters, 3.5 KB per launch: parameters are copied when a
-  // launch is enqueued, so `staging` may go out of scope when this function returns. (An
-  // asynchronous copy from pageable memory may still be reading its source then.)
   uint8_t* dst = static_cast<uint8_t*>(workspace) + plan->off_table;
-  for (size_t done = 0; done < table_bytes; done += ParamBlob::kBytes) {
-    ParamBlob blob;
-    const size_t bytes = std::min<size_t>(ParamBlob::kBytes, table_bytes - done);
-    std::memcpy(blob.data, staging.data() + done, bytes);
-    write_blob_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(dst + done, blob,
-                                                                        static_cast<int>(bytes));
-    CUDA_TRY(cudaGetLastError());
+  if (int rc = deliver_bytes(dst, staging.data(), table_bytes, stream)) return rc;
+  {
+    std::lock_guard<std::mutex> lock(plan->mutex);
+    plan->group_bound = true;
   }
+  return 0;
+}
+
+// The bind of a routed plan (nvfp4_moe_bind): what does not depend on the groups' row counts.
+int bind_routed(const nvfp4_plan* plan, const void* a, const void* sfa, const void* const* b,
+                const void* const* sfb, const void* const* b2, const void* const* sfb2, void* d,
+                void* sfd, void* workspace, void* stream) {
+  const bool dual = plan->maps_per_group == 3;
+  if (a == nullptr || sfa == nullptr || b == nullptr || sfb == nullptr || d == nullptr ||
+      workspace == nullptr || (dual && (b2 == nullptr || sfb2 == nullptr || sfd == nullptr))) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "null pointer");
+  }
+  if (!aligned(workspace, 256)) return fail(NVFP4_E_MISALIGNED, "workspace must be 256-byte aligned");
+  if (!aligned(a, 16) || !aligned(sfa, 16) || !aligned(d, 16) || !aligned(sfd, 16)) {
+    return fail(NVFP4_E_MISALIGNED, "shared buffers must be 16-byte aligned");
+  }
+  const size_t groups = plan->problems.size();
+  for (size_t g = 0; g < groups; ++g) {
+    if (b[g] == nullptr || sfb[g] == nullptr || (dual && (b2[g] == nullptr || sfb2[g] == nullptr))) {
+      return fail(NVFP4_E_INVALID_ARGUMENT, "group %zu: null operand", g);
+    }
+    if (!aligned(b[g], 16) || !aligned(sfb[g], 16) ||
+        (dual && (!aligned(b2[g], 16) || !aligned(sfb2[g], 16)))) {
+      return fail(NVFP4_E_MISALIGNED, "group %zu: operands must be 16-byte aligned", g);
+    }
+  }
+  DeviceGuard guard;
+  CUDA_TRY(guard.enter(plan->device));
+  const size_t table_bytes = plan->off_partials - plan->off_table;
+  std::vector<uint8_t> staging(table_bytes, 0);
+  ProblemDesc* table = reinterpret_cast<ProblemDesc*>(staging.data());
+  uint8_t* maps = staging.data() + (plan->off_maps - plan->off_table);
+  const int per_group = plan->maps_per_group;
+  const int b_box_rows = dual ? plan->out_tile_n : plan->tile_n;
+  const ProblemDesc& shape = plan->problems[0];
+  CUtensorMap tmp;
+  // Slot 0 of group 0: the A buffer all groups share (the other groups' A slots stay unused).
+  if (int rc = encode_operand_map(&tmp, a, plan->routed_rows, shape.k, 1, 128)) return rc;
+  std::memcpy(maps, &tmp, sizeof(tmp));
+  for (size_t g = 0; g < groups; ++g) {
+    ProblemDesc pd = plan->problems[g];  // m = 0 until the layout kernel has run
+    pd.sfb = static_cast<const uint8_t*>(sfb[g]);
+    pd.sfb2 = dual ? static_cast<const uint8_t*>(sfb2[g]) : nullptr;
+    table[g] = pd;
+    uint8_t* slot = maps + g * per_group * sizeof(CUtensorMap);
+    if (int rc = encode_operand_map(&tmp, b[g], pd.n, pd.k, 1, b_box_rows)) return rc;
+    std::memcpy(slot + sizeof(tmp), &tmp, sizeof(tmp));
+    if (dual) {
+      if (int rc = encode_operand_map(&tmp, b2[g], pd.n, pd.k, 1, b_box_rows)) return rc;
+      std::memcpy(slot + 2 * sizeof(tmp), &tmp, sizeof(tmp));
+    }
+  }
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (int rc = deliver_bytes(ws + plan->off_table, staging.data(), table_bytes, stream)) return rc;
+  RoutedHeader header = {};
+  header.sfa_base = static_cast<const uint8_t*>(sfa);
+  header.d_base = static_cast<uint8_t*>(d);
+  header.sfd_base = dual ? static_cast<uint8_t*>(sfd) : nullptr;
+  header.d_row_bytes = dual ? shape.n / 2 : 2ll * shape.n;
+  header.sfa_block_bytes = 512ll * shape.sf_kb;
+  header.sfd_block_bytes = 512ll * ceil_div(shape.n, 64);
+  header.max_rows = plan->routed_rows;
+  if (int rc = deliver_bytes(ws + plan->off_routed, &header, sizeof(header), stream)) return rc;
   {
     std::lock_guard<std::mutex> lock(plan->mutex);
     plan->group_bound = true;
@@ -1327,7 +1469,7 @@ extern "C" {
 int nvfp4_group_gemm_bind(const nvfp4_plan* plan, const void* const* a, const void* const* b,
                           const void* const* sfa, const void* const* sfb, void* const* d,
                           void* workspace, void* stream) {
-  if (plan == nullptr || plan->kind != kGrouped || plan->maps_per_group != 2) {
+  if (plan == nullptr || plan->kind != kGrouped || plan->maps_per_group != 2 || plan->routed) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped GEMM plan");
   }
   return bind_groups(plan, a, b, nullptr, sfa, sfb, nullptr, d, nullptr, workspace, stream);
@@ -1338,10 +1480,35 @@ int nvfp4_group_dual_gemm_bind_fp4(const nvfp4_plan* plan, const void* const* a,
                                    const void* const* sfa, const void* const* sfb1,
                                    const void* const* sfb2, void* const* d_packed,
                                    void* const* d_scales, void* workspace, void* stream) {
-  if (plan == nullptr || plan->kind != kGrouped || plan->maps_per_group != 3) {
+  if (plan == nullptr || plan->kind != kGrouped || plan->maps_per_group != 3 || plan->routed) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "not a grouped dual GEMM plan");
   }
   return bind_groups(plan, a, b1, b2, sfa, sfb1, sfb2, d_packed, d_scales, workspace, stream);
+}
+
+int nvfp4_moe_bind(const nvfp4_plan* plan, const void* a, const void* sfa, const void* const* b,
+                   const void* const* sfb, const void* const* b2, const void* const* sfb2, void* d,
+                   void* d_scales, void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kGrouped || !plan->routed) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a routed plan");
+  }
+  return bind_routed(plan, a, sfa, b, sfb, b2, sfb2, d, d_scales, workspace, stream);
+}
+
+int nvfp4_moe_layout(const nvfp4_plan* plan, const int* counts, void* workspace, void* stream) {
+  if (plan == nullptr || plan->kind != kGrouped || !plan->routed) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a routed plan");
+  }
+  if (counts == nullptr || workspace == nullptr || !aligned(workspace, 256) || !aligned(counts, 4)) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "counts or workspace is null or misaligned");
+  }
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  moe_layout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<ProblemDesc*>(ws + plan->off_table),
+      reinterpret_cast<RoutedHeader*>(ws + plan->off_routed), counts,
+      static_cast<int>(plan->problems.size()));
+  CUDA_TRY(cudaGetLastError());
+  return 0;
 }
 
 int nvfp4_group_gemm_launch(const nvfp4_plan* plan, void* workspace, void* stream) {
@@ -1555,11 +1722,12 @@ int nvfp4_moe_count(const void* ids, int ids_are_64bit, long long pairs, int exp
   return 0;
 }
 
-int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int choices, int experts,
-                    const int* first_rows, int rows, int* cursors, int* row_of_pair,
-                    int* token_of_row, void* stream) {
-  if (ids == nullptr || first_rows == nullptr || cursors == nullptr || row_of_pair == nullptr ||
-      token_of_row == nullptr) {
+static int moe_place_common(const void* ids, int ids_are_64bit, long long pairs, int choices,
+                            int experts, const int* host_first_rows, const int* device_first_rows,
+                            int rows, int* cursors, int* row_of_pair, int* token_of_row,
+                            void* stream) {
+  if (ids == nullptr || (host_first_rows == nullptr && device_first_rows == nullptr) ||
+      cursors == nullptr || row_of_pair == nullptr || token_of_row == nullptr) {
     return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
   }
   if (pairs < 0 || choices < 1 || rows < 0 || experts < 1 || experts > kMoeMaxExperts) {
@@ -1567,12 +1735,12 @@ int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int cho
                 pairs, experts, kMoeMaxExperts);
   }
   MoeStarts starts = {};
-  for (int e = 0; e < experts; ++e) {
-    if (first_rows[e] < 0 || first_rows[e] > rows) {
+  for (int e = 0; host_first_rows != nullptr && e < experts; ++e) {
+    if (host_first_rows[e] < 0 || host_first_rows[e] > rows) {
       return fail(NVFP4_E_INVALID_ARGUMENT, "expert %d: first row %d outside [0, %d]", e,
-                  first_rows[e], rows);
+                  host_first_rows[e], rows);
     }
-    starts.first_row[e] = first_rows[e];
+    starts.first_row[e] = host_first_rows[e];
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CUDA_TRY(cudaMemsetAsync(cursors, 0, sizeof(int) * static_cast<size_t>(experts), s));
@@ -1585,15 +1753,37 @@ int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int cho
       std::min<long long>((pairs + threads - 1) / threads, 4ll * current_sm_count()));
   if (ids_are_64bit) {
     moe_place_kernel<long long><<<blocks, threads, 0, s>>>(static_cast<const long long*>(ids), pairs,
-                                                           choices, experts, starts, cursors,
-                                                           row_of_pair, token_of_row);
+                                                           choices, experts, starts,
+                                                           device_first_rows, cursors, row_of_pair,
+                                                           token_of_row);
   } else {
     moe_place_kernel<int><<<blocks, threads, 0, s>>>(static_cast<const int*>(ids), pairs, choices,
-                                                     experts, starts, cursors, row_of_pair,
-                                                     token_of_row);
+                                                     experts, starts, device_first_rows, cursors,
+                                                     row_of_pair, token_of_row);
   }
   CUDA_TRY(cudaGetLastError());
   return 0;
+}
+
+int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int choices, int experts,
+                    const int* first_rows, int rows, int* cursors, int* row_of_pair,
+                    int* token_of_row, void* stream) {
+  if (first_rows == nullptr) return fail(NVFP4_E_INVALID_ARGUMENT, "null operand");
+  return moe_place_common(ids, ids_are_64bit, pairs, choices, experts, first_rows, nullptr, rows,
+                          cursors, row_of_pair, token_of_row, stream);
+}
+
+int nvfp4_moe_place_routed(const void* ids, int ids_are_64bit, long long pairs, int choices,
+                           const nvfp4_plan* plan, void* workspace, int* cursors, int* row_of_pair,
+                           int* token_of_row, void* stream) {
+  if (plan == nullptr || !plan->routed || workspace == nullptr) {
+    return fail(NVFP4_E_INVALID_ARGUMENT, "not a routed plan and its workspace");
+  }
+  const RoutedHeader* header =
+      reinterpret_cast<const RoutedHeader*>(static_cast<uint8_t*>(workspace) + plan->off_routed);
+  return moe_place_common(ids, ids_are_64bit, pairs, choices,
+                          static_cast<int>(plan->problems.size()), nullptr, header->first_rows,
+                          plan->routed_rows, cursors, row_of_pair, token_of_row, stream);
 }
 
 int nvfp4_moe_combine(const void* y, const int* row_of_pair, const float* weights, float* out,

@@ -62,9 +62,65 @@ struct alignas(16) ProblemDesc {
   uint8_t* sfd;          // NVFP4 output: blocked UE4M3 scales of D (rows m, one per 16 columns)
   long long tile_begin;  // first global tile index of this problem
   long long unit_begin;  // first global (tile, k-tile) unit of this problem
+  int a_row0;            // routed groups: the group's first row in the A buffer all groups share
+  int reserved;
 };
 
 enum : int { kModeDataParallel = 0, kModeStreamK = 1 };
+
+// Routed groups: what the device needs to lay the groups out once the row count of every
+// group is known (it lives in the plan's workspace, written by the bind).
+struct alignas(16) RoutedHeader {
+  long long total_tiles;        // written by moe_layout_kernel, read by the GEMM kernel
+  const uint8_t* sfa_base;      // scales of the shared A buffer (blocked, 128-row atom rows)
+  uint8_t* d_base;              // output buffer all groups share
+  uint8_t* sfd_base;            // its scales (NVFP4 output) or null
+  long long d_row_bytes;        // bytes of one output row
+  long long sfa_block_bytes;    // bytes of one 128-row atom row of A's scales
+  long long sfd_block_bytes;    // the same for D's scales
+  int max_rows;                 // rows of the shared buffers (a multiple of 128)
+  int overflow;                 // set if the groups' padded rows did not fit
+  int first_rows[kMoeMaxExperts];  // written by moe_layout_kernel: first row of every group
+};
+
+// Fills in what depends on the groups' row counts: every group's m, tile counts, first row
+// in the shared buffers (blocks padded to 128 rows), operand addresses, and the totals. One
+// thread walks the groups (at most 512); the rest of the table was written by the bind.
+__global__ void moe_layout_kernel(ProblemDesc* __restrict__ table, RoutedHeader* __restrict__ header,
+                                  const int* __restrict__ counts, int groups) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  long long tiles = 0;
+  int row = 0;
+  int overflow = 0;
+  for (int g = 0; g < groups; ++g) {
+    ProblemDesc pd = table[g];
+    int m = counts[g];
+    if (m < 0) m = 0;
+    int blocks = (m + 127) / 128;
+    if (row + blocks * 128 > header->max_rows) {  // does not fit: drop what is beyond
+      blocks = (header->max_rows - row) / 128;
+      m = min(m, blocks * 128);
+      overflow = 1;
+    }
+    pd.m = m;
+    pd.tiles_m = blocks;
+    pd.sf_mb = blocks;
+    pd.a_row0 = row;
+    pd.sfa = header->sfa_base + static_cast<long long>(row / 128) * header->sfa_block_bytes;
+    pd.d = header->d_base + static_cast<long long>(row) * header->d_row_bytes;
+    pd.sfd = header->sfd_base != nullptr
+                 ? header->sfd_base + static_cast<long long>(row / 128) * header->sfd_block_bytes
+                 : nullptr;
+    pd.tile_begin = tiles;
+    pd.unit_begin = tiles * pd.k_tiles;
+    table[g] = pd;
+    header->first_rows[g] = row;
+    tiles += static_cast<long long>(blocks) * pd.tiles_n;
+    row += blocks * 128;
+  }
+  header->total_tiles = tiles;
+  header->overflow = overflow;
+}
 
 enum : int {
   kStatusOk = 0,
@@ -101,6 +157,10 @@ struct alignas(64) KernelParams {
   int inbox_offset;  // byte offset of that inbox from the pipeline base, or -1: peers may then
                      // write only after this CTA has told them its pipeline memory is free
   int maps_per_group;  // grouped: 2, or 3 for the grouped dual GEMM
+  // Routed groups (a mixture-of-experts layer whose rows per expert are decided on the
+  // device): the number of tiles is read from here, the group table was filled in by
+  // moe_layout_kernel, and all groups share one A buffer described by maps[0]. Null otherwise.
+  const long long* routed_tiles;
 };
 
 struct Segment {
@@ -123,6 +183,9 @@ struct WorkIter {
     if (p.mode == kModeDataParallel) {
       cur = cta;
       end = p.total_tiles;
+      if constexpr (GROUPED) {
+        if (p.routed_tiles != nullptr) end = *p.routed_tiles;
+      }
       step = grid;
     } else {
       cur = p.total_units * cta / grid;
@@ -734,7 +797,8 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
       while (ok && it.next(s)) {
         const ProblemDesc& pd = it.pd;
         const CUtensorMap* group_maps = p.maps + p.maps_per_group * s.prob;  // grouped only
-        const CUtensorMap* map_a = Cfg::GROUPED ? group_maps : &p.map_a;
+        const bool routed = Cfg::GROUPED && p.routed_tiles != nullptr;
+        const CUtensorMap* map_a = Cfg::GROUPED ? (routed ? p.maps : group_maps) : &p.map_a;
         const CUtensorMap* map_b = Cfg::GROUPED ? group_maps + 1 : &p.map_b;
         const CUtensorMap* map_b2 = Cfg::GROUPED ? group_maps + 2 : &p.map_b2;
         if constexpr (Cfg::GROUPED) {
@@ -750,7 +814,7 @@ nvfp4_gemm_kernel(const __grid_constant__ KernelParams p) {
             acquired_prob = s.prob;
           }
         }
-        const int m0 = s.m_tile * Cfg::BM;
+        const int m0 = s.m_tile * Cfg::BM + (Cfg::GROUPED ? pd.a_row0 : 0);
         const int n0 = s.n_tile * Cfg::OUT_BN;
         // Scale atoms of this tile's rows: one 512-byte atom per 64 K elements, four per
         // k-tile, contiguous along K.

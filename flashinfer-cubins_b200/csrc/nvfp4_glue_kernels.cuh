@@ -280,6 +280,7 @@ __global__ void moe_count_kernel(const Id* __restrict__ ids, long long pairs, in
 template <typename Id>
 __global__ void moe_place_kernel(const Id* __restrict__ ids, long long pairs, int choices,
                                  int experts, const __grid_constant__ MoeStarts starts,
+                                 const int* __restrict__ device_starts,
                                  int* __restrict__ cursors, int* __restrict__ row_of_pair,
                                  int* __restrict__ token_of_row) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pairs;
@@ -287,7 +288,10 @@ __global__ void moe_place_kernel(const Id* __restrict__ ids, long long pairs, in
     const long long e = static_cast<long long>(ids[i]);
     int row = -1;
     if (e >= 0 && e < experts) {
-      row = starts.first_row[e] + atomicAdd(&cursors[e], 1);
+      // The blocks' first rows come from the host (a kernel parameter) or, when the layout
+      // was made on the device, from device memory.
+      const int first = device_starts != nullptr ? __ldg(device_starts + e) : starts.first_row[e];
+      row = first + atomicAdd(&cursors[e], 1);
       token_of_row[row] = static_cast<int>(i / choices);
     }
     row_of_pair[i] = row;

@@ -374,6 +374,121 @@ class MoELayer:
         return _combine(y, routing.row_of_pair, topk_weights)
 
 
+class RoutedMoELayer:
+    """The same layer with nothing read back from the device: one pair of plans
+    (``nvfp4_moe_plan_create``) and one set of buffers serve every routing of up to
+    ``max_pairs`` (token, choice) pairs. A forward is nine launches (count, two layouts, place,
+    gather-quantise, gate/up, down, combine) whose shapes do not depend on the routing, so it
+    can be captured in a CUDA graph once and replayed on new tokens and new expert choices.
+
+    The experts' blocks share buffers of ``max_pairs + 127 * E`` rows (rounded up to 128): the
+    most rows any routing can need when every expert's block is padded to whole 128-row
+    blocks. Weights as for ``MoELayer``; the intermediate size must be a multiple of 128."""
+
+    def __init__(self, w13, w13_scales, w2, w2_scales, max_pairs: int):
+        experts, two_i, half_h = w13.shape
+        self.experts, self.hidden, self.inter = experts, 2 * half_h, two_i // 2
+        hidden, inter = self.hidden, self.inter
+        if tuple(w2.shape) != (experts, hidden, inter // 2):
+            raise ValueError("w2 does not match w13")
+        if hidden % 64 or inter % ROW_BLOCK or max_pairs < 1:
+            raise ValueError("hidden must be a multiple of 64, the intermediate size of 128")
+        self.device = device = w13.device
+        if device.type != "cuda" or not native.device_supported(device.index or 0):
+            raise RuntimeError(f"sm_100a code cannot run on {device}")
+        self.max_pairs = max_pairs
+        self.capacity = capacity = -(-(max_pairs + (ROW_BLOCK - 1) * experts) // ROW_BLOCK) * ROW_BLOCK
+        self.w13, self.w13_scales, self.w2, self.w2_scales = w13, w13_scales, w2, w2_scales
+        index = device.index or 0
+        atoms_h, atoms_i = -(-hidden // 64), -(-inter // 64)
+        byte = dict(dtype=torch.uint8, device=device)
+        word = dict(dtype=torch.int32, device=device)
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            self.up_plan = native.Plan.routed(index, native.OUT_FP4, experts, inter, hidden, capacity)
+            self.down_plan = native.Plan.routed(index, native.OUT_F16, experts, hidden, inter, capacity)
+            self.up_ws, self.down_ws = (
+                torch.zeros(max(plan.workspace_bytes(), 256), **byte)
+                for plan in (self.up_plan, self.down_plan))
+            self.a1 = torch.zeros((capacity, hidden // 2), **byte)
+            self.s1 = torch.zeros((capacity // ROW_BLOCK, atoms_h, 32, 4, 4), **byte)
+            self.a2 = torch.zeros((capacity, inter // 2), **byte)
+            self.s2 = torch.zeros((capacity // ROW_BLOCK, atoms_i, 32, 4, 4), **byte)
+            self.y = torch.zeros((capacity, hidden), dtype=torch.float16, device=device)
+            self.counts = torch.zeros((experts,), **word)
+            self.cursors = torch.zeros((experts,), **word)
+            self.token_of_row = torch.full((capacity,), -1, **word)
+            self.row_of_pair = torch.zeros((max_pairs,), **word)
+            self.up_plan.init_workspace(self.up_ws.data_ptr(), stream)
+            self.down_plan.init_workspace(self.down_ws.data_ptr(), stream)
+            self.up_plan.bind_routed(
+                self.a1.data_ptr(), self.s1.data_ptr(),
+                [w13[e].data_ptr() for e in range(experts)],
+                [w13_scales[e].data_ptr() for e in range(experts)],
+                self.a2.data_ptr(), self.up_ws.data_ptr(), stream,
+                b2=[w13[e].data_ptr() + inter * (hidden // 2) for e in range(experts)],
+                sfb2=[w13_scales[e].data_ptr() + (inter // ROW_BLOCK) * atoms_h * 512
+                      for e in range(experts)],
+                d_scales=self.s2.data_ptr())
+            self.down_plan.bind_routed(
+                self.a2.data_ptr(), self.s2.data_ptr(),
+                [w2[e].data_ptr() for e in range(experts)],
+                [w2_scales[e].data_ptr() for e in range(experts)],
+                self.y.data_ptr(), self.down_ws.data_ptr(), stream)
+
+    def close(self) -> None:
+        if self.up_plan is not None:
+            torch.cuda.synchronize(self.device)
+            self.up_plan.destroy()
+            self.down_plan.destroy()
+            self.up_plan = self.down_plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check_status(self) -> None:
+        """Synchronise and raise ``native.NativeError`` if a kernel abandoned a wait."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.up_plan.status(self.up_ws.data_ptr(), stream)
+        self.down_plan.status(self.down_ws.data_ptr(), stream)
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """As ``MoELayer.forward`` (``x`` ``[T, H]`` FP32 or BF16, ids int32/int64 ``[T, K]`` in
+        ``[0, E)``, weights ``[T, K]``; FP32 ``[T, H]`` out), asynchronous from start to end."""
+        tokens, choices = topk_ids.shape
+        pairs = tokens * choices
+        if x.shape != (tokens, self.hidden) or topk_weights.shape != topk_ids.shape:
+            raise ValueError("activations, ids and weights do not match")
+        if pairs > self.max_pairs:
+            raise ValueError(f"{pairs} pairs; the layer was made for {self.max_pairs}")
+        if x.dtype not in (torch.float32, torch.bfloat16) or not x.is_contiguous():
+            x = x.float().contiguous()
+        ids = topk_ids if topk_ids.dtype in (torch.int32, torch.int64) else topk_ids.long()
+        ids = ids.contiguous()
+        weights = topk_weights.float().contiguous()
+        wide = ids.dtype == torch.int64
+        kind = native.IN_F32 if x.dtype == torch.float32 else native.IN_BF16
+        out = torch.empty((tokens, self.hidden), dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            native.moe_count(ids.data_ptr(), wide, pairs, self.experts, self.counts.data_ptr(), stream)
+            self.up_plan.layout_routed(self.counts.data_ptr(), self.up_ws.data_ptr(), stream)
+            self.down_plan.layout_routed(self.counts.data_ptr(), self.down_ws.data_ptr(), stream)
+            self.up_plan.place_routed(ids.data_ptr(), wide, pairs, choices, self.up_ws.data_ptr(),
+                                      self.cursors.data_ptr(), self.row_of_pair.data_ptr(),
+                                      self.token_of_row.data_ptr(), stream)
+            native.quantize_gather(x.data_ptr(), kind, self.a1.data_ptr(), self.s1.data_ptr(),
+                                   self.capacity, self.hidden, self.token_of_row.data_ptr(), stream)
+            self.up_plan.launch_groups(self.up_ws.data_ptr(), stream)
+            self.down_plan.launch_groups(self.down_ws.data_ptr(), stream)
+            native.moe_combine(self.y.data_ptr(), self.row_of_pair.data_ptr(), weights.data_ptr(),
+                               out.data_ptr(), tokens, choices, self.hidden, stream)
+        return out
+
+
 def moe_forward(x, topk_ids, topk_weights, w13, w13_scales, w2, w2_scales,
                 fused: bool | None = None) -> torch.Tensor:
     """One forward of a throw-away ``MoELayer`` (keep the layer to keep its plans)."""

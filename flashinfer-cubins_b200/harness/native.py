@@ -143,6 +143,15 @@ _PROTOTYPES = {
         ctypes.c_int, [_P, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, _P,
                        ctypes.c_int, _P, _P, _P, _P],
     ),
+    "nvfp4_moe_plan_create": (
+        ctypes.c_int, [ctypes.POINTER(_P), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                       ctypes.c_int, ctypes.c_int, ctypes.POINTER(Config)],
+    ),
+    "nvfp4_moe_bind": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "nvfp4_moe_layout": (ctypes.c_int, [_P, _P, _P, _P]),
+    "nvfp4_moe_place_routed": (
+        ctypes.c_int, [_P, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, _P, _P, _P, _P, _P, _P],
+    ),
     "nvfp4_moe_combine": (
         ctypes.c_int, [_P, _P, _P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
     ),
@@ -270,6 +279,17 @@ class Plan:
             ctypes.byref(handle), device, len(flat) // 3, array, cls._config(**config)))
         return cls(handle.value)
 
+    @classmethod
+    def routed(cls, device: int, out_kind: int, experts: int, n: int, k: int, max_rows: int,
+               **config):
+        """Grouped GEMM over ``experts`` groups whose row counts are decided on the device:
+        ``OUT_FP4`` = gate/up dual GEMM with NVFP4 output, ``OUT_F16`` = GEMM with FP16 output;
+        all groups share buffers of ``max_rows`` rows."""
+        handle = _P()
+        check(load().nvfp4_moe_plan_create(ctypes.byref(handle), device, experts, n, k, max_rows,
+                                           out_kind, cls._config(**config)))
+        return cls(handle.value)
+
     @property
     def handle(self) -> ctypes.c_void_p:
         if self._handle is None:
@@ -333,6 +353,26 @@ class Plan:
         check(load().nvfp4_group_dual_gemm_bind_fp4(
             self.handle, array(a), array(b1), array(b2), array(sfa), array(sfb1), array(sfb2),
             array(d_packed), array(d_scales), workspace, stream))
+
+    def bind_routed(self, a, sfa, b, sfb, d, workspace, stream, b2=None, sfb2=None,
+                    d_scales=0) -> None:
+        """The shared buffers (``a``, ``sfa``, ``d``, ``d_scales``: addresses) and every
+        expert's weights and scales (lists of addresses) of a routed plan, once."""
+        def array(values):
+            return (_P * len(values))(*values) if values is not None else None
+
+        check(load().nvfp4_moe_bind(self.handle, a, sfa, array(b), array(sfb), array(b2),
+                                    array(sfb2), d, d_scales, workspace, stream))
+
+    def layout_routed(self, counts: int, workspace, stream) -> None:
+        """Lay the groups out for the row counts in ``counts`` (device int32 array)."""
+        check(load().nvfp4_moe_layout(self.handle, counts, workspace, stream))
+
+    def place_routed(self, ids: int, ids_are_64bit: bool, pairs: int, choices: int, workspace,
+                     cursors: int, row_of_pair: int, token_of_row: int, stream) -> None:
+        """``moe_place`` with the first rows that ``layout_routed`` left in ``workspace``."""
+        check(load().nvfp4_moe_place_routed(ids, int(ids_are_64bit), pairs, choices, self.handle,
+                                            workspace, cursors, row_of_pair, token_of_row, stream))
 
     def launch_groups(self, workspace, stream) -> None:
         check(load().nvfp4_group_gemm_launch(self.handle, workspace, stream))

@@ -314,6 +314,38 @@ int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int cho
                     const int* first_rows, int rows, int* cursors, int* row_of_pair,
                     int* token_of_row, void* stream);
 
+/* Grouped GEMMs whose groups' row counts are decided on the device (the experts of a
+ * mixture-of-experts layer under a routing that changes with every forward): one plan and one
+ * bind for the life of the layer, no host read of the counts, every step a plain launch, so the
+ * whole forward can be captured in a CUDA graph.
+ *   nvfp4_moe_plan_create: `experts` groups of [m_g, n, k] with m_g unknown; out_kind
+ *     NVFP4_OUT_FP4 = the gate/up dual GEMM with NVFP4 output (n = rows of each of B1, B2, a
+ *     multiple of 64), NVFP4_OUT_F16 = a GEMM with FP16 output. All groups share one A buffer,
+ *     one D buffer (and their scale buffers) of `max_rows` rows (a multiple of 128): group g
+ *     owns a block of ceil(m_g / 128) * 128 rows, blocks in group order.
+ *   nvfp4_moe_bind: the shared buffers (a packed [max_rows][k/2], sfa blocked
+ *     [max_rows/128][ceil(k/64)][32][4][4], d [max_rows][n] FP16 or packed [max_rows][n/2] with
+ *     d_scales [max_rows/128][n/64][32][4][4]) and every expert's weights and scales (host
+ *     arrays of `experts` device pointers; b2 / sfb2 / d_scales for NVFP4_OUT_FP4 only).
+ *   nvfp4_moe_layout: from `counts` (device, `experts` ints, e.g. nvfp4_moe_count's) fills in
+ *     the groups' rows, first rows, tile counts and addresses in the workspace. Groups that do
+ *     not fit in max_rows are cut (callers size max_rows as pairs + 127 * experts, rounded up).
+ *   nvfp4_moe_place_routed: nvfp4_moe_place with the first rows that nvfp4_moe_layout wrote
+ *     (`rows` = max_rows; token_of_row has max_rows entries).
+ *   nvfp4_group_gemm_launch launches the plan. Rows of a block beyond m_g are neither
+ *     meaningful on input nor written on output.
+ * No counterpart in the reference, whose grouped launch takes its shapes from the host
+ * (harness/workloads/nvfp4_group_gemm.py:514-591). */
+int nvfp4_moe_plan_create(nvfp4_plan** plan, int device, int experts, int n, int k, int max_rows,
+                          int out_kind, const nvfp4_config* config);
+int nvfp4_moe_bind(const nvfp4_plan* plan, const void* a, const void* sfa, const void* const* b,
+                   const void* const* sfb, const void* const* b2, const void* const* sfb2, void* d,
+                   void* d_scales, void* workspace, void* stream);
+int nvfp4_moe_layout(const nvfp4_plan* plan, const int* counts, void* workspace, void* stream);
+int nvfp4_moe_place_routed(const void* ids, int ids_are_64bit, long long pairs, int choices,
+                           const nvfp4_plan* plan, void* workspace, int* cursors, int* row_of_pair,
+                           int* token_of_row, void* stream);
+
 /* The combine of that layer: out[t][:] = sum over j of weights[t][j] * y[row_of_pair[t * choices
  * + j]][:] in FP32 (`out` [tokens][hidden] FP32, `y` FP16 rows of `hidden` columns, `weights`
  * [tokens][choices] FP32, `row_of_pair` as nvfp4_moe_place wrote it; a negative row adds

@@ -136,6 +136,57 @@ def test_device_routing_places_every_pair_in_its_experts_block(tokens, experts, 
     assert routing.token_of_row.numel() == max(128, sum(-(-c // 128) * 128 for c in routing.counts))
 
 
+def test_routed_layer_needs_no_host_read_and_equals_the_planned_layer():
+    """RoutedMoELayer (row counts, layout, placement on the device; one pair of plans for any
+    routing) against MoELayer (plans per routing pattern) on several routings, with experts
+    that get nothing and experts that get more than one 128-row block: every row is computed
+    on its own, so the two must agree bit for bit. Then the routed forward captured once in a
+    CUDA graph is replayed on other tokens and other expert choices."""
+    device = torch.device("cuda:0")
+    hidden, inter, experts, choices, tokens = 512, 256, 7, 2, 400
+    w13, _, w13_blocked = quantised_weights(experts, 2 * inter, hidden, 1, device)
+    w2, _, w2_blocked = quantised_weights(experts, hidden, inter, 2, device)
+    planned = moe.MoELayer(w13, w13_blocked, w2, w2_blocked, fused=True)
+    routed = moe.RoutedMoELayer(w13, w13_blocked, w2, w2_blocked, max_pairs=tokens * choices)
+    g = torch.Generator().manual_seed(21)
+    cases = []
+    for seed in (1, 2, 3):
+        x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).to(device)
+        ids, weights = routing(tokens, experts, choices, seed, device)
+        if seed == 3:
+            ids = torch.zeros_like(ids)           # everything to one expert (and a duplicate)
+            ids[:, 1] = 3
+        want = planned.forward(x, ids, weights)
+        got = routed.forward(x, ids, weights)
+        assert torch.equal(got, want) and torch.isfinite(got).all() and got.abs().max() > 0
+        cases.append((x, ids, weights, want))
+    planned.check_status()
+    routed.check_status()
+    fewer = routed.forward(cases[0][0][:50], cases[0][1][:50], cases[0][2][:50])
+    assert torch.equal(fewer, planned.forward(cases[0][0][:50], cases[0][1][:50], cases[0][2][:50]))
+
+    side = torch.cuda.Stream(device)
+    x_in, ids_in, w_in = (t.clone() for t in cases[0][:3])
+    with torch.cuda.stream(side):
+        routed.forward(x_in, ids_in, w_in)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = routed.forward(x_in, ids_in, w_in)
+        for x, ids, weights, want in reversed(cases):
+            x_in.copy_(x)
+            ids_in.copy_(ids)
+            w_in.copy_(weights)
+            graph.replay()
+            side.synchronize()
+            assert torch.equal(out, want)
+    routed.check_status()
+    with pytest.raises(ValueError):
+        routed.forward(torch.cat([x_in, x_in]), torch.cat([ids_in, ids_in]), torch.cat([w_in, w_in]))
+    planned.close()
+    routed.close()
+
+
 def test_combine_kernel_matches_a_gather_and_a_batched_product():
     """nvfp4_moe_combine: the weighted sum of each token's rows in FP32, padding rows (-1)
     adding nothing."""
