@@ -947,7 +947,9 @@ def row_moe(device) -> list[dict]:
     buffers) called from Python, ``layer_graph_us`` the same forward replayed from a CUDA
     graph; ``kernels_us`` the two grouped launches alone replayed from a graph;
     ``shard_forward_us`` everything a rank does with the rows an all-to-all delivered (route,
-    gather-quantise, both GEMMs, un-permute; ``moe.ep_local_experts``). The busiest
+    gather-quantise, both GEMMs, un-permute; ``moe.ep_local_experts``);
+    ``routed_forward_us`` / ``routed_forward_graph_us`` the same work by ``RoutedMoELayer``,
+    which reads nothing back from the device. The busiest
     expert's rows are checked against the stage-by-stage torch reference."""
     from harness import moe
     from harness.models import MODELS
@@ -1049,6 +1051,39 @@ def row_moe(device) -> list[dict]:
         stop.record()
         torch.cuda.synchronize()
         shard_us = start.elapsed_time(stop) * 1e3 / repeats
+        # The same with nothing read back (RoutedMoELayer: counts, layout and placement on the
+        # device, one pair of plans for any routing), called from Python and replayed from a
+        # CUDA graph; it must give the planned layer's bits.
+        routed_layer = moe.RoutedMoELayer(w13, w13_scales, w2, w2_scales, max_pairs=routed)
+        ones = torch.ones((routed, 1), device=device)
+        ids = expert_of_row[:, None].contiguous()
+        same = torch.equal(routed_layer.forward(arrived, ids, ones), shard(arrived, expert_of_row).float())
+        for _ in range(2):
+            routed_layer.forward(arrived, ids, ones)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(repeats):
+            routed_layer.forward(arrived, ids, ones)
+        stop.record()
+        torch.cuda.synchronize()
+        routed_us = start.elapsed_time(stop) * 1e3 / repeats
+        with torch.cuda.stream(side):
+            routed_layer.forward(arrived, ids, ones)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    routed_layer.forward(arrived, ids, ones)
+            graph.replay()
+            side.synchronize()
+            start.record(side)
+            graph.replay()
+            stop.record(side)
+            side.synchronize()
+        routed_graph_us = start.elapsed_time(stop) * 1e3 / 20
+        routed_layer.check_status()
+        del graph
+        routed_layer.close()
         del arrived
         layer.check_status()
         del y
@@ -1070,6 +1105,8 @@ def row_moe(device) -> list[dict]:
                                 f"hidden {hidden}, intermediate {inter}",
                     "layer_us": layer_us, "layer_graph_us": layer_graph_us,
                     "shard_forward_us": shard_us,
+                    "routed_forward_us": routed_us, "routed_forward_graph_us": routed_graph_us,
+                    "routed_equals_planned": bool(same),
                     "kernels_us": kernels_us,
                     "us_per_call": kernels_us, "tflops": flops / kernels_us / 1e6,
                     "validated": bool(error < 1e-2), "relative_error_of_probed_expert": error,

@@ -1503,7 +1503,7 @@ int nvfp4_moe_layout(const nvfp4_plan* plan, const int* counts, void* workspace,
     return fail(NVFP4_E_INVALID_ARGUMENT, "counts or workspace is null or misaligned");
   }
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  moe_layout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  moe_layout_kernel<<<1, kMoeMaxExperts, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<ProblemDesc*>(ws + plan->off_table),
       reinterpret_cast<RoutedHeader*>(ws + plan->off_routed), counts,
       static_cast<int>(plan->problems.size()));

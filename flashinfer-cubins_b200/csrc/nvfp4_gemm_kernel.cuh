@@ -79,47 +79,64 @@ struct alignas(16) RoutedHeader {
   long long sfa_block_bytes;    // bytes of one 128-row atom row of A's scales
   long long sfd_block_bytes;    // the same for D's scales
   int max_rows;                 // rows of the shared buffers (a multiple of 128)
-  int overflow;                 // set if the groups' padded rows did not fit
+  int overflow;                 // set (and left set) if some layout's padded rows did not fit
   int first_rows[kMoeMaxExperts];  // written by moe_layout_kernel: first row of every group
 };
 
 // Fills in what depends on the groups' row counts: every group's m, tile counts, first row
-// in the shared buffers (blocks padded to 128 rows), operand addresses, and the totals. One
-// thread walks the groups (at most 512); the rest of the table was written by the bind.
-__global__ void moe_layout_kernel(ProblemDesc* __restrict__ table, RoutedHeader* __restrict__ header,
-                                  const int* __restrict__ counts, int groups) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  long long tiles = 0;
-  int row = 0;
-  int overflow = 0;
-  for (int g = 0; g < groups; ++g) {
-    ProblemDesc pd = table[g];
-    int m = counts[g];
-    if (m < 0) m = 0;
-    int blocks = (m + 127) / 128;
-    if (row + blocks * 128 > header->max_rows) {  // does not fit: drop what is beyond
-      blocks = (header->max_rows - row) / 128;
-      m = min(m, blocks * 128);
-      overflow = 1;
+// in the shared buffers (blocks padded to 128 rows), operand addresses, and the totals; the
+// rest of the table was written by the bind. One CTA of kMoeMaxExperts threads, one group per
+// thread, two prefix sums in shared memory (blocks before a group; blocks that fit).
+__global__ void __launch_bounds__(kMoeMaxExperts)
+moe_layout_kernel(ProblemDesc* __restrict__ table, RoutedHeader* __restrict__ header,
+                  const int* __restrict__ counts, int groups) {
+  __shared__ int scan[kMoeMaxExperts];
+  const int g = threadIdx.x;
+  const int max_blocks = header->max_rows / 128;
+  auto exclusive_prefix = [&](int value) {
+    // Inclusive Hillis-Steele scan, then shifted by the own value.
+    scan[g] = value;
+    __syncthreads();
+    for (int step = 1; step < kMoeMaxExperts; step *= 2) {
+      const int other = g >= step ? scan[g - step] : 0;
+      __syncthreads();
+      scan[g] += other;
+      __syncthreads();
     }
-    pd.m = m;
-    pd.tiles_m = blocks;
-    pd.sf_mb = blocks;
-    pd.a_row0 = row;
-    pd.sfa = header->sfa_base + static_cast<long long>(row / 128) * header->sfa_block_bytes;
-    pd.d = header->d_base + static_cast<long long>(row) * header->d_row_bytes;
-    pd.sfd = header->sfd_base != nullptr
-                 ? header->sfd_base + static_cast<long long>(row / 128) * header->sfd_block_bytes
-                 : nullptr;
-    pd.tile_begin = tiles;
-    pd.unit_begin = tiles * pd.k_tiles;
-    table[g] = pd;
+    const int before = scan[g] - value;
+    __syncthreads();
+    return before;
+  };
+  int m = g < groups ? max(counts[g], 0) : 0;
+  int blocks = (m + 127) / 128;
+  const int first_block = exclusive_prefix(blocks);
+  // Groups that do not fit in the shared buffers are cut (the caller sized them too small).
+  const int fits = min(blocks, max(max_blocks - first_block, 0));
+  const bool cut = fits < blocks;
+  blocks = fits;
+  m = min(m, blocks * 128);
+  const int tiles_before = exclusive_prefix(blocks);  // in units of one row of tiles
+  if (g < groups) {
+    ProblemDesc* pd = table + g;
+    const int row = first_block * 128;
+    const long long tile_begin = static_cast<long long>(tiles_before) * pd->tiles_n;
+    pd->m = m;
+    pd->tiles_m = blocks;
+    pd->sf_mb = blocks;
+    pd->a_row0 = row;
+    pd->sfa = header->sfa_base + static_cast<long long>(first_block) * header->sfa_block_bytes;
+    pd->d = header->d_base + static_cast<long long>(row) * header->d_row_bytes;
+    pd->sfd = header->sfd_base != nullptr
+                  ? header->sfd_base + static_cast<long long>(first_block) * header->sfd_block_bytes
+                  : nullptr;
+    pd->tile_begin = tile_begin;
+    pd->unit_begin = tile_begin * pd->k_tiles;
     header->first_rows[g] = row;
-    tiles += static_cast<long long>(blocks) * pd.tiles_n;
-    row += blocks * 128;
+    if (cut) header->overflow = 1;
+    if (g == groups - 1) {
+      header->total_tiles = tile_begin + static_cast<long long>(blocks) * pd->tiles_n;
+    }
   }
-  header->total_tiles = tiles;
-  header->overflow = overflow;
 }
 
 enum : int {
