@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstddef>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -1543,6 +1544,20 @@ int nvfp4_plan_status(const nvfp4_plan* plan, void* workspace, void* stream, int
   CUDA_TRY(cudaMemcpyAsync(&value, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
   CUDA_TRY(cudaStreamSynchronize(s));
   *status = value;
+  if (plan->routed && value == 0) {
+    // A layout whose groups did not fit in the shared buffers cut them: say so once.
+    uint8_t* header = static_cast<uint8_t*>(workspace) + plan->off_routed;
+    int overflow = 0;
+    CUDA_TRY(cudaMemcpyAsync(&overflow, header + offsetof(RoutedHeader, overflow), sizeof(int),
+                             cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    if (overflow != 0) {
+      CUDA_TRY(cudaMemsetAsync(header + offsetof(RoutedHeader, overflow), 0, sizeof(int), s));
+      return fail(NVFP4_E_UNSUPPORTED_SHAPE,
+                  "a routed layout needed more than the plan's %d rows; groups were cut",
+                  plan->routed_rows);
+    }
+  }
   if (value != 0) {
     // A launch that gave up may have left tile arrival counters of the stream-K schedule
     // non-zero: clear them with the status word, as nvfp4_plan_init_workspace does, so that

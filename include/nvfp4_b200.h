@@ -329,7 +329,8 @@ int nvfp4_moe_place(const void* ids, int ids_are_64bit, long long pairs, int cho
  *     arrays of `experts` device pointers; b2 / sfb2 / d_scales for NVFP4_OUT_FP4 only).
  *   nvfp4_moe_layout: from `counts` (device, `experts` ints, e.g. nvfp4_moe_count's) fills in
  *     the groups' rows, first rows, tile counts and addresses in the workspace. Groups that do
- *     not fit in max_rows are cut (callers size max_rows as pairs + 127 * experts, rounded up).
+ *     not fit in max_rows are cut (callers size max_rows as pairs + 127 * experts, rounded up);
+ *     nvfp4_plan_status then reports NVFP4_E_UNSUPPORTED_SHAPE once.
  *   nvfp4_moe_place_routed: nvfp4_moe_place with the first rows that nvfp4_moe_layout wrote
  *     (`rows` = max_rows; token_of_row has max_rows entries).
  *   nvfp4_group_gemm_launch launches the plan. Rows of a block beyond m_g are neither

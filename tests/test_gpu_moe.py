@@ -187,6 +187,35 @@ def test_routed_layer_needs_no_host_read_and_equals_the_planned_layer():
     routed.close()
 
 
+def test_routed_layout_that_does_not_fit_is_reported():
+    """A routed plan whose shared buffers are too small for the counts it is given cuts the
+    groups and says so through the status call, once; a layout that fits clears nothing else."""
+    device = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    plan = native.Plan.routed(0, native.OUT_F16, 3, 256, 256, 256)
+    ws = torch.zeros(max(plan.workspace_bytes(), 256), dtype=torch.uint8, device=device)
+    plan.init_workspace(ws.data_ptr(), stream)
+    a = torch.zeros((256, 128), dtype=torch.uint8, device=device)
+    sfa = torch.zeros((2, 4, 512), dtype=torch.uint8, device=device)
+    b = torch.zeros((3, 256, 128), dtype=torch.uint8, device=device)
+    sfb = torch.zeros((3, 2, 4, 512), dtype=torch.uint8, device=device)
+    d = torch.zeros((256, 256), dtype=torch.float16, device=device)
+    plan.bind_routed(a.data_ptr(), sfa.data_ptr(), [b[e].data_ptr() for e in range(3)],
+                     [sfb[e].data_ptr() for e in range(3)], d.data_ptr(), ws.data_ptr(), stream)
+    fits = torch.tensor([100, 0, 128], dtype=torch.int32, device=device)
+    plan.layout_routed(fits.data_ptr(), ws.data_ptr(), stream)
+    plan.launch_groups(ws.data_ptr(), stream)
+    assert plan.status(ws.data_ptr(), stream) == 0
+    too_many = torch.tensor([100, 100, 100], dtype=torch.int32, device=device)
+    plan.layout_routed(too_many.data_ptr(), ws.data_ptr(), stream)
+    plan.launch_groups(ws.data_ptr(), stream)
+    with pytest.raises(ValueError):
+        plan.status(ws.data_ptr(), stream)
+    plan.layout_routed(fits.data_ptr(), ws.data_ptr(), stream)
+    assert plan.status(ws.data_ptr(), stream) == 0
+    plan.destroy()
+
+
 def test_combine_kernel_matches_a_gather_and_a_batched_product():
     """nvfp4_moe_combine: the weighted sum of each token's rows in FP32, padding rows (-1)
     adding nothing."""
