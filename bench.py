@@ -1123,7 +1123,8 @@ def row_expert_parallel(info, device) -> dict:
     """The MoE layer expert-parallel over the ranks of this run: DeepSeek-V3's 256 experts
     (hidden 7168, intermediate 2048) in contiguous blocks per rank, 2,048 BF16 tokens per rank
     routed top-8 over all experts; one forward = route, two all-to-all exchanges (rows out as
-    BF16, back as FP16), the local experts on the grouped kernels, weighted combine. Expert e's
+    BF16, back as FP16), the local experts on the routed grouped kernels (``RoutedMoELayer``: no
+    host read on the receiving side), weighted combine. Expert e's
     weights come from seed e on whichever rank owns it, so rank 0 can rebuild any expert and
     checks a few of its tokens against the stage-by-stage torch reference."""
     from harness import moe
@@ -1148,7 +1149,9 @@ def row_expert_parallel(info, device) -> dict:
 
     mine = range(rank * per_rank, min(experts, (rank + 1) * per_rank))
     parts = [expert_weights(e) for e in mine]
-    layer = moe.MoELayer(*(torch.stack([p[i] for p in parts]) for i in range(4)), fused=True)
+    # A layer that reads nothing back, made for as many pairs as can arrive at this rank.
+    layer = moe.RoutedMoELayer(*(torch.stack([p[i] for p in parts]) for i in range(4)),
+                               max_pairs=tokens * spec.top_k * world)
     del parts
     g = torch.Generator(device=device).manual_seed(7000 + rank)
     x = torch.randn((tokens, hidden), device=device, generator=g).to(torch.bfloat16)

@@ -455,23 +455,21 @@ class RoutedMoELayer:
         self.up_plan.status(self.up_ws.data_ptr(), stream)
         self.down_plan.status(self.down_ws.data_ptr(), stream)
 
-    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
-        """As ``MoELayer.forward`` (``x`` ``[T, H]`` FP32 or BF16, ids int32/int64 ``[T, K]`` in
-        ``[0, E)``, weights ``[T, K]``; FP32 ``[T, H]`` out), asynchronous from start to end."""
+    def _experts(self, x: torch.Tensor, topk_ids: torch.Tensor) -> None:
+        """Everything up to the down projection: afterwards ``self.y[self.row_of_pair[i]]`` is
+        the result of pair i."""
         tokens, choices = topk_ids.shape
         pairs = tokens * choices
-        if x.shape != (tokens, self.hidden) or topk_weights.shape != topk_ids.shape:
-            raise ValueError("activations, ids and weights do not match")
+        if x.shape != (tokens, self.hidden):
+            raise ValueError("activations and ids do not match")
         if pairs > self.max_pairs:
             raise ValueError(f"{pairs} pairs; the layer was made for {self.max_pairs}")
         if x.dtype not in (torch.float32, torch.bfloat16) or not x.is_contiguous():
             x = x.float().contiguous()
         ids = topk_ids if topk_ids.dtype in (torch.int32, torch.int64) else topk_ids.long()
         ids = ids.contiguous()
-        weights = topk_weights.float().contiguous()
         wide = ids.dtype == torch.int64
         kind = native.IN_F32 if x.dtype == torch.float32 else native.IN_BF16
-        out = torch.empty((tokens, self.hidden), dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
             stream = torch.cuda.current_stream(self.device).cuda_stream
             native.moe_count(ids.data_ptr(), wide, pairs, self.experts, self.counts.data_ptr(), stream)
@@ -484,9 +482,30 @@ class RoutedMoELayer:
                                    self.capacity, self.hidden, self.token_of_row.data_ptr(), stream)
             self.up_plan.launch_groups(self.up_ws.data_ptr(), stream)
             self.down_plan.launch_groups(self.down_ws.data_ptr(), stream)
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """As ``MoELayer.forward`` (``x`` ``[T, H]`` FP32 or BF16, ids int32/int64 ``[T, K]`` in
+        ``[0, E)``, weights ``[T, K]``; FP32 ``[T, H]`` out), asynchronous from start to end."""
+        tokens, choices = topk_ids.shape
+        if topk_weights.shape != topk_ids.shape:
+            raise ValueError("ids and weights do not match")
+        weights = topk_weights.float().contiguous()
+        self._experts(x, topk_ids)
+        out = torch.empty((tokens, self.hidden), dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
             native.moe_combine(self.y.data_ptr(), self.row_of_pair.data_ptr(), weights.data_ptr(),
-                               out.data_ptr(), tokens, choices, self.hidden, stream)
+                               out.data_ptr(), tokens, choices, self.hidden,
+                               torch.cuda.current_stream(self.device).cuda_stream)
         return out
+
+    def apply_rows(self, rows: torch.Tensor, expert_ids: torch.Tensor) -> torch.Tensor:
+        """Every row through its one expert (``expert_ids`` ``[R]``): FP16 ``[R, H]`` in the
+        order the rows came. What a rank does with the rows an all-to-all delivered
+        (``moe_forward_ep``)."""
+        if rows.shape[0] == 0:
+            return torch.empty((0, self.hidden), dtype=torch.float16, device=self.device)
+        self._experts(rows, expert_ids.reshape(-1, 1))
+        return self.y.index_select(0, self.row_of_pair[:rows.shape[0]])
 
 
 def moe_forward(x, topk_ids, topk_weights, w13, w13_scales, w2, w2_scales,
@@ -617,9 +636,12 @@ def moe_forward_ep(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.
     return _combine(back, place, topk_weights)
 
 
-def ep_local_experts(layer: MoELayer) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
-    """``local_experts`` for ``moe_forward_ep`` on a GPU: the rank's ``MoELayer`` applied to
-    the received rows (each row has exactly one expert, weight 1)."""
+def ep_local_experts(layer: MoELayer | RoutedMoELayer) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
+    """``local_experts`` for ``moe_forward_ep`` on a GPU: the rank's layer applied to the
+    received rows (each row has exactly one expert, weight 1). A ``RoutedMoELayer`` (made for
+    as many pairs as can arrive) does it without reading anything back."""
+    if isinstance(layer, RoutedMoELayer):
+        return layer.apply_rows
 
     def apply(rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
         if rows.shape[0] == 0:

@@ -273,8 +273,14 @@ layer = moe.MoELayer(w13[mine].contiguous(), w13_blocked[mine].contiguous(),
                      w2[mine].contiguous(), w2_blocked[mine].contiguous())
 out = moe.moe_forward_ep(x, ids, weights, experts, moe.ep_local_experts(layer))
 layer.check_status()
+routed = moe.RoutedMoELayer(w13[mine].contiguous(), w13_blocked[mine].contiguous(),
+                            w2[mine].contiguous(), w2_blocked[mine].contiguous(), max_pairs=4096)
+again = moe.moe_forward_ep(x, ids, weights, experts, moe.ep_local_experts(routed))
+routed.check_status()
 ref = moe.moe_reference(x, ids, weights, w13, w13_logical, w2, w2_logical, fused=True)
 ok = (out - ref).norm().item() <= 3e-3 * ref.norm().item() and bool(torch.isfinite(out).all())
+ok = ok and torch.equal(out, again)
+routed.close()
 flag = torch.tensor([1.0 if ok else 0.0], device=device)
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 layer.close()
