@@ -23,9 +23,14 @@ Layout choices that keep every stage a plain kernel launch on whole buffers:
   blocked scales ``[E, 2I/128, ceil(H/64), 32, 4, 4]``; ``w2`` packed ``[E, H, I/2]``
   with ``[E, ceil(H/128), ceil(I/64), 32, 4, 4]``. With ``fused=True`` the intermediate size
   must be a multiple of 128 (the up projection's scales then start on an atom row).
-* Plans, workspaces and the buffers between the stages are kept per tuple of expert row
-  counts and bound once (``MoELayer``): a forward with a routing pattern seen before is one
+* ``MoELayer`` keeps plans, workspaces and the buffers between the stages per tuple of expert
+  row counts and binds them once: a forward with a routing pattern seen before is one
   quantiser launch and two grouped GEMM launches, with nothing allocated, encoded or bound.
+  It reads the row counts back (the plans' shapes are the host's).
+* ``RoutedMoELayer`` reads nothing back: its two plans take the experts' row counts from the
+  device (``nvfp4_moe_plan_create`` and friends), all experts share buffers sized for the
+  worst case, and one plan pair serves every routing, so a forward is a fixed sequence of
+  launches that a CUDA graph can hold. Both layers give the same bits.
 
 Expert parallelism (``moe_forward_ep``): rank r owns experts ``[r E/W, (r+1) E/W)``. Every
 rank routes its own tokens, sends each (token, choice) row to the owner of its expert with
